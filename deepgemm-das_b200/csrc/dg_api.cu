@@ -1,0 +1,392 @@
+// C ABI of libdeepgemm_b200.so: argument validation, TMA descriptor encoding, kernel
+// selection and launch.  No torch types, no allocation, no stream synchronisation.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "deepgemm_b200.h"
+#include "dg_grouped_gemm.cuh"
+#include "dg_pack.cuh"
+
+namespace {
+
+using namespace dg;
+
+thread_local int tl_last_cuda_error = 0;
+std::atomic<long long> g_launch_count{0};
+
+int cuda_fail(cudaError_t e) {
+  tl_last_cuda_error = static_cast<int>(e);
+  return DG_ERR_CUDA;
+}
+
+// ---- per-device cache (filled once; the reference queries device properties per call,
+//      csrc/arch/gfx936_gfx938_shared/m_grouped_w8a8_gemm_nt_masked.cu:85-89)
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  std::once_flag once;
+  int status = DG_ERR_NO_DEVICE;
+  int sm_count = 0;
+  int max_smem = 0;
+  int cc = 0;
+};
+DeviceInfo g_dev[kMaxDevices];
+
+int device_info(const DeviceInfo** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    tl_last_cuda_error = static_cast<int>(e);
+    (void)cudaGetLastError();
+    return DG_ERR_NO_DEVICE;
+  }
+  if (dev < 0 || dev >= kMaxDevices) return DG_ERR_NO_DEVICE;
+  DeviceInfo& d = g_dev[dev];
+  std::call_once(d.once, [&]() {
+    int major = 0, minor = 0;
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&d.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) !=
+            cudaSuccess ||
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) {
+      d.status = DG_ERR_NO_DEVICE;
+      return;
+    }
+    d.cc = major * 10 + minor;
+    d.status = (major == 10) ? DG_OK : DG_ERR_NO_DEVICE;
+  });
+  *out = &d;
+  return d.status;
+}
+
+// ---- cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link)
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+EncodeTiledFn get_encode() {
+  std::call_once(g_encode_once, []() {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    else
+      (void)cudaGetLastError();
+  });
+  return g_encode;
+}
+
+// rank-2 or rank-3 tiled map; dims/strides innermost first, strides in bytes for dims 1..
+int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
+               const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+               CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return DG_ERR_CUDA;
+  cuuint64_t gdim[3] = {1, 1, 1};
+  cuuint64_t gstr[2] = {0, 0};
+  cuuint32_t bdim[3] = {1, 1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  CUresult r = enc(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr,
+                   bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    tl_last_cuda_error = 10000 + static_cast<int>(r);
+    return DG_ERR_CUDA;
+  }
+  return DG_OK;
+}
+
+// ---- kernel instantiations: (kind, BN) -> stages so the ring holds ~192-200 KB
+template <int KIND, int BN>
+struct StagesFor {
+  static constexpr int per_stage =
+      kATileBytes + BN * kRowBytes + (KIND == DG_KIND_W4A8 ? BN * 64 : 0);
+  static constexpr int value = (200 * 1024) / per_stage;
+};
+
+struct Problem {
+  int kind, scale_mode, mode;
+  const void* a;
+  const void* b;
+  void* d;
+  const float* a_scale;
+  const float* b_scale;
+  const int32_t* sched;
+  int G, M, N, K, block_n, expected_m;
+  void* debug_acc;
+  int32_t* status;
+};
+
+template <int KIND, int BN>
+int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
+  constexpr int STAGES = StagesFor<KIND, BN>::value;
+  using L = SmemLayout<KIND, BN, STAGES>;
+  static_assert(STAGES >= 2, "ring too shallow");
+  auto kernel = grouped_gemm_kernel<KIND, BN, STAGES>;
+
+  const int esize = (KIND == DG_KIND_BF16) ? 2 : 1;
+  const int elems_per_row = kRowBytes / esize;  // A elements per 128-byte K block
+  KernelParams p{};
+  p.mode = pr.mode;
+  p.scale_mode = pr.scale_mode;
+  p.G = pr.G;
+  p.M = pr.M;
+  p.N = pr.N;
+  p.K = pr.K;
+  p.kblocks = pr.K / elems_per_row;
+  p.n_tiles = (pr.N + BN - 1) / BN;
+  p.m_blocks = (pr.M + kBM - 1) / kBM;
+  p.sched = pr.sched;
+  p.a_scale = pr.a_scale;
+  p.b_scale = pr.b_scale;
+  p.d = static_cast<__nv_bfloat16*>(pr.d);
+  p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
+  p.status = pr.status;
+
+  const long long max_items =
+      (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : (long long)p.m_blocks) * p.n_tiles;
+  if (max_items <= 0) return DG_OK;
+  const int table_bytes =
+      (pr.mode == MODE_MASKED) ? (2 * pr.G + 1) * 4 : p.m_blocks * 4;
+  const int smem_bytes = L::total(table_bytes);
+  if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
+
+  // A: rows of K elements.  Masked: (K, max_m, G) so a box never crosses into the next
+  // group; contiguous: (K, M_total).  Rows past the extent read as zero.
+  const CUtensorMapDataType dt_a =
+      (KIND == DG_KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if (pr.mode == MODE_MASKED) {
+    const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
+    const uint64_t strides[2] = {(uint64_t)pr.K * esize, (uint64_t)pr.M * pr.K * esize};
+    const uint32_t box[3] = {(uint32_t)elems_per_row, (uint32_t)kBM, 1u};
+    rc = encode_map(&tm_a, dt_a, 3, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
+    const uint64_t strides[1] = {(uint64_t)pr.K * esize};
+    const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)kBM};
+    rc = encode_map(&tm_a, dt_a, 2, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc != DG_OK) return rc;
+  // B (packed): a flat list of G*kblocks*N rows, 128 bytes each (64 for W4A8), so a
+  // BN-row box is one contiguous span.  W4A8 rows land unswizzled; the unpack warps
+  // write the swizzled int8 tile themselves.
+  {
+    const uint64_t rows = (uint64_t)pr.G * p.kblocks * pr.N;
+    if (KIND == DG_KIND_W4A8) {
+      const uint64_t dims[2] = {64, rows};
+      const uint64_t strides[1] = {64};
+      const uint32_t box[2] = {64, (uint32_t)BN};
+      rc = encode_map(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.b, dims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else {
+      const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
+      const uint64_t strides[1] = {(uint64_t)kRowBytes};
+      const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)BN};
+      rc = encode_map(&tm_b, dt_a, 2, pr.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+  }
+  if (rc != DG_OK) return rc;
+
+  // Opt in to the large shared-memory carve-out once per device and instantiation.
+  static std::atomic<unsigned long long> configured{0};
+  int devid = 0;
+  cudaGetDevice(&devid);
+  const unsigned long long bit = 1ull << (devid & 63);
+  if ((configured.load(std::memory_order_acquire) & bit) == 0) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    if (e != cudaSuccess) return cuda_fail(e);
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+
+  const int grid = static_cast<int>(max_items < dev.sm_count ? max_items : dev.sm_count);
+  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_b, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate_and_launch(const Problem& pr, cudaStream_t stream) {
+  if (pr.kind < DG_KIND_I8 || pr.kind > DG_KIND_BF16) return DG_ERR_BAD_KIND;
+  if (pr.scale_mode < DG_SCALE_PER_CHANNEL || pr.scale_mode > DG_SCALE_NONE)
+    return DG_ERR_BAD_SCALE_MODE;
+  if ((pr.kind == DG_KIND_BF16) != (pr.scale_mode == DG_SCALE_NONE)) return DG_ERR_BAD_SCALE_MODE;
+  if (pr.G < 1 || pr.M < 0 || pr.N < 16 || pr.K < 1) return DG_ERR_BAD_SHAPE;
+  if (pr.G > DG_MAX_GROUPS) return DG_ERR_TOO_LARGE;
+  if (pr.mode == MODE_CONTIG && pr.M > DG_MAX_CONTIG_ROWS) return DG_ERR_TOO_LARGE;
+  if (pr.N % 16 != 0) return DG_ERR_BAD_SHAPE;
+  const int kq = (pr.kind == DG_KIND_BF16) ? 64 : 128;
+  if (pr.K % kq != 0) return DG_ERR_BAD_SHAPE;
+  if ((long long)pr.G * (pr.K / kq) * pr.N > 0x7fffffffLL) return DG_ERR_TOO_LARGE;
+  if (pr.M == 0) return DG_OK;
+  if (!pr.a || !pr.b || !pr.d || !pr.sched) return DG_ERR_NULL_POINTER;
+  if (pr.scale_mode != DG_SCALE_NONE && (!pr.a_scale || !pr.b_scale)) return DG_ERR_NULL_POINTER;
+  if (!aligned16(pr.a) || !aligned16(pr.b) || !aligned16(pr.d)) return DG_ERR_BAD_ALIGNMENT;
+  if (pr.scale_mode == DG_SCALE_PER_CHANNEL && !aligned16(pr.b_scale)) return DG_ERR_BAD_ALIGNMENT;
+  if (pr.debug_acc && !aligned16(pr.debug_acc)) return DG_ERR_BAD_ALIGNMENT;
+  if (pr.block_n != 0 && pr.block_n != 128 && pr.block_n != 256) return DG_ERR_BAD_ARGUMENT;
+
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != DG_OK) return rc;
+
+  // Tile width.  Weight-streaming shapes (few rows per group) want many equal items so the
+  // 148 SMs stay balanced: BN = 128.  Compute-bound shapes want the larger tile, which
+  // halves the shared-memory traffic per flop: BN = 256.
+  int bn = pr.block_n;
+  if (bn == 0) {
+    if (pr.mode == MODE_CONTIG)
+      bn = (pr.N >= 256) ? 256 : 128;
+    else
+      bn = (pr.expected_m > 256 && pr.N >= 256) ? 256 : 128;
+  }
+  if (pr.kind == DG_KIND_W4A8) bn = 128;
+
+  switch (pr.kind) {
+    case DG_KIND_I8:
+      return bn == 256 ? launch<DG_KIND_I8, 256>(pr, *dev, stream)
+                       : launch<DG_KIND_I8, 128>(pr, *dev, stream);
+    case DG_KIND_E4M3:
+      return bn == 256 ? launch<DG_KIND_E4M3, 256>(pr, *dev, stream)
+                       : launch<DG_KIND_E4M3, 128>(pr, *dev, stream);
+    case DG_KIND_BF16:
+      return bn == 256 ? launch<DG_KIND_BF16, 256>(pr, *dev, stream)
+                       : launch<DG_KIND_BF16, 128>(pr, *dev, stream);
+    case DG_KIND_W4A8:
+      return launch<DG_KIND_W4A8, 128>(pr, *dev, stream);
+  }
+  return DG_ERR_BAD_KIND;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dg_masked_gemm(const dg_masked_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  Problem pr{};
+  pr.kind = a->kind;
+  pr.scale_mode = a->scale_mode;
+  pr.mode = MODE_MASKED;
+  pr.a = a->a;
+  pr.b = a->b_packed;
+  pr.d = a->d;
+  pr.a_scale = a->a_scale;
+  pr.b_scale = a->b_scale;
+  pr.sched = a->masked_m;
+  pr.G = a->num_groups;
+  pr.M = a->max_m;
+  pr.N = a->n;
+  pr.K = a->k;
+  pr.block_n = a->block_n;
+  pr.expected_m = a->expected_m;
+  pr.debug_acc = a->debug_acc;
+  pr.status = a->status;
+  return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
+}
+
+int dg_contig_gemm(const dg_contig_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  Problem pr{};
+  pr.kind = a->kind;
+  pr.scale_mode = a->scale_mode;
+  pr.mode = MODE_CONTIG;
+  pr.a = a->a;
+  pr.b = a->b_packed;
+  pr.d = a->d;
+  pr.a_scale = a->a_scale;
+  pr.b_scale = a->b_scale;
+  pr.sched = a->m_indices;
+  pr.G = a->num_groups;
+  pr.M = a->m_total;
+  pr.N = a->n;
+  pr.K = a->k;
+  pr.block_n = a->block_n;
+  pr.expected_m = 0;
+  pr.debug_acc = a->debug_acc;
+  pr.status = a->status;
+  return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
+}
+
+static int pack_common(bool unpack, int32_t kind, const void* src, void* dst, int32_t G,
+                       int32_t n, int32_t k, int32_t nibble_order, void* stream) {
+  if (kind < DG_KIND_I8 || kind > DG_KIND_BF16) return DG_ERR_BAD_KIND;
+  if (!src || !dst) return DG_ERR_NULL_POINTER;
+  if (G < 1 || n < 1 || k < 1) return DG_ERR_BAD_SHAPE;
+  const int kq = (kind == DG_KIND_BF16) ? 64 : 128;
+  if (k % kq != 0) return DG_ERR_BAD_SHAPE;
+  if (!aligned16(src) || !aligned16(dst)) return DG_ERR_BAD_ALIGNMENT;
+  if (nibble_order != DG_NIBBLE_HIGH_FIRST && nibble_order != DG_NIBBLE_LOW_FIRST)
+    return DG_ERR_BAD_ARGUMENT;
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != DG_OK) return rc;
+  cudaError_t e = dg::launch_pack(unpack, kind, src, dst, G, n, k, nibble_order,
+                                  static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
+int dg_pack_weight(int32_t kind, const void* src, void* dst, int32_t G, int32_t n, int32_t k,
+                   int32_t nibble_order, void* stream) {
+  return pack_common(false, kind, src, dst, G, n, k, nibble_order, stream);
+}
+
+int dg_unpack_weight(int32_t kind, const void* src, void* dst, int32_t G, int32_t n, int32_t k,
+                     int32_t nibble_order, void* stream) {
+  return pack_common(true, kind, src, dst, G, n, k, nibble_order, stream);
+}
+
+int64_t dg_query(int32_t what) {
+  if (what == DG_QUERY_ABI_VERSION) return DG_ABI_VERSION;
+  if (what == DG_QUERY_LAUNCH_COUNT) return g_launch_count.load(std::memory_order_relaxed);
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (what == DG_QUERY_CC && dev != nullptr && dev->cc > 0) return dev->cc;
+  if (rc != DG_OK) return rc;
+  switch (what) {
+    case DG_QUERY_SM_COUNT: return dev->sm_count;
+    case DG_QUERY_MAX_SMEM: return dev->max_smem;
+    case DG_QUERY_CC: return dev->cc;
+    default: return DG_ERR_BAD_ARGUMENT;
+  }
+}
+
+const char* dg_strerror(int code) {
+  switch (code) {
+    case DG_OK: return "ok";
+    case DG_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case DG_ERR_BAD_KIND: return "unknown operand kind";
+    case DG_ERR_BAD_SHAPE:
+      return "bad shape: need N % 16 == 0, K % 128 == 0 (K % 64 for bf16), groups >= 1";
+    case DG_ERR_BAD_ALIGNMENT: return "a base pointer is not 16-byte aligned";
+    case DG_ERR_BAD_SCALE_MODE: return "scale mode does not fit the operand kind";
+    case DG_ERR_NO_DEVICE: return "no current CUDA device of compute capability 10.x (B200)";
+    case DG_ERR_CUDA: return "a CUDA call failed (see dg_last_cuda_error)";
+    case DG_ERR_TOO_LARGE: return "a size exceeds the library maximum";
+    case DG_ERR_BAD_ARGUMENT: return "bad argument value";
+    default: return "unknown status code";
+  }
+}
+
+int dg_last_cuda_error(void) { return tl_last_cuda_error; }
+
+}  // extern "C"

@@ -1,0 +1,467 @@
+// Persistent, warp-specialised grouped GEMM kernel for sm_100a.
+//
+//   D[row][n] = bf16( (float(sum_k A[row][k] * B[g][n][k]) * a_scale[row]) * b_scale[g][n] )
+//
+// One thread block per SM walks a list of work items (group g, 128-row block, BN-column
+// tile) derived on the device from masked_m (masked layout) or m_indices (contiguous
+// layout), so groups without rows and padding row blocks produce no items at all.
+//
+// Roles inside a block
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A tile
+//               (128 rows x 128 bytes of K) and the weight tile (BN rows x 128 bytes of K,
+//               one contiguous span of the packed weight) into a STAGES-deep ring.
+//   warp 1      UMMA issuer: one lane issues four tcgen05.mma (K = 32 bytes each) per
+//               ring stage into one of two TMEM accumulators (128 lanes x BN columns),
+//               and owns TMEM allocation.
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator, scale, bf16 convert, predicated
+//               16-byte stores; overlaps the next item's main loop through the second
+//               TMEM accumulator.
+//   warps 6..9  (W4A8 only) unpack: expand the packed int4 stage to an int8 tile in the
+//               128-byte-swizzled layout the UMMA descriptor expects.
+//
+// Every wait on an mbarrier is bounded; on expiry the block records a status word and
+// leaves through the common tear-down path (TMEM is always released).
+//
+// Semantics follow the reference kernels
+//   csrc/arch/gfx936_gfx938_shared/m_grouped_fp8_gemm_nt_maksed_low_latency.cu:272-604 (masked)
+//   csrc/include/m_grouped_i8_gemm_nt_contiguous/bm128_bn256_bk64_nloop4.inc.cuh:206-652 (contiguous)
+//   csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_masked_hipc.cu:678-963 (W4A8 unpack rule)
+// but none of their structure: those stream operands through registers on wave64 hardware.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "deepgemm_b200.h"
+#include "dg_ptx.cuh"
+
+namespace dg {
+
+constexpr int kBM = 128;         // rows of A per tile = UMMA M
+constexpr int kRowBytes = 128;   // bytes of K per shared-memory row (one swizzle span)
+constexpr int kATileBytes = kBM * kRowBytes;
+constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per block on sm_100
+
+enum : int { MODE_MASKED = 0, MODE_CONTIG = 1 };
+
+// Where a bounded wait gave up (reported in status[2]).
+enum : int {
+  SITE_PRODUCER_EMPTY = 1,
+  SITE_MMA_ACC_EMPTY = 2,
+  SITE_MMA_FULL = 3,
+  SITE_MMA_UNPACKED = 4,
+  SITE_EPI_ACC_FULL = 5,
+  SITE_UNPACK_FULL = 6,
+  SITE_PRODUCER_DRAIN = 7
+};
+
+struct KernelParams {
+  int mode;        // MODE_MASKED / MODE_CONTIG
+  int scale_mode;  // dg_scale_mode
+  int G;           // groups
+  int M;           // max_m (masked) or M_total (contiguous)
+  int N;
+  int K;
+  int kblocks;     // K / (elements per 128 bytes)
+  int n_tiles;     // ceil(N / BN)
+  int m_blocks;    // masked: ceil(max_m/128); contiguous: ceil(M_total/128)
+  const int32_t* sched;  // masked_m[G] or m_indices[M_total]
+  const float* a_scale;
+  const float* b_scale;
+  __nv_bfloat16* d;
+  uint32_t* debug_acc;
+  int32_t* status;
+};
+
+template <int KIND, int BN, int STAGES>
+struct SmemLayout {
+  static constexpr bool kW4 = (KIND == DG_KIND_W4A8);
+  static constexpr int kBBytes = BN * kRowBytes;         // int8/fp8/bf16 weight tile
+  static constexpr int kPBytes = kW4 ? BN * 64 : 0;      // packed int4 weight tile
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * kATileBytes;
+  static constexpr int off_p = off_b + STAGES * kBBytes;
+  static constexpr int off_bar = off_p + STAGES * kPBytes;
+  // full[S], empty[S], unpacked[S], acc_full[2], acc_empty[2], drain
+  static constexpr int kNumBars = 3 * STAGES + 5;
+  static constexpr int off_misc = off_bar + kNumBars * 8;  // tmem slot, abort, n_items, pad
+  static constexpr int off_table = off_misc + 16;
+  static constexpr int kThreads = kW4 ? 320 : 192;
+  static constexpr int kTmemCols = 2 * BN;
+  __host__ __device__ static constexpr int total(int table_bytes) {
+    return off_table + table_bytes + 1024;  // + slack to align the base to 1024 bytes
+  }
+};
+
+struct TileCoord {
+  int g;           // group
+  int row0;        // first row: within the group (masked) or global (contiguous)
+  int n0;          // first output column
+  int rows_valid;  // rows of this tile that may be stored (before the m_indices check)
+};
+
+// Maps a work-item number to its tile using the block's shared-memory schedule table.
+struct ItemDecoder {
+  const KernelParams& p;
+  const int32_t* tbl;
+  int bn;
+  int cursor;
+  __device__ ItemDecoder(const KernelParams& p_, const int32_t* tbl_, int bn_)
+      : p(p_), tbl(tbl_), bn(bn_), cursor(0) {}
+  __device__ __forceinline__ TileCoord get(int item) {
+    TileCoord t;
+    if (p.mode == MODE_MASKED) {
+      const int32_t* cnt = tbl;
+      const int32_t* pref = tbl + p.G;
+      while (item >= pref[cursor + 1]) ++cursor;  // items only grow, so the cursor persists
+      const int local = item - pref[cursor];
+      const int mt = local / p.n_tiles;
+      t.g = cursor;
+      t.row0 = mt * kBM;
+      t.n0 = (local - mt * p.n_tiles) * bn;
+      t.rows_valid = min(kBM, cnt[cursor] - t.row0);
+    } else {
+      const int bi = item / p.n_tiles;
+      const int e = tbl[bi];
+      t.g = e >> 16;
+      t.row0 = (e & 0xFFFF) * kBM;
+      t.n0 = (item - bi * p.n_tiles) * bn;
+      t.rows_valid = min(kBM, p.M - t.row0);
+    }
+    return t;
+  }
+};
+
+template <int KIND, int BN, int STAGES>
+__global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
+                    const __grid_constant__ CUtensorMap tm_b, const KernelParams p) {
+  using L = SmemLayout<KIND, BN, STAGES>;
+  constexpr bool kW4 = L::kW4;
+  constexpr int kUmmaKind =
+      (KIND == DG_KIND_E4M3) ? UMMA_F8F6F4 : (KIND == DG_KIND_BF16 ? UMMA_F16 : UMMA_I8);
+  constexpr bool kIntAcc = (KIND == DG_KIND_I8 || KIND == DG_KIND_W4A8);
+  constexpr int kElemsPerRow = (KIND == DG_KIND_BF16) ? 64 : 128;  // A elements per 128 bytes
+  constexpr uint32_t kIdesc =
+      umma_idesc(kIntAcc ? 2u : 1u, (KIND == DG_KIND_E4M3) ? 0u : 1u, kBM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  auto bar_full = [&](int s) { return base + L::off_bar + 8u * s; };
+  auto bar_empty = [&](int s) { return base + L::off_bar + 8u * (STAGES + s); };
+  auto bar_unp = [&](int s) { return base + L::off_bar + 8u * (2 * STAGES + s); };
+  auto bar_acc_full = [&](int b) { return base + L::off_bar + 8u * (3 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return base + L::off_bar + 8u * (3 * STAGES + 2 + b); };
+  const uint32_t bar_drain = base + L::off_bar + 8u * (3 * STAGES + 4);
+
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
+  volatile int* n_items_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 8);
+  int32_t* tbl = reinterpret_cast<int32_t*>(smem + L::off_table);
+
+  // ------------------------------------------------------------------ one-time set-up
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), 1);
+      mbar_init(bar_unp(s), 4);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 4);
+    }
+    mbar_init(bar_drain, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+
+  // Schedule table.  Masked: cnt[G] (clamped masked_m) and pref[G+1] (running number of
+  // work items).  Contiguous: the list of 128-row blocks whose first row belongs to a
+  // group, as (group << 16 | block).
+  if (p.mode == MODE_MASKED) {
+    int32_t* cnt = tbl;
+    int32_t* pref = tbl + p.G;
+    for (int g = tid; g < p.G; g += blockDim.x) cnt[g] = max(0, min(p.sched[g], p.M));
+    __syncthreads();
+    if (warp == 0) {
+      int running = 0;
+      for (int g0 = 0; g0 < p.G; g0 += 32) {
+        const int g = g0 + lane;
+        int x = (g < p.G) ? ((cnt[g] + kBM - 1) / kBM) * p.n_tiles : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, x, o);
+          if (lane >= o) x += y;
+        }
+        if (g < p.G) pref[g + 1] = running + x;
+        running += __shfl_sync(0xffffffffu, x, 31);
+      }
+      if (lane == 0) {
+        pref[0] = 0;
+        *n_items_s = running;
+      }
+    }
+  } else {
+    for (int b = tid; b < p.m_blocks; b += blockDim.x) tbl[b] = p.sched[(size_t)b * kBM];
+    __syncthreads();
+    if (warp == 0) {
+      int count = 0;
+      bool bad = false;
+      for (int b0 = 0; b0 < p.m_blocks; b0 += 32) {
+        const int b = b0 + lane;
+        const int e = (b < p.m_blocks) ? tbl[b] : -1;
+        const bool ok = (e >= 0) && (e < p.G);
+        bad |= (e >= p.G);
+        const unsigned mask = __ballot_sync(0xffffffffu, ok);
+        __syncwarp();
+        if (ok) tbl[count + __popc(mask & ((1u << lane) - 1u))] = (e << 16) | b;
+        count += __popc(mask);
+        __syncwarp();
+      }
+      if (lane == 0) *n_items_s = count * p.n_tiles;
+      if (__any_sync(0xffffffffu, bad) && lane == 0 && blockIdx.x == 0 && p.status != nullptr)
+        atomicCAS(p.status, DG_DEV_OK, DG_DEV_BAD_GROUP_INDEX);
+    }
+  }
+
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_items = *n_items_s;
+
+  // ------------------------------------------------------------------ roles
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer
+      const uint64_t pol_a = l2_policy_evict_last();   // A tiles are re-read by other n-tiles
+      const uint64_t pol_b = l2_policy_evict_first();  // weights stream through once
+      ItemDecoder dec(p, tbl, BN);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        const TileCoord t = dec.get(item);
+        const int b_row0 = t.g * p.kblocks * p.N + t.n0;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(bar_full(s), kATileBytes + (kW4 ? L::kPBytes : L::kBBytes));
+          const uint32_t a_dst = base + L::off_a + s * kATileBytes;
+          if (p.mode == MODE_MASKED)
+            tma_load_3d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, t.g, pol_a);
+          else
+            tma_load_2d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, pol_a);
+          const uint32_t b_dst =
+              kW4 ? base + L::off_p + s * L::kPBytes : base + L::off_b + s * L::kBBytes;
+          tma_load_2d(b_dst, &tm_b, bar_full(s), 0, b_row0 + kb * p.N, pol_b);
+        }
+      }
+      // Do not leave while a copy into this block's shared memory is still in flight:
+      // wait (bounded) for the last fill of every stage.
+      int local_abort = 0;
+      for (int s = 0; s < STAGES; ++s) {
+        const uint32_t fills = (it + STAGES - 1 - s) / STAGES;
+        if (fills > 0 && !mbar_wait_bounded(bar_full(s), (fills - 1) & 1u, &local_abort,
+                                            SITE_PRODUCER_DRAIN))
+          *abort_flag = SITE_PRODUCER_DRAIN;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- UMMA issuer
+      uint32_t it = 0, tile = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++tile) {
+        const uint32_t buf = tile & 1u;
+        const uint32_t aph = (tile >> 1) & 1u;
+        if (!mbar_wait_bounded(bar_acc_empty(buf), aph ^ 1u, abort_flag, SITE_MMA_ACC_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          if (kW4 && !mbar_wait_bounded(bar_unp(s), ph, abort_flag, SITE_MMA_UNPACKED)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t a_desc = umma_desc_sw128(base + L::off_a + s * kATileBytes);
+          const uint64_t b_desc = umma_desc_sw128(base + L::off_b + s * L::kBBytes);
+#pragma unroll
+          for (int k = 0; k < kRowBytes / 32; ++k) {
+            // +2 in the start-address field = +32 bytes along K inside the swizzled row
+            umma_ss<kUmmaKind>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc,
+                               (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty(s));  // frees the stage once these UMMAs have read it
+        }
+        if (ok) umma_commit(bar_acc_full(buf));
+      }
+      if (*abort_flag) {
+        // Abnormal exit: make sure no UMMA is still running before TMEM is released.
+        int local_abort = 0;
+        umma_commit(bar_drain);
+        mbar_wait_bounded(bar_drain, 0, &local_abort, 0);
+      }
+    }
+  } else if (warp < 6) {
+    // ---- epilogue: this warp may touch TMEM lanes [32q, 32q+32)
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    ItemDecoder dec(p, tbl, BN);
+    uint32_t tile = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
+      const TileCoord t = dec.get(item);
+      const uint32_t buf = tile & 1u;
+      const uint32_t aph = (tile >> 1) & 1u;
+      if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
+      tc_fence_after_sync();
+      if (t.rows_valid > q * 32) {  // warp-uniform
+        bool rv = row_in_tile < t.rows_valid;
+        const size_t grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 +
+                            row_in_tile;
+        if (p.mode == MODE_CONTIG && rv) rv = p.sched[grow] >= 0;
+        const float as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
+        const float bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
+        const float* bs_row = p.b_scale + (size_t)t.g * p.N + t.n0;  // PER_CHANNEL only
+        __nv_bfloat16* d_row = p.d + grow * p.N + t.n0;
+        uint32_t* dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int cols_left = p.N - (t.n0 + c * 32);
+          if (cols_left <= 0) break;  // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (rv) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (j + 8 <= cols_left) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  v[i] = kIntAcc ? __int2float_rn(static_cast<int>(r[j + i]))
+                                 : __uint_as_float(r[j + i]);
+                if (p.scale_mode == DG_SCALE_PER_CHANNEL) {
+                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(bs_row + c * 32 + j));
+                  const float4 b1 =
+                      __ldg(reinterpret_cast<const float4*>(bs_row + c * 32 + j + 4));
+                  v[0] = (v[0] * as) * b0.x;
+                  v[1] = (v[1] * as) * b0.y;
+                  v[2] = (v[2] * as) * b0.z;
+                  v[3] = (v[3] * as) * b0.w;
+                  v[4] = (v[4] * as) * b1.x;
+                  v[5] = (v[5] * as) * b1.y;
+                  v[6] = (v[6] * as) * b1.z;
+                  v[7] = (v[7] * as) * b1.w;
+                } else if (p.scale_mode == DG_SCALE_TENSOR_WISE) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) v[i] = (v[i] * as) * bs_g;
+                }
+                uint4 o;
+                __nv_bfloat162 h;
+                h = __floats2bfloat162_rn(v[0], v[1]);
+                o.x = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(v[2], v[3]);
+                o.y = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(v[4], v[5]);
+                o.z = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(v[6], v[7]);
+                o.w = *reinterpret_cast<uint32_t*>(&h);
+                *reinterpret_cast<uint4*>(d_row + c * 32 + j) = o;
+                if (dbg_row != nullptr) {
+                  *reinterpret_cast<uint4*>(dbg_row + c * 32 + j) =
+                      make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                  *reinterpret_cast<uint4*>(dbg_row + c * 32 + j + 4) =
+                      make_uint4(r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
+                }
+              }
+            }
+          }
+        }
+      }
+      // hand the accumulator back to the UMMA issuer
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+    }
+  } else {
+    if constexpr (kW4) {
+      // ---- W4A8 unpack: packed stage [BN][64 bytes] -> int8 stage [BN][128 bytes], swizzled.
+      // Byte i of 16-byte chunk j of a packed row carries w[32j+i] (high nibble) and
+      // w[32j+16+i] (low nibble); `& 0xF0` / `<< 4` turn each into the int8 value 16*w, the
+      // reference's rule (m_grouped_w4a8_gemm_nt_masked_hipc.cu:378-381).
+      const int ut = tid - 192;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_UNPACK_FULL)) {
+            ok = false;
+            break;
+          }
+          const uint4* src = reinterpret_cast<const uint4*>(smem + L::off_p + s * L::kPBytes);
+          uint8_t* dst = smem + L::off_b + s * L::kBBytes;
+#pragma unroll 4
+          for (int i = ut; i < BN * 4; i += 128) {
+            const uint4 v = src[i];
+            const int r = i >> 2, j = i & 3, sw = r & 7;
+            const uint4 hi = make_uint4(v.x & 0xF0F0F0F0u, v.y & 0xF0F0F0F0u, v.z & 0xF0F0F0F0u,
+                                        v.w & 0xF0F0F0F0u);
+            const uint4 lo = make_uint4((v.x << 4) & 0xF0F0F0F0u, (v.y << 4) & 0xF0F0F0F0u,
+                                        (v.z << 4) & 0xF0F0F0F0u, (v.w << 4) & 0xF0F0F0F0u);
+            *reinterpret_cast<uint4*>(dst + r * kRowBytes + (((2 * j) ^ sw) << 4)) = hi;
+            *reinterpret_cast<uint4*>(dst + r * kRowBytes + (((2 * j + 1) ^ sw) << 4)) = lo;
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the UMMA (async proxy)
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_unp(s));
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, L::kTmemCols);
+  }
+  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, DG_DEV_OK, DG_DEV_WAIT_EXPIRED) == DG_DEV_OK) {
+      p.status[1] = blockIdx.x;
+      p.status[2] = *abort_flag;
+      p.status[3] = n_items;
+    }
+  }
+}
+
+}  // namespace dg

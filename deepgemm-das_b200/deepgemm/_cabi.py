@@ -1,0 +1,120 @@
+"""ctypes binding of libdeepgemm_b200.so (declared in include/deepgemm_b200.h).
+
+The library is the only compute path: there is no CPU or PyTorch fallback.  Importing this
+module raises ImportError when the shared object has not been built.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_LIB_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
+LIB_PATH = os.environ.get("DEEP_GEMM_LIB_PATH") or os.path.join(_LIB_DIR, "libdeepgemm_b200.so")
+
+# enum dg_kind / dg_scale_mode
+KIND_I8, KIND_E4M3, KIND_W4A8, KIND_BF16 = 0, 1, 2, 3
+SCALE_PER_CHANNEL, SCALE_TENSOR_WISE, SCALE_NONE = 0, 1, 2
+NIBBLE_HIGH_FIRST, NIBBLE_LOW_FIRST = 0, 1
+STATUS_WORDS = 4
+QUERY_ABI_VERSION, QUERY_SM_COUNT, QUERY_MAX_SMEM, QUERY_CC, QUERY_LAUNCH_COUNT = 0, 1, 2, 3, 4
+ERR_CUDA = -7
+
+EXPORTED_SYMBOLS = (
+    "dg_masked_gemm",
+    "dg_contig_gemm",
+    "dg_pack_weight",
+    "dg_unpack_weight",
+    "dg_query",
+    "dg_strerror",
+    "dg_last_cuda_error",
+)
+
+
+class MaskedArgs(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("scale_mode", C.c_int32),
+        ("a", C.c_void_p),
+        ("b_packed", C.c_void_p),
+        ("d", C.c_void_p),
+        ("a_scale", C.c_void_p),
+        ("b_scale", C.c_void_p),
+        ("masked_m", C.c_void_p),
+        ("num_groups", C.c_int32),
+        ("max_m", C.c_int32),
+        ("n", C.c_int32),
+        ("k", C.c_int32),
+        ("expected_m", C.c_int32),
+        ("block_n", C.c_int32),
+        ("debug_acc", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
+class ContigArgs(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("scale_mode", C.c_int32),
+        ("a", C.c_void_p),
+        ("b_packed", C.c_void_p),
+        ("d", C.c_void_p),
+        ("a_scale", C.c_void_p),
+        ("b_scale", C.c_void_p),
+        ("m_indices", C.c_void_p),
+        ("num_groups", C.c_int32),
+        ("m_total", C.c_int32),
+        ("n", C.c_int32),
+        ("k", C.c_int32),
+        ("block_n", C.c_int32),
+        ("reserved", C.c_int32),
+        ("debug_acc", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"libdeepgemm_b200.so not found at {LIB_PATH}. Build it with "
+            "`python deepgemm-das_b200/build.py` (needs nvcc with sm_100a support). "
+            "There is no fallback implementation."
+        )
+    lib = C.CDLL(LIB_PATH)
+    lib.dg_masked_gemm.argtypes = [C.POINTER(MaskedArgs), C.c_void_p]
+    lib.dg_masked_gemm.restype = C.c_int
+    lib.dg_contig_gemm.argtypes = [C.POINTER(ContigArgs), C.c_void_p]
+    lib.dg_contig_gemm.restype = C.c_int
+    for fn in (lib.dg_pack_weight, lib.dg_unpack_weight):
+        fn.argtypes = [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                       C.c_int32, C.c_void_p]
+        fn.restype = C.c_int
+    lib.dg_query.argtypes = [C.c_int32]
+    lib.dg_query.restype = C.c_int64
+    lib.dg_strerror.argtypes = [C.c_int]
+    lib.dg_strerror.restype = C.c_char_p
+    lib.dg_last_cuda_error.argtypes = []
+    lib.dg_last_cuda_error.restype = C.c_int
+    return lib
+
+
+lib = _load()
+
+
+class DeepGemmError(RuntimeError):
+    """A non-zero dg_status from the library (RuntimeError, like the reference's TORCH_CHECK)."""
+
+    def __init__(self, code: int, where: str):
+        self.code = code
+        msg = lib.dg_strerror(code).decode()
+        if code == ERR_CUDA:
+            msg += f" [cuda error {lib.dg_last_cuda_error()}]"
+        super().__init__(f"{where}: {msg} (dg_status {code})")
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise DeepGemmError(code, where)
+
+
+def query(what: int) -> int:
+    return int(lib.dg_query(what))

@@ -1,0 +1,185 @@
+"""Tensor-level marshalling from torch tensors to the C ABI.
+
+Every public grouped-GEMM entry point of the package ends here (through the
+``torch.ops.deep_gemm.*`` custom ops of ``deepgemm.op``).  Checks mirror the reference's
+host-side TORCH_CHECKs (csrc/arch/gfx936_gfx938_shared/m_grouped_fp8_gemm_nt_maksed_low_latency.cu:1053-1126,
+csrc/include/m_grouped_i8_gemm_nt_contiguous/bm128_bn256_bk64_nloop4.inc.cuh:729-791) and
+raise RuntimeError like they do; nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi
+from ._cabi import (KIND_BF16, KIND_E4M3, KIND_I8, KIND_W4A8, SCALE_NONE, SCALE_PER_CHANNEL,
+                    SCALE_TENSOR_WISE)
+
+_FP8 = torch.float8_e4m3fn
+
+# bytes of K per packed row, and elements per row, by kind
+_ROW_ELEMS = {KIND_I8: 128, KIND_E4M3: 128, KIND_BF16: 64, KIND_W4A8: 64}
+_K_PER_BLOCK = {KIND_I8: 128, KIND_E4M3: 128, KIND_BF16: 64, KIND_W4A8: 128}
+_A_DTYPES = {KIND_I8: (torch.int8,), KIND_E4M3: (_FP8,), KIND_W4A8: (torch.int8,),
+             KIND_BF16: (torch.bfloat16,)}
+_B_DTYPES = {KIND_I8: (torch.int8, torch.uint8), KIND_E4M3: (_FP8, torch.int8, torch.uint8),
+             KIND_W4A8: (torch.int8, torch.uint8), KIND_BF16: (torch.bfloat16,)}
+KIND_NAMES = {KIND_I8: "int8", KIND_E4M3: "fp8_e4m3", KIND_W4A8: "w4a8", KIND_BF16: "bf16"}
+
+
+def _chk(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def packed_weight_dims(b: torch.Tensor, kind: int, k_hint: Optional[int] = None
+                       ) -> Tuple[int, int, int]:
+    """(G, N, K) of a packed weight tensor; rejects tensors that do not carry the packed shape.
+
+    Packed weights are 4-D ``[G, K/BK, N, row]`` with row = 128 (8-bit), 64 (bf16 elements, or
+    int4 bytes).  W4A8 weights may also be the 3-D ``[G, N, K/2]`` tensor that the reference's
+    in-place packer returns (deepgemm/group_gemm_weight_pack.py:691-714) -- that shape cannot
+    be told apart from an unpacked one, exactly as in the reference.
+    """
+    if kind == KIND_W4A8 and b.dim() == 3:
+        g, n, kh = b.shape
+        return int(g), int(n), int(kh) * 2
+    if b.dim() != 4 or int(b.shape[3]) != _ROW_ELEMS[kind]:
+        raise ValueError(
+            f"{KIND_NAMES[kind]} grouped GEMM expects a packed weight [G, K/{_K_PER_BLOCK[kind]}, N, "
+            f"{_ROW_ELEMS[kind]}] from the deepgemm.group_gemm_weight_pack packers, got shape "
+            f"{tuple(b.shape)}"
+        )
+    g, kb, n, _ = b.shape
+    return int(g), int(n), int(kb) * _K_PER_BLOCK[kind]
+
+
+def _common_checks(kind, a, b, d, sched, what):
+    _chk(a.is_cuda and b.is_cuda and d.is_cuda and sched.is_cuda,
+         f"{what}: all tensors must be CUDA tensors (there is no CPU implementation)")
+    _chk(a.device == b.device == d.device == sched.device, f"{what}: tensors on different devices")
+    _chk(a.dtype in _A_DTYPES[kind], f"{what}: activation dtype {a.dtype} does not fit {KIND_NAMES[kind]}")
+    _chk(b.dtype in _B_DTYPES[kind], f"{what}: weight dtype {b.dtype} does not fit {KIND_NAMES[kind]}")
+    _chk(d.dtype == torch.bfloat16, f"{what}: output must be torch.bfloat16, got {d.dtype}")
+    _chk(a.is_contiguous(), f"{what}: activation must be contiguous")
+    _chk(b.is_contiguous(), f"{what}: packed weight must be contiguous")
+    _chk(d.is_contiguous(), f"{what}: output must be contiguous")
+    _chk(sched.dtype == torch.int32 and sched.is_contiguous(),
+         f"{what}: masked_m / m_indices must be contiguous torch.int32")
+
+
+def _scale(t: torch.Tensor, shape: Tuple[int, ...], name: str, what: str) -> torch.Tensor:
+    _chk(t.is_cuda, f"{what}: {name} must be a CUDA tensor")
+    _chk(t.dtype == torch.float32, f"{what}: {name} must be torch.float32, got {t.dtype}")
+    if t.dim() == len(shape) + 1 and t.shape[-1] == 1:
+        t = t.squeeze(-1)
+    _chk(tuple(t.shape) == tuple(shape), f"{what}: {name} must have shape {tuple(shape)} "
+         f"(optionally with a trailing 1), got {tuple(t.shape)}")
+    t = t.contiguous()
+    if t.data_ptr() % 16 != 0:  # a sliced view can be misaligned for the float4 loads
+        t = t.clone()
+    return t
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _debug_and_status(debug_acc, status, rows, n, dev, what):
+    if debug_acc is not None:
+        _chk(debug_acc.is_cuda and debug_acc.device == dev and debug_acc.is_contiguous()
+             and debug_acc.element_size() == 4 and debug_acc.numel() == rows * n,
+             f"{what}: debug_acc must be a contiguous 32-bit tensor of {rows}x{n} on the same device")
+    if status is not None:
+        _chk(status.is_cuda and status.device == dev and status.dtype == torch.int32
+             and status.is_contiguous() and status.numel() >= _cabi.STATUS_WORDS,
+             f"{what}: status must be int32[{_cabi.STATUS_WORDS}] on the same device")
+
+
+def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Tensor,
+                        d: torch.Tensor, a_scale: Optional[torch.Tensor],
+                        b_scale: Optional[torch.Tensor], masked_m: torch.Tensor,
+                        expected_m: int, *, block_n: int = 0,
+                        debug_acc: Optional[torch.Tensor] = None,
+                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """d[g, :masked_m[g]] = bf16((A[g] @ B[g]^T) * a_scale[g] * b_scale[g]) via dg_masked_gemm."""
+    what = f"masked {KIND_NAMES[kind]} grouped GEMM"
+    _chk(a.dim() == 3, f"{what}: activation must be [G, max_m, K], got {tuple(a.shape)}")
+    _chk(d.dim() == 3, f"{what}: output must be [G, max_m, N], got {tuple(d.shape)}")
+    g, max_m, k = (int(x) for x in a.shape)
+    bg, n, bk = packed_weight_dims(b, kind)
+    _common_checks(kind, a, b, d, masked_m, what)
+    _chk(bg == g, f"{what}: weight has {bg} groups, activation has {g}")
+    _chk(bk == k, f"{what}: weight K={bk} does not match activation K={k}")
+    _chk(tuple(d.shape) == (g, max_m, n), f"{what}: output must be {(g, max_m, n)}, got {tuple(d.shape)}")
+    _chk(masked_m.numel() == g, f"{what}: masked_m must have {g} entries, got {masked_m.numel()}")
+    if scale_mode == SCALE_NONE:
+        a_s = b_s = None
+    else:
+        _chk(a_scale is not None and b_scale is not None, f"{what}: scales are required")
+        a_s = _scale(a_scale, (g, max_m), "a_scale", what)
+        b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
+    _debug_and_status(debug_acc, status, g * max_m, n, a.device, what)
+
+    args = _cabi.MaskedArgs(
+        kind=kind, scale_mode=scale_mode, a=a.data_ptr(), b_packed=b.data_ptr(), d=d.data_ptr(),
+        a_scale=_ptr(a_s), b_scale=_ptr(b_s), masked_m=masked_m.data_ptr(), num_groups=g,
+        max_m=max_m, n=n, k=k, expected_m=int(expected_m), block_n=int(block_n),
+        debug_acc=_ptr(debug_acc), status=_ptr(status))
+    with torch.cuda.device(a.device):
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        _cabi.check(_cabi.lib.dg_masked_gemm(C.byref(args), C.c_void_p(stream)), what)
+    return d
+
+
+def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Tensor,
+                            d: torch.Tensor, a_scale: Optional[torch.Tensor],
+                            b_scale: Optional[torch.Tensor], m_indices: torch.Tensor, *,
+                            block_n: int = 0, debug_acc: Optional[torch.Tensor] = None,
+                            status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """d[i] = bf16((A[i] @ B[m_indices[i]]^T) * a_scale[i] * b_scale[m_indices[i]]) via dg_contig_gemm."""
+    what = f"contiguous {KIND_NAMES[kind]} grouped GEMM"
+    _chk(a.dim() == 2, f"{what}: activation must be [M, K], got {tuple(a.shape)}")
+    _chk(d.dim() == 2, f"{what}: output must be [M, N], got {tuple(d.shape)}")
+    m_total, k = (int(x) for x in a.shape)
+    g, n, bk = packed_weight_dims(b, kind)
+    _common_checks(kind, a, b, d, m_indices, what)
+    _chk(bk == k, f"{what}: weight K={bk} does not match activation K={k}")
+    _chk(tuple(d.shape) == (m_total, n), f"{what}: output must be {(m_total, n)}, got {tuple(d.shape)}")
+    _chk(m_indices.numel() == m_total, f"{what}: m_indices must have {m_total} entries")
+    if scale_mode == SCALE_NONE:
+        a_s = b_s = None
+    else:
+        _chk(a_scale is not None and b_scale is not None, f"{what}: scales are required")
+        a_s = _scale(a_scale, (m_total,), "a_scale", what)
+        b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
+    _debug_and_status(debug_acc, status, m_total, n, a.device, what)
+
+    args = _cabi.ContigArgs(
+        kind=kind, scale_mode=scale_mode, a=a.data_ptr(), b_packed=b.data_ptr(), d=d.data_ptr(),
+        a_scale=_ptr(a_s), b_scale=_ptr(b_s), m_indices=m_indices.data_ptr(), num_groups=g,
+        m_total=m_total, n=n, k=k, block_n=int(block_n), reserved=0,
+        debug_acc=_ptr(debug_acc), status=_ptr(status))
+    with torch.cuda.device(a.device):
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        _cabi.check(_cabi.lib.dg_contig_gemm(C.byref(args), C.c_void_p(stream)), what)
+    return d
+
+
+def kind_of_activation(a: torch.Tensor) -> int:
+    """INT8 or FP8 from the activation dtype, as the reference's low-latency op does
+    (m_grouped_fp8_gemm_nt_maksed_low_latency.cu:1150-1161)."""
+    if a.dtype == torch.int8:
+        return KIND_I8
+    if a.dtype == _FP8:
+        return KIND_E4M3
+    raise RuntimeError(f"activation must be torch.int8 or torch.float8_e4m3fn, got {a.dtype}")
+
+
+__all__ = [
+    "grouped_gemm_masked", "grouped_gemm_contiguous", "packed_weight_dims", "kind_of_activation",
+    "KIND_I8", "KIND_E4M3", "KIND_W4A8", "KIND_BF16",
+    "SCALE_PER_CHANNEL", "SCALE_TENSOR_WISE", "SCALE_NONE",
+]

@@ -1,0 +1,211 @@
+"""Op layer: ``torch.ops.deep_gemm.*`` custom ops plus the reference's pybind names.
+
+The reference exposes its C++ launchers twice: as the pybind module ``deepgemm.op``
+(csrc/common/deepgemm_ops.cpp:127-144, argument names in csrc/include/deepgemm_ops.hpp) and
+as dispatcher ops in namespace ``deep_gemm`` (csrc/common/000_deep_gemm_torch_library_root.cu:6,
+schemas e.g. csrc/arch/gfx936_gfx938_shared/low_latency_grouped_gemm.cu:56-103).  Both are
+kept: every function of this module calls the dispatcher op of the same name, and each op
+has a CUDA implementation only, which marshals to the C ABI of libdeepgemm_b200.so.  The
+``mode`` / ``cu_s`` / ``block_m`` / ``block_n`` / ``n_loop_num`` integers selected Hygon tile
+variants; here they are accepted and ignored (the library picks its own tile).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _core
+from ._core import (KIND_BF16, KIND_E4M3, KIND_I8, KIND_W4A8, SCALE_NONE, SCALE_PER_CHANNEL,
+                    SCALE_TENSOR_WISE)
+
+_NS = "deep_gemm"
+_lib = torch.library.Library(_NS, "FRAGMENT")
+
+
+def _define(name: str, schema: str, fn) -> None:
+    _lib.define(f"{name}{schema}")
+    _lib.impl(name, fn, "CUDA")
+
+
+# --------------------------------------------------------------------------- masked
+def _ll_impl(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
+             max_tokens, experts, cu_s, block_wise, b_overlap, signal):
+    if block_wise:
+        raise RuntimeError("block-wise scales are not supported")
+    if b_overlap or signal is not None:
+        raise RuntimeError("overlap mode / signal is not supported")
+    if int(experts) != int(matrix_a.shape[0]):
+        raise RuntimeError(f"experts={experts} does not match matrix_a.shape[0]={matrix_a.shape[0]}")
+    kind = _core.kind_of_activation(matrix_a)
+    return _core.grouped_gemm_masked(kind, SCALE_PER_CHANNEL, matrix_a, matrix_b, matrix_c,
+                                     matrix_a_scale, matrix_b_scale, actual_tokens, max_tokens)
+
+
+def _ll_tw_impl(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
+                max_tokens, experts, cu_s, b_overlap, signal):
+    if b_overlap or signal is not None:
+        raise RuntimeError("overlap mode / signal is not supported")
+    if int(experts) != int(matrix_a.shape[0]):
+        raise RuntimeError(f"experts={experts} does not match matrix_a.shape[0]={matrix_a.shape[0]}")
+    kind = _core.kind_of_activation(matrix_a)
+    return _core.grouped_gemm_masked(kind, SCALE_TENSOR_WISE, matrix_a, matrix_b, matrix_c,
+                                     matrix_a_scale, matrix_b_scale, actual_tokens, max_tokens)
+
+
+_LL_SCHEMA = ("(Tensor matrix_a, Tensor matrix_b, Tensor matrix_a_scale, Tensor matrix_b_scale, "
+              "Tensor actual_tokens, Tensor(a!) matrix_c, int max_tokens, int experts, int cu_s, "
+              "bool block_wise, bool b_overlap, Tensor? signal) -> Tensor(a!)")
+_define("low_latency_grouped_gemm", _LL_SCHEMA, _ll_impl)
+_define("m_grouped_w8a8_gemm_nt_masked_gfx936", _LL_SCHEMA, _ll_impl)
+_define("low_latency_grouped_gemm_tensor_wise",
+        "(Tensor matrix_a, Tensor matrix_b, Tensor matrix_a_scale, Tensor matrix_b_scale, "
+        "Tensor actual_tokens, Tensor(a!) matrix_c, int max_tokens, int experts, int cu_s, "
+        "bool b_overlap, Tensor? signal) -> Tensor(a!)", _ll_tw_impl)
+
+_MASKED_SCHEMA = ("(Tensor input, Tensor b_qweight, Tensor(a!) output, Tensor a_scale, "
+                  "Tensor b_scale, Tensor masked_m, int expected_m_per_group, int mode) -> Tensor(a!)")
+
+
+def _masked_i8_impl(input, b_qweight, output, a_scale, b_scale, masked_m, expected_m_per_group,
+                    mode):
+    return _core.grouped_gemm_masked(KIND_I8, SCALE_PER_CHANNEL, input, b_qweight, output,
+                                     a_scale, b_scale, masked_m, expected_m_per_group)
+
+
+def _masked_w4a8_impl(input, b_qweight, output, a_scale, b_scale, masked_m,
+                      expected_m_per_group, mode):
+    return _core.grouped_gemm_masked(KIND_W4A8, SCALE_PER_CHANNEL, input, b_qweight, output,
+                                     a_scale, b_scale, masked_m, expected_m_per_group)
+
+
+def _masked_bf16_impl(input, b_qweight, output, masked_m, expected_m_per_group, mode):
+    return _core.grouped_gemm_masked(KIND_BF16, SCALE_NONE, input, b_qweight, output, None, None,
+                                     masked_m, expected_m_per_group)
+
+
+_define("m_grouped_marlin_w8a8_gemm_nt_masked", _MASKED_SCHEMA, _masked_i8_impl)
+_define("m_grouped_marlin_w4a8_gemm_nt_masked", _MASKED_SCHEMA, _masked_w4a8_impl)
+_define("m_grouped_marlin_w4a8_gemm_nt_masked_hipc", _MASKED_SCHEMA, _masked_w4a8_impl)
+_BF16_SCHEMA = ("(Tensor input, Tensor b_qweight, Tensor(a!) output, Tensor masked_m, "
+                "int expected_m_per_group, int mode) -> Tensor(a!)")
+_define("m_grouped_bf16_gemm_nt_masked", _BF16_SCHEMA, _masked_bf16_impl)
+_define("m_grouped_bf16_gemm_nt_masked_hipc", _BF16_SCHEMA, _masked_bf16_impl)
+
+
+# --------------------------------------------------------------------------- contiguous
+def _contig_block_impl(kind, scale_mode):
+    def impl(input, b_qweight, output, a_scale, b_scale, m_indices, block_m, block_n, n_loop_num):
+        return _core.grouped_gemm_contiguous(kind, scale_mode, input, b_qweight, output, a_scale,
+                                             b_scale, m_indices)
+    return impl
+
+
+def _contig_mode_impl(kind, scale_mode):
+    def impl(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
+        return _core.grouped_gemm_contiguous(kind, scale_mode, input, b_qweight, output, a_scale,
+                                             b_scale, m_indices)
+    return impl
+
+
+def _contig_fp8_marlin_impl(scale_mode):
+    def impl(input, b_qweight, output, a_scale, b_scale, m_indices, mode, n_loop_num):
+        return _core.grouped_gemm_contiguous(KIND_E4M3, scale_mode, input, b_qweight, output,
+                                             a_scale, b_scale, m_indices)
+    return impl
+
+
+_CONTIG_BLOCK_SCHEMA = ("(Tensor input, Tensor b_qweight, Tensor(a!) output, Tensor a_scale, "
+                        "Tensor b_scale, Tensor m_indices, int block_m, int block_n, "
+                        "int n_loop_num) -> Tensor(a!)")
+_CONTIG_MODE_SCHEMA = ("(Tensor input, Tensor b_qweight, Tensor(a!) output, Tensor a_scale, "
+                       "Tensor b_scale, Tensor m_indices, int mode) -> Tensor(a!)")
+_CONTIG_MARLIN_SCHEMA = ("(Tensor input, Tensor b_qweight, Tensor(a!) output, Tensor a_scale, "
+                         "Tensor b_scale, Tensor m_indices, int mode, int n_loop_num) -> Tensor(a!)")
+_define("m_grouped_i8_gemm_nt_contiguous", _CONTIG_BLOCK_SCHEMA,
+        _contig_block_impl(KIND_I8, SCALE_PER_CHANNEL))
+_define("m_grouped_w8a8_gemm_nt_contiguous_gfx936", _CONTIG_BLOCK_SCHEMA,
+        _contig_block_impl(KIND_I8, SCALE_PER_CHANNEL))
+_define("m_grouped_fp8_gemm_nt_contiguous", _CONTIG_BLOCK_SCHEMA,
+        _contig_block_impl(KIND_E4M3, SCALE_PER_CHANNEL))
+_define("m_grouped_fp8_gemm_nt_contiguous_marlin", _CONTIG_MARLIN_SCHEMA,
+        _contig_fp8_marlin_impl(SCALE_PER_CHANNEL))
+_define("m_grouped_fp8_gemm_nt_contiguous_marlin_tensor_wise", _CONTIG_MARLIN_SCHEMA,
+        _contig_fp8_marlin_impl(SCALE_TENSOR_WISE))
+_define("m_grouped_w8a8_gemm_nt_contiguous", _CONTIG_MODE_SCHEMA,
+        _contig_mode_impl(KIND_I8, SCALE_PER_CHANNEL))
+_define("m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc", _CONTIG_MODE_SCHEMA,
+        _contig_mode_impl(KIND_W4A8, SCALE_PER_CHANNEL))
+
+_ops = getattr(torch.ops, _NS)
+
+
+# --------------------------------------------------------------------------- pybind names
+def low_latency_grouped_gemm(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens,
+                             matrix_c, max_tokens, experts, cu_s, block_wise, b_overlap,
+                             signal: Optional[torch.Tensor] = None):
+    return _ops.low_latency_grouped_gemm(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale,
+                                         actual_tokens, matrix_c, int(max_tokens), int(experts),
+                                         int(cu_s), bool(block_wise), bool(b_overlap), signal)
+
+
+def m_grouped_w8a8_gemm_nt_masked_gfx936(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale,
+                                         actual_tokens, matrix_c, max_tokens, experts, cu_s,
+                                         block_wise, b_overlap,
+                                         signal: Optional[torch.Tensor] = None):
+    return _ops.m_grouped_w8a8_gemm_nt_masked_gfx936(
+        matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
+        int(max_tokens), int(experts), int(cu_s), bool(block_wise), bool(b_overlap), signal)
+
+
+def low_latency_grouped_gemm_tensor_wise(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale,
+                                         actual_tokens, matrix_c, max_tokens, experts, cu_s,
+                                         b_overlap, signal: Optional[torch.Tensor] = None):
+    return _ops.low_latency_grouped_gemm_tensor_wise(
+        matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
+        int(max_tokens), int(experts), int(cu_s), bool(b_overlap), signal)
+
+
+def m_grouped_marlin_w8a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale, masked_m,
+                                         expected_m_per_group, mode):
+    return _ops.m_grouped_marlin_w8a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale,
+                                                     masked_m, int(expected_m_per_group), int(mode))
+
+
+def m_grouped_marlin_w4a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale, masked_m,
+                                         expected_m_per_group, mode):
+    return _ops.m_grouped_marlin_w4a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale,
+                                                     masked_m, int(expected_m_per_group), int(mode))
+
+
+def m_grouped_marlin_w4a8_gemm_nt_masked_hipc(input, b_qweight, output, a_scale, b_scale,
+                                              masked_m, expected_m_per_group, mode):
+    return _ops.m_grouped_marlin_w4a8_gemm_nt_masked_hipc(
+        input, b_qweight, output, a_scale, b_scale, masked_m, int(expected_m_per_group), int(mode))
+
+
+def m_grouped_bf16_gemm_nt_masked(input, b_qweight, output, masked_m, expected_m_per_group, mode):
+    return _ops.m_grouped_bf16_gemm_nt_masked(input, b_qweight, output, masked_m,
+                                              int(expected_m_per_group), int(mode))
+
+
+def m_grouped_bf16_gemm_nt_masked_hipc(input, b_qweight, output, masked_m, expected_m_per_group,
+                                       mode):
+    return _ops.m_grouped_bf16_gemm_nt_masked_hipc(input, b_qweight, output, masked_m,
+                                                   int(expected_m_per_group), int(mode))
+
+
+def m_grouped_w8a8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
+    return _ops.m_grouped_w8a8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
+                                                  m_indices, int(mode))
+
+
+def m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc(input, b_qweight, output, a_scale, b_scale,
+                                                  m_indices, mode):
+    return _ops.m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc(input, b_qweight, output, a_scale,
+                                                              b_scale, m_indices, int(mode))
+
+
+def m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
+    return _ops.m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
+                                                 m_indices, int(mode), 256, 4)

@@ -1,0 +1,208 @@
+/*
+ * deepgemm_b200.h -- C ABI of libdeepgemm_b200.so
+ *
+ * Grouped MoE GEMM for NVIDIA B200 (sm_100a): D = bf16( a_scale * (A . B^T) * b_scale )
+ * over groups ("experts"), in the two row layouts the HYGON-AI/deepgemm-das library
+ * exposes (masked and contiguous), for INT8, FP8-e4m3, W4A8 and BF16 operands.
+ *
+ * The reference library has no C ABI of its own: its shared object is a PyTorch
+ * extension whose C++ entry points take at::Tensor.  Each function below names the
+ * reference C++ entry point(s) it stands in for (path inside the reference tree:line).
+ *
+ * Conventions
+ *   - Every pointer is a device pointer unless stated otherwise; all buffers are
+ *     caller-owned; nothing is allocated, freed or synchronised inside any call,
+ *     except where a function's comment says so.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *     Work is enqueued on it and the call returns immediately.
+ *   - Return value: DG_OK (0) or a negative dg_status code; dg_strerror() maps it to
+ *     text.  No call prints, exits the process or launches partially.
+ *   - The device that owns the buffers must be current (cudaSetDevice) in the calling
+ *     thread.  Calls are thread-safe.
+ */
+#ifndef DEEPGEMM_B200_H_
+#define DEEPGEMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DG_ABI_VERSION 1
+
+/* Exported-symbol marker: the library is built with hidden default visibility. */
+#if defined(__GNUC__)
+#define DG_API __attribute__((visibility("default")))
+#else
+#define DG_API
+#endif
+
+/* Operand kinds.  The arithmetic type the tensor cores run in is given in brackets. */
+typedef enum dg_kind {
+  DG_KIND_I8   = 0, /* A int8,  B int8           [s8 x s8 -> s32]                    */
+  DG_KIND_E4M3 = 1, /* A e4m3,  B e4m3           [e4m3 x e4m3 -> f32]                */
+  DG_KIND_W4A8 = 2, /* A int8,  B packed int4    [s8 x s8 -> s32, B = nibble << 4]   */
+  DG_KIND_BF16 = 3  /* A bf16,  B bf16           [bf16 x bf16 -> f32], no scales     */
+} dg_kind;
+
+typedef enum dg_scale_mode {
+  DG_SCALE_PER_CHANNEL = 0, /* a_scale per row, b_scale[g][n] per output channel   */
+  DG_SCALE_TENSOR_WISE = 1, /* a_scale per row, b_scale[g] one value per group     */
+  DG_SCALE_NONE        = 2  /* no scales (BF16)                                    */
+} dg_scale_mode;
+
+typedef enum dg_status {
+  DG_OK                 = 0,
+  DG_ERR_NULL_POINTER   = -1,
+  DG_ERR_BAD_KIND       = -2,
+  DG_ERR_BAD_SHAPE      = -3, /* N, K, group count or row count outside what the kernels take */
+  DG_ERR_BAD_ALIGNMENT  = -4, /* a base pointer is not 16-byte aligned                       */
+  DG_ERR_BAD_SCALE_MODE = -5,
+  DG_ERR_NO_DEVICE      = -6, /* no CUDA device, or the device is not compute capability 10.x */
+  DG_ERR_CUDA           = -7, /* a CUDA runtime/driver call failed; dg_last_cuda_error() has it */
+  DG_ERR_TOO_LARGE      = -8, /* a size exceeds a stated maximum                              */
+  DG_ERR_BAD_ARGUMENT   = -9
+} dg_status;
+
+/* Words of the optional device-side status buffer (`status`, int32[DG_STATUS_WORDS]).
+ * The kernels never trap: a wait that runs out records {code, block, role, detail} here,
+ * the block leaves cleanly, and the host reads the words after synchronising the stream.
+ * status[0] == 0 means no device-side problem was seen. */
+#define DG_STATUS_WORDS 4
+#define DG_DEV_OK              0
+#define DG_DEV_WAIT_EXPIRED    1  /* a bounded mbarrier wait gave up */
+#define DG_DEV_BAD_GROUP_INDEX 2  /* an m_indices entry was >= num_groups (row block skipped) */
+
+/*
+ * Packed weight layout ("k-block-major tiles"), produced by dg_pack_weight():
+ *
+ *   packed[g][kb][n][0..127]  =  the 128 bytes of row n of group g that cover
+ *                                K-range [kb*BK, (kb+1)*BK)
+ *
+ * BK = 128 elements for 8-bit kinds, 64 for bf16, 128 int4 values (64 bytes per row)
+ * for W4A8.  Each (kb, n-range) tile a thread block needs is one contiguous span, so a
+ * single TMA box fetches it.  Same byte count as the row-major [G][N][K] source.
+ * For W4A8 each 16-byte chunk j (of 4) of a 64-byte row holds, in byte i, value
+ * w[32j+i] in the high nibble and w[32j+16+i] in the low nibble (two's-complement
+ * nibbles), so that `x & 0xF0` and `(x << 4) & 0xF0` each yield 16 consecutive int8
+ * values equal to 16*w.  Replaces the reference's W6 / marlin / HIPC-N32 layouts
+ * (deepgemm/m_group_gemm.py:826-863, deepgemm/group_gemm_weight_pack.py:167-331,594-714).
+ */
+
+/* Arguments of the masked-layout grouped GEMM.
+ *   for g in [0,num_groups), m in [0, masked_m[g]), n in [0,N):
+ *     acc      = sum_k A[g][m][k] * B[g][n][k]            (s32 or f32)
+ *     D[g][m][n] = bf16_rne( (float(acc) * a_scale[g][m]) * b_scale[g][n] )
+ *   Rows m >= masked_m[g] of D are never written.  masked_m[g] is clamped to [0,max_m]. */
+typedef struct dg_masked_args {
+  int32_t kind;               /* dg_kind */
+  int32_t scale_mode;         /* dg_scale_mode */
+  const void*    a;           /* [G][max_m][K] row-major; int8 / e4m3 / bf16 */
+  const void*    b_packed;    /* packed layout above */
+  void*          d;           /* [G][max_m][N] bf16 */
+  const float*   a_scale;     /* [G][max_m]          (NULL iff DG_SCALE_NONE) */
+  const float*   b_scale;     /* [G][N] or [G]       (NULL iff DG_SCALE_NONE) */
+  const int32_t* masked_m;    /* [G] valid rows per group */
+  int32_t num_groups;         /* G, 1..DG_MAX_GROUPS */
+  int32_t max_m;              /* rows allocated per group */
+  int32_t n;                  /* N, multiple of 16 */
+  int32_t k;                  /* K, multiple of 128 (64 for bf16) */
+  int32_t expected_m;         /* hint only: typical masked_m; never limits the rows computed */
+  int32_t block_n;            /* 0 = choose; else 128 or 256 (tile width override, for tuning) */
+  void*          debug_acc;   /* NULL, or [G][max_m][N] of raw 32-bit accumulators (s32 / f32) */
+  int32_t*       status;      /* NULL, or int32[DG_STATUS_WORDS] device status words */
+} dg_masked_args;
+
+/* Arguments of the contiguous-layout grouped GEMM.
+ *   for every row i with e = m_indices[i] >= 0:
+ *     D[i][n] = bf16_rne( (float(sum_k A[i][k]*B[e][n][k]) * a_scale[i]) * b_scale[e][n] )
+ *   Rows are processed in blocks of 128; a block's group is m_indices of its FIRST row
+ *   and the block is skipped when that is negative, so each group's rows must start on
+ *   a multiple of 128 (callers pad to 256).  Rows with m_indices[i] < 0 are never written. */
+typedef struct dg_contig_args {
+  int32_t kind;
+  int32_t scale_mode;
+  const void*    a;           /* [M_total][K] */
+  const void*    b_packed;
+  void*          d;           /* [M_total][N] bf16 */
+  const float*   a_scale;     /* [M_total] */
+  const float*   b_scale;     /* [G][N] or [G] */
+  const int32_t* m_indices;   /* [M_total] group id per row, -1 = padding row */
+  int32_t num_groups;
+  int32_t m_total;            /* <= DG_MAX_CONTIG_ROWS */
+  int32_t n;
+  int32_t k;
+  int32_t block_n;            /* 0 = choose; else 128 or 256 */
+  int32_t reserved;
+  void*          debug_acc;   /* NULL, or [M_total][N] raw accumulators */
+  int32_t*       status;
+} dg_contig_args;
+
+#define DG_MAX_GROUPS      1024
+#define DG_MAX_CONTIG_ROWS (4096 * 128)
+
+/* Masked grouped GEMM.  Stands in for, in the reference:
+ *   m_grouped_marlin_w8a8_gemm_nt_masked   csrc/arch/gfx936_gfx938_shared/m_grouped_w8a8_gemm_nt_masked.cu:1699-1765
+ *   group_gemm_fp8_masked / masked_fp8_gemm_impl<false|true>
+ *                                          csrc/arch/gfx936_gfx938_shared/low_latency_grouped_gemm.cu:5-26,
+ *                                          csrc/arch/gfx936_gfx938_shared/m_grouped_fp8_gemm_nt_maksed_low_latency.cu:1037-1199
+ *   m_grouped_marlin_w4a8_gemm_nt_masked[_hipc]
+ *                                          csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_masked.cu:214-241,
+ *                                          csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_masked_hipc.cu:1158-1213
+ *   m_grouped_bf16_gemm_nt_masked          csrc/arch/gfx936_gfx938_shared/m_grouped_bf16_gemm_nt_masked.cu:222-262 */
+DG_API int dg_masked_gemm(const dg_masked_args* args, void* stream);
+
+/* Contiguous grouped GEMM.  Stands in for, in the reference:
+ *   m_grouped_i8_contiguous::m_grouped_i8_gemm_nt_contiguous
+ *                                          csrc/include/m_grouped_i8_gemm_nt_contiguous/dispatch.inc.cuh:9-27
+ *   m_grouped_fp8_gemm_nt_contiguous       csrc/arch/gfx938/m_grouped_fp8_gemm_nt_contiguous/dispatch.inc.cuh:8-32
+ *   m_grouped_fp8_gemm_nt_contiguous_marlin_tensor_wise
+ *                                          csrc/arch/gfx938/m_grouped_fp8_gemm_nt_contiguous.cu:199-266
+ *   m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc
+ *                                          csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_contiguous_hipc.cu:861-915 */
+DG_API int dg_contig_gemm(const dg_contig_args* args, void* stream);
+
+/* Nibble order of a row-major int4 source [G][N][K/2]:
+ *   DG_NIBBLE_HIGH_FIRST: byte j holds w[2j] in its high nibble (the reference's
+ *     framework layout, deepgemm/group_gemm_weight_pack.py:594-602)
+ *   DG_NIBBLE_LOW_FIRST:  byte j holds w[2j] in its low nibble. */
+#define DG_NIBBLE_HIGH_FIRST 0
+#define DG_NIBBLE_LOW_FIRST  1
+
+/* Re-lays a row-major weight [G][N][K] (W4A8: [G][N][K/2] bytes) into the packed layout.
+ * src and dst must not overlap (the Python packers pass a per-group temporary to get the
+ * reference's in-place behaviour).  Stands in for the torch re-layout code of
+ * pack_int8_weight_enk_to_w6_low_latency_inplace (deepgemm/m_group_gemm.py:826-863) and
+ * pack_w4a8_moe_hipc_weight_inplace (deepgemm/group_gemm_weight_pack.py:691-714). */
+DG_API int dg_pack_weight(int32_t kind, const void* src, void* dst, int32_t num_groups, int32_t n,
+                   int32_t k, int32_t nibble_order, void* stream);
+
+/* Inverse of dg_pack_weight (packed -> row-major, W4A8 in the given nibble order).
+ * No counterpart in the reference, which never unpacks; used to verify packers. */
+DG_API int dg_unpack_weight(int32_t kind, const void* src, void* dst, int32_t num_groups, int32_t n,
+                     int32_t k, int32_t nibble_order, void* stream);
+
+/* dg_query() selectors. */
+#define DG_QUERY_ABI_VERSION   0
+#define DG_QUERY_SM_COUNT      1 /* multiprocessors of the current device (cached per device) */
+#define DG_QUERY_MAX_SMEM      2 /* opt-in shared memory per block, bytes */
+#define DG_QUERY_CC            3 /* compute capability major*10+minor of the current device */
+#define DG_QUERY_LAUNCH_COUNT  4 /* kernels this library has launched in this process */
+
+/* Returns the queried value (>= 0) or a negative dg_status.  Replaces the reference's
+ * per-call hipGetDeviceProperties (m_grouped_w8a8_gemm_nt_masked.cu:85-89) and rocminfo
+ * parsing (deepgemm/utils.py:15-50). */
+DG_API int64_t dg_query(int32_t what);
+
+/* Text for a dg_status code; never NULL.  Replaces TORCH_CHECK message strings. */
+DG_API const char* dg_strerror(int code);
+
+/* The cudaError_t (as int) behind the calling thread's most recent DG_ERR_CUDA. */
+DG_API int dg_last_cuda_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEEPGEMM_B200_H_ */

@@ -1,0 +1,201 @@
+"""CPU oracle for the grouped MoE GEMM path -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+A restatement, in plain torch CPU ops, of the dequant-matmul references that the
+HYGON-AI/deepgemm-das test scripts compare their GPU kernels with.  Only tests/,
+__graft_entry__.smoke() and bench.py's CPU-baseline / reference arm may import this module;
+the shipped package never does.
+
+Parity pin: tests/golden/*.npz holds inputs and outputs produced by the reference's own
+helper functions (imported from its op_test/ directory by tests/golden/make_golden.py);
+tests/test_oracle.py checks every function here against them bit for bit.
+
+Every function names the reference lines it follows (paths inside the reference tree).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+
+
+# ----------------------------------------------------------------------------- quantisers
+def per_token_quant_int8(x: torch.Tensor, eps: float = 1e-10) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Symmetric per-row int8 quantisation; op_test/quant_utils.py:4-19.
+    scale = absmax/127 (keepdim), q = round(x * (127/absmax)) clamped to [-128,127]."""
+    xf = x.float()
+    absmax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(eps)
+    scale = absmax / 127.0
+    q = torch.round(xf * (127.0 / absmax)).clamp(-128, 127).to(torch.int8)
+    return q.contiguous(), scale.contiguous()
+
+
+def per_token_quant_fp8(x: torch.Tensor, eps: float = 1e-10) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Symmetric per-row e4m3 quantisation with scale = absmax/448.  The reference has no such
+    helper (its FP8 tests cast small integers); this mirrors per_token_quant_int8's structure
+    with the e4m3 maximum, as the benchmark configurations specify."""
+    xf = x.float()
+    absmax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(eps)
+    scale = absmax / FP8_MAX
+    q = (xf * (FP8_MAX / absmax)).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return q.contiguous(), scale.contiguous()
+
+
+def to_int8(t: torch.Tensor) -> torch.Tensor:
+    """op_test/masked_w8a8_int8_common.py:25-26."""
+    return torch.round(t.clamp(min=-128, max=127)).to(torch.int8)
+
+
+# ----------------------------------------------------------------------------- int4
+def unpack_int4_to_int8_x16(packed: torch.Tensor, nibble_order: str = "high_first") -> torch.Tensor:
+    """Framework int4 bytes [E,N,K/2] -> int8 [E,N,K] holding 16 * (signed nibble): the value
+    the W4A8 kernels multiply by.  op_test/test_deepgemm_masked_w4a8.py:19-30 (high nibble =
+    even k).  `low_first` swaps the two nibbles of each byte first."""
+    p = packed.view(torch.uint8).to(torch.int16)
+    high = (p & 0xF0)
+    low = ((p << 4) & 0xF0)
+    first, second = (high, low) if nibble_order == "high_first" else (low, high)
+    e, n, kh = packed.shape
+    out = torch.empty((e, n, kh * 2), dtype=torch.int16)
+    out[..., 0::2] = first
+    out[..., 1::2] = second
+    out = torch.where(out > 127, out - 256, out)  # reinterpret the byte as int8
+    return out.to(torch.int8)
+
+
+def signed_int4(u4: torch.Tensor) -> torch.Tensor:
+    """Unsigned nibble 0..15 -> signed -8..7; op_test/test_deepgemm_masked_w4a8_hipc.py:77."""
+    u = u4.to(torch.int16) & 0xF
+    return torch.where(u > 7, u - 16, u).to(torch.int8)
+
+
+# ----------------------------------------------------------------------------- masked references
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().cpu().to(torch.float32)
+
+
+def ref_masked_scaled(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor,
+                      b_scale: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Per-token x per-channel masked reference, all rows computed (callers compare rows below
+    masked_m only).  a [E,M,K], b [E,N,K] (int8 or e4m3, row-major), a_scale [E,M,1],
+    b_scale [E,N,1].  op_test/masked_w8a8_int8_common.py:55-69,
+    op_test/test_deepgemm_masked_w8a8_fp8.py:15-34: fp32 bmm, then a_scale * c * b_scale^T."""
+    c = torch.bmm(_f32(a), _f32(b).transpose(1, 2))
+    e, m, _ = a.shape
+    n = b.shape[1]
+    c = _f32(a_scale).reshape(e, m, 1) * c * _f32(b_scale).reshape(e, n, 1).transpose(1, 2)
+    return c.to(out_dtype)
+
+
+def ref_masked_tensor_wise(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor,
+                           b_scale: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """One weight scale per expert; op_test/test_deepgemm_masked_w8a8_fp8_tensor_wise.py:15-33:
+    input_scale * C * weight_scale.view(-1,1,1)."""
+    c = torch.bmm(_f32(a), _f32(b).transpose(1, 2))
+    e, m, _ = a.shape
+    c = _f32(a_scale).reshape(e, m, 1) * c * _f32(b_scale).reshape(-1, 1, 1)
+    return c.to(out_dtype)
+
+
+def ref_masked_bf16(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """op_test/test_deepgemm_masked_w16a16_bf16.py:74: fp32 matmul per expert -> bf16."""
+    return torch.bmm(_f32(a), _f32(b).transpose(1, 2)).to(torch.bfloat16)
+
+
+def ref_masked_w4a8(a: torch.Tensor, packed_b: torch.Tensor, a_scale: torch.Tensor,
+                    b_scale: torch.Tensor, nibble_order: str = "high_first") -> torch.Tensor:
+    """op_test/test_deepgemm_masked_w4a8.py:19-45: weights unpacked with the nibble in the high
+    4 bits (16 x value), then the per-channel reference; b_scale already carries the 1/16."""
+    return ref_masked_scaled(a, unpack_int4_to_int8_x16(packed_b, nibble_order), a_scale, b_scale)
+
+
+# ----------------------------------------------------------------------------- contiguous references
+def ref_contiguous(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor,
+                   m_indices: torch.Tensor, out_dtype=torch.bfloat16,
+                   tensor_wise: bool = False) -> torch.Tensor:
+    """a [M,K], b [E,N,K], a_scale [M] or [M,1], b_scale [E,N(,1)] or (tensor-wise) [E(,1)],
+    m_indices [M] (-1 = padding row, left zero).  op_test/contiguous_w8a8_int8_common.py:73-109,
+    op_test/test_deepgemm_contiguous_w8a8_fp8.py:77-112: per expert fp32 matmul, times the row
+    scale, times the column scale; tensor-wise form
+    op_test/test_deepgemm_contiguous_w8a8_fp8_tensor_wise.py:72-99."""
+    af, bf = _f32(a), _f32(b)
+    sa = _f32(a_scale).reshape(-1)
+    sb = _f32(b_scale)
+    idx = m_indices.detach().cpu().to(torch.long)
+    m, n = a.shape[0], b.shape[1]
+    out = torch.zeros((m, n), dtype=out_dtype)
+    for e in range(b.shape[0]):
+        rows = torch.nonzero(idx == e, as_tuple=False).flatten()
+        if rows.numel() == 0:
+            continue
+        o = af.index_select(0, rows).matmul(bf[e].t())
+        o = o * sa.index_select(0, rows).view(-1, 1)
+        o = o * (sb.reshape(-1)[e] if tensor_wise else sb[e].reshape(1, -1))
+        out[rows] = o.to(out_dtype)
+    return out
+
+
+# ----------------------------------------------------------------------------- exact accumulators
+def exact_int_acc(a_rows: torch.Tensor, b_rows: torch.Tensor) -> torch.Tensor:
+    """Exact sum_k a[m,k]*b[n,k] for int8 operands as int32 [M,N] (float64 matmul is exact:
+    |acc| <= K*128*128 << 2^53).  The fp32 matmul of the references above is only exact while
+    partial sums stay below 2^24, so bit-exactness of the kernels' int32 accumulators is
+    checked against this function instead."""
+    acc = a_rows.detach().cpu().to(torch.float64).matmul(b_rows.detach().cpu().to(torch.float64).t())
+    return acc.to(torch.int64).to(torch.int32)
+
+
+def epilogue_from_acc(acc: torch.Tensor, a_scale_rows: torch.Tensor, b_scale_cols) -> torch.Tensor:
+    """bf16( (float32(acc) * a_scale[row]) * b_scale[col] ), the order every reference uses
+    (a_scale * c * w_scale^T evaluates left to right).  acc int32 or float32 [M,N]."""
+    c = acc.to(torch.float32)
+    c = c * _f32(a_scale_rows).reshape(-1, 1)
+    if torch.is_tensor(b_scale_cols):
+        c = c * _f32(b_scale_cols).reshape(1, -1)
+    else:
+        c = c * torch.tensor(float(b_scale_cols), dtype=torch.float32)
+    return c.to(torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- comparison helpers
+def calc_diff(x: torch.Tensor, y: torch.Tensor) -> float:
+    """1 - 2*sum(x*y)/sum(x^2+y^2) (DeepGEMM's similarity measure), in float64."""
+    xd, yd = x.detach().cpu().double(), y.detach().cpu().double()
+    denom = (xd * xd + yd * yd).sum()
+    if float(denom) == 0.0:
+        return 0.0
+    return float(1.0 - 2.0 * (xd * yd).sum() / denom)
+
+
+def bf16_ulp_distance(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """Distance in units of bf16 representable steps between two bf16 tensors (int64)."""
+    def ordered(t):
+        bits = t.detach().cpu().contiguous().view(torch.int16).to(torch.int64) & 0xFFFF
+        return torch.where(bits >= 0x8000, 0x8000 - bits, bits)  # sign-magnitude -> ordered
+    return (ordered(x) - ordered(y)).abs()
+
+
+# ----------------------------------------------------------------------------- layout helpers
+def build_contiguous_layout(rows_per_group, align: int = 256) -> Tuple[torch.Tensor, int]:
+    """m_indices for groups padded to `align` rows with -1 on padding rows
+    (op_test/contiguous_w8a8_int8_common.py:38-62).  Returns (m_indices int32 [M_total], M_total)."""
+    chunks = []
+    for g, m in enumerate(rows_per_group):
+        m = int(m)
+        padded = ((m + align - 1) // align) * align
+        chunks.append(torch.full((m,), g, dtype=torch.int32))
+        chunks.append(torch.full((padded - m,), -1, dtype=torch.int32))
+    idx = torch.cat(chunks) if chunks else torch.zeros((0,), dtype=torch.int32)
+    return idx, int(idx.numel())
+
+
+def topk_routing_counts(num_tokens: int, num_experts: int, top_k: int,
+                        gen: torch.Generator, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tokens per expert when each token picks top_k distinct experts by random score."""
+    scores = torch.rand(num_tokens, num_experts, generator=gen) if bias is None else \
+        torch.randn(num_tokens, num_experts, generator=gen) + bias
+    picks = scores.topk(top_k, dim=1).indices.flatten()
+    return torch.bincount(picks, minlength=num_experts)

@@ -1,0 +1,77 @@
+"""The C-ABI library loads on a CPU-only box and exports exactly what include/*.h declares.
+No compute call is made here."""
+import ctypes
+import os
+import re
+
+import deepgemm
+from deepgemm import _cabi
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(REPO, "include", "deepgemm_b200.h")
+
+
+def _declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\bDG_API\s+[\w\s\*]+?\b(dg_\w+)\s*\(", text)))
+
+
+def test_header_functions_are_exported():
+    names = _declared_functions()
+    assert set(names) == set(_cabi.EXPORTED_SYMBOLS), names
+    lib = ctypes.CDLL(_cabi.LIB_PATH)
+    for n in names:
+        assert getattr(lib, n) is not None
+
+
+def test_struct_layouts_match_header_field_order():
+    text = open(HEADER).read()
+    for struct, cls in (("dg_masked_args", _cabi.MaskedArgs), ("dg_contig_args", _cabi.ContigArgs)):
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), text, flags=re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        fields = re.findall(r"(\w+)\s*;", body)
+        assert fields == [f[0] for f in cls._fields_], (struct, fields)
+    assert ctypes.sizeof(_cabi.MaskedArgs) == 96 and ctypes.sizeof(_cabi.ContigArgs) == 96
+
+
+def test_query_and_strerror_without_a_device():
+    assert _cabi.query(_cabi.QUERY_ABI_VERSION) == 1
+    assert _cabi.lib.dg_strerror(0) == b"ok"
+    assert b"16-byte" in _cabi.lib.dg_strerror(-4)
+    assert _cabi.lib.dg_strerror(12345) == b"unknown status code"
+    assert _cabi.query(_cabi.QUERY_LAUNCH_COUNT) >= 0
+
+
+def test_calls_validate_before_touching_the_device():
+    # argument errors are reported by code, never by a crash, also without any GPU
+    assert _cabi.lib.dg_masked_gemm(None, None) == -1
+    a = _cabi.MaskedArgs(kind=9)
+    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -2
+    a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=_cabi.SCALE_NONE, num_groups=1, max_m=4, n=64, k=128)
+    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -5      # int8 needs scales
+    a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=1, max_m=4, n=60, k=128)
+    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -3      # N % 16
+    a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=1, max_m=4, n=64, k=100)
+    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -3      # K % 128
+    a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=5000, max_m=4, n=64, k=128)
+    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -8
+    a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=1, max_m=4, n=64, k=128)
+    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -1      # null pointers
+    c = _cabi.ContigArgs(kind=_cabi.KIND_E4M3, scale_mode=0, num_groups=1, m_total=1 << 22, n=64, k=128)
+    assert _cabi.lib.dg_contig_gemm(ctypes.byref(c), None) == -8
+    assert _cabi.lib.dg_pack_weight(0, None, None, 1, 16, 128, 0, None) == -1
+    assert _cabi.lib.dg_pack_weight(7, 16, 32, 1, 16, 128, 0, None) == -2
+    assert _cabi.lib.dg_pack_weight(0, 16, 32, 1, 16, 100, 0, None) == -3
+    assert _cabi.lib.dg_pack_weight(0, 17, 32, 1, 16, 128, 0, None) == -4
+    assert _cabi.lib.dg_pack_weight(2, 16, 32, 1, 16, 128, 5, None) == -9
+
+
+def test_missing_library_is_a_loud_import_error(tmp_path, monkeypatch):
+    import importlib
+    import pytest
+    monkeypatch.setenv("DEEP_GEMM_LIB_PATH", str(tmp_path / "nope.so"))
+    spec = importlib.util.spec_from_file_location("cabi_probe", _cabi.__file__)
+    mod = importlib.util.module_from_spec(spec)
+    with pytest.raises(ImportError, match="no fallback"):
+        spec.loader.exec_module(mod)

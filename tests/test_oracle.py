@@ -1,0 +1,93 @@
+"""The CPU oracle against the golden vectors produced by the reference's own helpers
+(tests/golden/make_golden.py).  Bit-exact comparisons: both sides are torch CPU fp32."""
+import torch
+
+import dg_oracle as O
+from helpers import load_golden
+
+
+def _same_bits(x, y):
+    assert x.dtype == y.dtype and x.shape == y.shape
+    xb = x.contiguous().view(torch.int16) if x.dtype == torch.bfloat16 else x
+    yb = y.contiguous().view(torch.int16) if y.dtype == torch.bfloat16 else y
+    assert torch.equal(xb, yb)
+
+
+def test_per_token_quant_int8_matches_reference():
+    g = load_golden("quant_int8")
+    q, s = O.per_token_quant_int8(g["x"])
+    assert torch.equal(q, g["q"]) and torch.equal(s, g["scale"])
+
+
+def test_masked_int8_matches_reference():
+    g = load_golden("masked_int8")
+    _same_bits(O.ref_masked_scaled(g["a"], g["b"], g["a_scale"], g["b_scale"]), g["out"])
+
+
+def test_masked_fp8_matches_reference():
+    g = load_golden("masked_fp8")
+    _same_bits(O.ref_masked_scaled(g["a"], g["b"], g["a_scale"], g["b_scale"]), g["out"])
+
+
+def test_masked_fp8_tensor_wise_matches_reference():
+    g = load_golden("masked_fp8_tensor_wise")
+    _same_bits(O.ref_masked_tensor_wise(g["a"], g["b"], g["a_scale"], g["b_scale"]), g["out"])
+
+
+def test_int4_unpack_and_w4a8_match_reference():
+    g = load_golden("masked_w4a8")
+    unpacked = O.unpack_int4_to_int8_x16(g["framework"])
+    assert torch.equal(unpacked, g["unpacked"])
+    # nibble in the high bits == 16 x the signed nibble
+    assert torch.equal(unpacked.to(torch.int16), O.signed_int4(g["u4"]).to(torch.int16) * 16)
+    _same_bits(O.ref_masked_w4a8(g["a"], g["framework"], g["a_scale"], g["b_scale"]), g["out"])
+
+
+def test_contiguous_int8_matches_reference():
+    g = load_golden("contig_int8")
+    _same_bits(O.ref_contiguous(g["a"], g["b"], g["a_scale"], g["b_scale"], g["m_indices"]), g["out"])
+
+
+def test_contiguous_fp8_matches_reference():
+    g = load_golden("contig_fp8")
+    _same_bits(O.ref_contiguous(g["a"], g["b"], g["a_scale"], g["b_scale"], g["m_indices"]), g["out"])
+
+
+def test_contiguous_fp8_tensor_wise_matches_reference():
+    # The reference helper for this case accumulates with torch.dot per element, so summation
+    # order differs from a matmul: compare within 1 bf16 ulp rather than bit for bit.
+    g = load_golden("contig_fp8_tensor_wise")
+    got = O.ref_contiguous(g["a"], g["b"], g["a_scale"], g["b_scale"], g["m_indices"],
+                           tensor_wise=True)
+    assert int(O.bf16_ulp_distance(got, g["out"]).max()) <= 1
+    pad = g["m_indices"] < 0
+    assert torch.equal(got[pad].float(), torch.zeros_like(got[pad].float()))
+
+
+def test_exact_accumulator_and_epilogue_agree_with_fp32_reference_on_small_sums():
+    # With |acc| < 2^24 the reference's fp32 matmul is exact, so the exact-accumulator route
+    # (the one the GPU parity tests use) must reproduce it bit for bit.
+    g = load_golden("masked_int8")
+    for e in range(g["a"].shape[0]):
+        acc = O.exact_int_acc(g["a"][e], g["b"][e])
+        assert int(acc.abs().max()) < 2 ** 24
+        out = O.epilogue_from_acc(acc, g["a_scale"][e], g["b_scale"][e])
+        _same_bits(out, g["out"][e])
+
+
+def test_calc_diff_and_ulp_helpers():
+    x = torch.randn(64, 64)
+    assert O.calc_diff(x, x) < 1e-12
+    assert abs(O.calc_diff(x, -x) - 2.0) < 1e-9
+    a = torch.tensor([1.0, -1.0, 0.0], dtype=torch.bfloat16)
+    b = torch.tensor([1.0078125, -1.0078125, 0.0], dtype=torch.bfloat16)
+    assert O.bf16_ulp_distance(a, b).tolist() == [1, 1, 0]
+    assert O.bf16_ulp_distance(torch.tensor([0.0], dtype=torch.bfloat16),
+                               torch.tensor([-0.0], dtype=torch.bfloat16)).tolist() == [0]
+
+
+def test_contiguous_layout_builder():
+    idx, m = O.build_contiguous_layout([3, 0, 256, 257], align=256)
+    assert m == 256 + 0 + 256 + 512
+    assert idx[:3].tolist() == [0, 0, 0] and int(idx[3]) == -1
+    assert int((idx == 3).sum()) == 257 and int((idx == -1).sum()) == m - 3 - 256 - 257
