@@ -1,0 +1,249 @@
+"""GPU parity of the masked grouped GEMM entry points (through the Python API -> custom op
+-> C ABI) against the CPU oracle.
+
+Criteria: INT8 / W4A8 -- raw int32 accumulators bit-exact and bf16 output within 1 bf16 ulp
+of the reference formula; FP8 / BF16 -- calc_diff (1 - 2*sum(xy)/sum(x^2+y^2)) < 1e-3, and
+bit-exact where inputs are small integers (sums are then order independent)."""
+import pytest
+import torch
+
+import deepgemm
+from deepgemm import _cabi, _core
+from deepgemm import group_gemm_weight_pack as P
+
+import dg_oracle as O
+from helpers import (assert_bf16_within_ulp, assert_calc_diff, gen_masked_fp8, gen_masked_int8,
+                     gen_masked_w4a8, load_golden)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+SENTINEL = 17.0
+
+
+def _status():
+    return torch.zeros(_cabi.STATUS_WORDS, dtype=torch.int32, device=DEV)
+
+
+def _check_int_case(c, kind, b_rows_int8, b_packed, b_scale_kernel, block_n=0, what=""):
+    """Runs the kernel with the accumulator dump on and checks acc bit-exact, output <= 1 ulp,
+    rows >= masked_m untouched."""
+    G, max_m, K = c["a"].shape
+    N = b_rows_int8.shape[1]
+    d = torch.full((G, max_m, N), SENTINEL, dtype=torch.bfloat16, device=DEV)
+    acc = torch.full((G, max_m, N), -12345, dtype=torch.int32, device=DEV)
+    st = _status()
+    _core.grouped_gemm_masked(kind, _cabi.SCALE_PER_CHANNEL, c["a"].to(DEV), b_packed.to(DEV), d,
+                              c["a_scale"].to(DEV), b_scale_kernel.to(DEV), c["masked_m"].to(DEV),
+                              int(c["masked_m"].max()), block_n=block_n, debug_acc=acc, status=st)
+    torch.cuda.synchronize()
+    assert st.tolist() == [0, 0, 0, 0], f"{what}: device status {st.tolist()}"
+    d, acc = d.cpu(), acc.cpu()
+    for g in range(G):
+        m = int(c["masked_m"][g])
+        want_acc = O.exact_int_acc(c["a"][g, :m], b_rows_int8[g])
+        assert torch.equal(acc[g, :m], want_acc), f"{what}: int32 accumulators differ in group {g}"
+        want = O.epilogue_from_acc(want_acc, c["a_scale"][g, :m], b_scale_kernel[g])
+        assert_bf16_within_ulp(d[g, :m], want, 0, f"{what} group {g} vs exact epilogue")
+        assert torch.all(d[g, m:].float() == SENTINEL), f"{what}: rows >= masked_m written (group {g})"
+        assert torch.all(acc[g, m:] == -12345)
+    ref = O.ref_masked_scaled(c["a"], b_rows_int8, c["a_scale"].unsqueeze(-1), b_scale_kernel.unsqueeze(-1))
+    for g in range(G):
+        m = int(c["masked_m"][g])
+        assert_bf16_within_ulp(d[g, :m], ref[g, :m], 1, f"{what} group {g} vs reference formula")
+
+
+def test_config1_masked_int8_bit_exact():
+    """G=4, max_m=64, N=512, K=256, masked_m uniform in [1,64]."""
+    gen = torch.Generator().manual_seed(0)
+    mm = torch.randint(1, 65, (4,), generator=gen)
+    c = gen_masked_int8(4, 64, 512, 256, mm, seed=0)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], what="config 1")
+
+
+def test_config1_through_public_api_and_both_tile_widths():
+    gen = torch.Generator().manual_seed(1)
+    mm = torch.randint(1, 65, (4,), generator=gen)
+    c = gen_masked_int8(4, 64, 512, 256, mm, seed=1)
+    bp = P.marlin_i8_masked_weight(c["b"].clone().to(DEV))          # GPU packer
+    outs = []
+    for fn in (deepgemm.m_grouped_w8a8_gemm_nt_masked, deepgemm.m_grouped_i8_gemm_nt_masked,
+               deepgemm.m_grouped_w8a8_gemm_nt_masked_ll):
+        d = torch.zeros(4, 64, 512, dtype=torch.bfloat16, device=DEV)
+        r = fn([c["a"].to(DEV), c["a_scale"].unsqueeze(-1).to(DEV)],
+               [bp, c["b_scale"].unsqueeze(-1).to(DEV)], d, c["masked_m"].to(DEV), int(mm.max()))
+        assert r is d
+        outs.append(d.cpu())
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert torch.equal(outs[0].view(torch.int16), outs[2].view(torch.int16))
+    for bn in (128, 256):
+        _check_int_case(c, _cabi.KIND_I8, c["b"], bp.cpu(), c["b_scale"], block_n=bn, what=f"BN={bn}")
+
+
+def test_golden_masked_int8():
+    g = load_golden("masked_int8")
+    E, M, K = g["a"].shape
+    bp = P.marlin_i8_masked_weight(g["b"].clone())
+    d = torch.zeros(E, M, g["b"].shape[1], dtype=torch.bfloat16, device=DEV)
+    deepgemm.m_grouped_w8a8_gemm_nt_masked((g["a"].to(DEV), g["a_scale"].to(DEV)),
+                                           (bp.to(DEV), g["b_scale"].to(DEV)), d,
+                                           torch.full((E,), M, dtype=torch.int32, device=DEV), M)
+    assert_bf16_within_ulp(d.cpu(), g["out"], 1, "golden masked int8")
+
+
+def test_every_masked_m_from_0_to_max():
+    """One group per possible row count, crossing the 128-row tile boundary."""
+    max_m, N, K = 160, 128, 128
+    mm = torch.arange(0, max_m + 1)
+    c = gen_masked_int8(max_m + 1, max_m, N, K, mm, seed=2)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], what="masked_m sweep")
+
+
+def test_skewed_routing_and_empty_groups():
+    """Many empty groups, one very long one (the shape of real decode routing)."""
+    mm = torch.tensor([0, 0, 700, 0, 1, 0, 0, 129, 0, 0, 0, 31, 0, 0, 0, 0, 256, 0, 0, 3])
+    c = gen_masked_int8(len(mm), 704, 256, 256, mm, seed=3)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    for bn in (128, 256):
+        _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn, what=f"skew BN={bn}")
+
+
+def test_all_groups_empty_is_a_no_op():
+    c = gen_masked_int8(3, 16, 64, 128, [0, 0, 0], seed=4)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], what="all empty")
+
+
+@pytest.mark.parametrize("N,K", [(48, 128), (192, 384), (272, 7168)])
+def test_ragged_n_and_deep_k(N, K):
+    """N not a multiple of the tile width; K long enough to wrap the stage ring many times."""
+    c = gen_masked_int8(2, 128, N, K, [77, 128], seed=5)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    for bn in (128, 256):
+        _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn, what=f"N={N} K={K} BN={bn}")
+
+
+def test_int32_accumulator_beyond_fp32_exact_range():
+    """All-extreme operands: |acc| = K*127*127 > 2^24, where an fp32-accumulating path would round."""
+    G, M, N, K = 1, 16, 64, 7168
+    a = torch.full((G, M, K), 127, dtype=torch.int8)
+    b = torch.full((G, N, K), -127, dtype=torch.int8)
+    a[0, 1, 5] = 126
+    c = dict(a=a, a_scale=torch.ones(G, M), b=b, b_scale=torch.ones(G, N),
+             masked_m=torch.tensor([M], dtype=torch.int32))
+    _check_int_case(c, _cabi.KIND_I8, b, P.marlin_i8_masked_weight(b.clone()), c["b_scale"], what="big acc")
+
+
+# ----------------------------------------------------------------------------- FP8
+def _run_fp8(c, tensor_wise, fn, block_n=0):
+    G, max_m, K = c["a"].shape
+    N = c["b"].shape[1]
+    bp = P.marlin_fp8_masked_weight(c["b"].clone().to(DEV))
+    d = torch.full((G, max_m, N), SENTINEL, dtype=torch.bfloat16, device=DEV)
+    if fn is None:
+        st = _status()
+        _core.grouped_gemm_masked(_cabi.KIND_E4M3,
+                                  _cabi.SCALE_TENSOR_WISE if tensor_wise else _cabi.SCALE_PER_CHANNEL,
+                                  c["a"].to(DEV), bp, d, c["a_scale"].to(DEV), c["b_scale"].to(DEV),
+                                  c["masked_m"].to(DEV), int(c["masked_m"].max()), block_n=block_n, status=st)
+        torch.cuda.synchronize()
+        assert st.tolist() == [0, 0, 0, 0]
+    else:
+        fn((c["a"].to(DEV), c["a_scale"].to(DEV)), (bp, c["b_scale"].to(DEV)), d,
+           c["masked_m"].to(DEV), int(c["masked_m"].max()))
+    return d.cpu()
+
+
+@pytest.mark.parametrize("tensor_wise", [False, True])
+def test_masked_fp8_random(tensor_wise):
+    mm = [0, 5, 64, 128, 100, 1]
+    c = gen_masked_fp8(6, 128, 512, 1024, mm, seed=6, tensor_wise=tensor_wise)
+    fn = deepgemm.m_grouped_fp8_gemm_nt_masked_tensor_wise if tensor_wise else deepgemm.m_grouped_fp8_gemm_nt_masked
+    d = _run_fp8(c, tensor_wise, fn)
+    ref = (O.ref_masked_tensor_wise if tensor_wise else O.ref_masked_scaled)(
+        c["a"], c["b"], c["a_scale"], c["b_scale"])
+    for g, m in enumerate(mm):
+        if m:
+            assert_calc_diff(d[g, :m], ref[g, :m], 1e-3, f"fp8 group {g}")   # tolerance: calc_diff < 1e-3
+        assert torch.all(d[g, m:].float() == SENTINEL)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_masked_fp8_integer_inputs_are_bit_exact(bn):
+    """Small-integer e4m3 operands (as the reference's unified tests use): every partial sum is
+    exact in fp32, so the result must equal the oracle's bit for bit."""
+    mm = [128, 3, 0, 77]
+    c = gen_masked_fp8(4, 128, 256, 512, mm, seed=7, integer=True)
+    d = _run_fp8(c, False, None, block_n=bn)
+    ref = O.ref_masked_scaled(c["a"], c["b"], c["a_scale"], c["b_scale"])
+    for g, m in enumerate(mm):
+        assert_bf16_within_ulp(d[g, :m], ref[g, :m], 0, f"fp8 integer group {g}")
+
+
+def test_golden_masked_fp8_and_tensor_wise():
+    for name, tw in (("masked_fp8", False), ("masked_fp8_tensor_wise", True)):
+        g = load_golden(name)
+        E, M, K = g["a"].shape
+        c = dict(a=g["a"], a_scale=g["a_scale"], b=g["b"], b_scale=g["b_scale"],
+                 masked_m=torch.full((E,), M, dtype=torch.int32))
+        fn = deepgemm.m_grouped_fp8_gemm_nt_masked_ll_tensor_wise if tw else deepgemm.m_grouped_fp8_gemm_nt_masked_ll
+        d = _run_fp8(c, tw, fn)
+        assert_bf16_within_ulp(d, g["out"], 0, f"golden {name}")
+
+
+def test_fp8_nan_rows_above_masked_m_do_not_leak():
+    """Rows >= masked_m may hold anything, even NaN bit patterns: valid rows are unaffected."""
+    mm = [40, 128]
+    c = gen_masked_fp8(2, 128, 256, 256, mm, seed=8)
+    ref = O.ref_masked_scaled(c["a"], c["b"], c["a_scale"], c["b_scale"])
+    a_bits = c["a"].view(torch.uint8).clone()
+    a_bits[0, 40:] = 0x7F                       # e4m3 NaN
+    c["a"] = a_bits.view(torch.float8_e4m3fn)
+    d = _run_fp8(c, False, None)
+    assert torch.isfinite(d[0, :40].float()).all()
+    assert_calc_diff(d[0, :40], ref[0, :40], 1e-3, "rows below a NaN tail")
+
+
+# ----------------------------------------------------------------------------- W4A8
+@pytest.mark.parametrize("order", ["high_first", "low_first"])
+def test_masked_w4a8_bit_exact(order):
+    mm = [0, 256, 17, 130]
+    c = gen_masked_w4a8(4, 256, 384, 512, mm, seed=9, nibble_order=order)
+    bp = P.pack_w4a8_moe_hipc_weight(c["b_framework"].clone().to(DEV), nibble_order=order).cpu()
+    w_x16 = (c["w4"].to(torch.int16) * 16).to(torch.int8)     # what the kernel multiplies by
+    assert torch.equal(w_x16, O.unpack_int4_to_int8_x16(c["b_framework"], order))
+    _check_int_case(c, _cabi.KIND_W4A8, w_x16, bp, c["b_scale"] / 16.0, what=f"w4a8 {order}")
+
+
+def test_masked_w4a8_public_api_and_golden():
+    g = load_golden("masked_w4a8")
+    E, M, K = g["a"].shape
+    N = g["framework"].shape[1]
+    bp = P.pack_w4a8_moe_hipc_weight(g["framework"].clone().to(DEV))
+    mm = torch.full((E,), M, dtype=torch.int32, device=DEV)
+    for fn in (deepgemm.m_grouped_w4a8_gemm_nt_masked, deepgemm.m_grouped_w4a8_gemm_nt_masked_hipc):
+        d = torch.zeros(E, M, N, dtype=torch.bfloat16, device=DEV)
+        fn((g["a"].to(DEV), g["a_scale"].to(DEV)), (bp, g["b_scale"].to(DEV)), d, mm, M)
+        assert_bf16_within_ulp(d.cpu(), g["out"], 1, "golden masked w4a8")
+
+
+# ----------------------------------------------------------------------------- BF16
+def test_masked_bf16():
+    gen = torch.Generator().manual_seed(10)
+    G, M, N, K = 4, 128, 512, 1024
+    a = (torch.randn(G, M, K, generator=gen) * 0.1).bfloat16()
+    w = (torch.randn(G, N, K, generator=gen) * 0.1).bfloat16()
+    mm = [14, 56, 0, 128]
+    packed, cfg = deepgemm.pack_bf16_masked_weight(w.clone().to(DEV))
+    d = torch.zeros(G, M, N, dtype=torch.bfloat16, device=DEV)
+    r = deepgemm.m_grouped_bf16_gemm_nt_masked(a.to(DEV), packed, d,
+                                               torch.tensor(mm, dtype=torch.int32, device=DEV), 128, cfg)
+    assert r is d
+    d = d.cpu()
+    ref = O.ref_masked_bf16(a, w)
+    for g, m in enumerate(mm):
+        if m:
+            assert_calc_diff(d[g, :m], ref[g, :m], 1e-3, f"bf16 group {g}")      # calc_diff < 1e-3
+            assert torch.allclose(d[g, :m].float(), ref[g, :m].float(), rtol=1e-2, atol=1e-2)
+        assert torch.all(d[g, m:] == 0), "tail rows of a zero-initialised output must stay zero"
