@@ -1,0 +1,476 @@
+#!/usr/bin/env python
+"""Benchmark of the grouped MoE GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+
+A step is one pass of the hot path over one batch of synthetic input: one launch of the
+masked FP8 low-latency decode GEMM of the headline configuration (32 local experts,
+K=7168, N=4096, max_m=128, 256 tokens routed top-8; per-token x per-channel e4m3 scales).
+The metric is achieved HBM bandwidth: algorithmic bytes (activations and outputs of valid
+rows, weights of experts that have rows, scales, masked_m) per second.  With N > 1 every
+rank holds its own 32 local experts and its own routed tokens (expert parallel, weak
+scaling, no data-path collective inside the GEMM step); the expert-parallel prefill
+configuration, whose dispatch is a real NCCL all-to-all, is measured after the timed region
+and reported under "ep_prefill" with the all-to-all time kept separate from the GEMM time.
+
+One JSON line is printed by rank 0.  `--impl reference` times the reference's CPU
+implementation of the same path (its torch dequant-matmul, restated in oracle/dg_oracle.py)
+on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(REPO, "deepgemm-das_b200"))
+
+import torch  # noqa: E402
+
+# DRAM bytes (read + write) one decode launch moves per expert, from the ncu capture of the
+# 8-expert case summarised in profiles/grouped_gemm_e4m3_bn128_masked_fp8_decode.md
+# (246.03 MB per launch); traffic grows in proportion to the number of experts.
+NCU_DECODE_DRAM_BYTES_PER_EXPERT = 246.03e6 / 8
+METRIC = "masked_fp8_decode_hbm_bandwidth"
+UNIT = "GB/s"
+C2 = dict(G=32, K=7168, N=4096, max_m=128, tokens=256, top_k=8)
+
+
+def _peaks():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+    _REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+                0x2: "applications_clocks_setting", 0x10: "sync_boost"}
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.samples, self.period, self._stop, self._thread, self.h = [], period_s, False, None, None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.h = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, int(rs)))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.h is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+
+    def summary(self, t0: float, t1: float) -> dict:
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mhz = sorted(s[1] for s in inside)
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(n for b, n in self._REASONS.items() if bits & b),
+                "samples": len(inside)}
+
+
+# ----------------------------------------------------------------------------- workloads
+def make_decode_workload(device, seed: int, cfg=C2, tensor_wise: bool = False):
+    """Headline decode workload, built on the device (torch ops are plumbing here)."""
+    import deepgemm
+    from deepgemm.quant_utils import per_token_quant_fp8
+    G, K, N, max_m = cfg["G"], cfg["K"], cfg["N"], cfg["max_m"]
+    cpu_gen = torch.Generator().manual_seed(seed)
+    picks = torch.rand(cfg["tokens"], G, generator=cpu_gen).topk(cfg["top_k"], dim=1).indices
+    masked_m = torch.bincount(picks.flatten(), minlength=G).clamp(max=max_m).to(torch.int32)
+    gen = torch.Generator(device=device).manual_seed(seed)
+    a, a_scale = per_token_quant_fp8(torch.randn(G, max_m, K, device=device, generator=gen))
+    b = torch.empty(G, N, K, dtype=torch.float8_e4m3fn, device=device)
+    b_scale = torch.empty(G, N, dtype=torch.float32, device=device)
+    for g in range(G):
+        q, s = per_token_quant_fp8(torch.randn(N, K, device=device, generator=gen))
+        b[g], b_scale[g] = q, s.reshape(N)
+    if tensor_wise:  # one scale per expert for the weights (per-token scales stay)
+        b_scale = b_scale.mean(dim=1).contiguous()
+    b_packed = deepgemm.marlin_fp8_masked_weight(b)
+    d = torch.zeros(G, max_m, N, dtype=torch.bfloat16, device=device)
+    return dict(a=a, a_scale=a_scale.reshape(G, max_m).contiguous(), b=b_packed, b_scale=b_scale,
+                masked_m=masked_m.to(device), masked_m_cpu=masked_m, d=d, cfg=cfg,
+                tensor_wise=tensor_wise)
+
+
+def decode_bytes(w) -> float:
+    from deepgemm.quant_utils import algorithmic_bytes
+    cfg, mm = w["cfg"], w["masked_m_cpu"]
+    return algorithmic_bytes(int(mm.sum()), int((mm > 0).sum()), cfg["G"], cfg["N"], cfg["K"], 1, 1,
+                             tensor_wise=w["tensor_wise"])
+
+
+def run_decode(w):
+    import deepgemm
+    fn = deepgemm.m_grouped_fp8_gemm_nt_masked_tensor_wise if w["tensor_wise"] \
+        else deepgemm.m_grouped_fp8_gemm_nt_masked
+    fn((w["a"], w["a_scale"]), (w["b"], w["b_scale"]), w["d"], w["masked_m"], int(w["cfg"]["max_m"]))
+
+
+def time_launches(fn, steps: int, warmup: int, barrier=None):
+    """CUDA-event time in ms of `steps` back-to-back calls on the current stream."""
+    for _ in range(warmup):
+        fn()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    if barrier:
+        barrier()
+    return e0.elapsed_time(e1), t0, t1
+
+
+# ----------------------------------------------------------------------------- extra configurations
+def make_contig_int8_prefill(device, small=False):
+    """Contiguous INT8 prefill: 32 experts, K=7168, N=4096, 4096 tokens top-8, groups padded to
+    256 (small: 8 experts, 1024 tokens).  Returns (launch function, info)."""
+    import deepgemm
+    from deepgemm.quant_utils import algorithmic_bytes, contiguous_layout, per_token_quant_int8
+    G, K, N, tokens = (8, 7168, 4096, 1024) if small else (32, 7168, 4096, 4096)
+    cpu_gen = torch.Generator().manual_seed(3)
+    picks = torch.rand(tokens, G, generator=cpu_gen).topk(8, dim=1).indices
+    rows = torch.bincount(picks.flatten(), minlength=G)
+    m_indices, _, m_total = contiguous_layout(rows.tolist(), 256, device)
+    gen = torch.Generator(device=device).manual_seed(3)
+    a, a_s = per_token_quant_int8(torch.randn(m_total, K, device=device, generator=gen))
+    b = torch.empty(G, N, K, dtype=torch.int8, device=device)
+    b_s = torch.empty(G, N, dtype=torch.float32, device=device)
+    for g in range(G):
+        q, s = per_token_quant_int8(torch.randn(N, K, device=device, generator=gen))
+        b[g], b_s[g] = q, s.reshape(N)
+    bp = deepgemm.marlin_i8_contiguous_weight(b)
+    out = torch.zeros(m_total, N, dtype=torch.bfloat16, device=device)
+    a_s = a_s.reshape(m_total).contiguous()
+    fn = lambda: deepgemm.m_grouped_i8_gemm_nt_contiguous((a, a_s), (bp, b_s), out, m_indices)
+    v = int(rows.sum())
+    info = {"workload": "contiguous_int8_prefill G=%d K=%d N=%d V=%d M_total=%d" % (G, K, N, v, m_total),
+            "ops": 2.0 * v * N * K,
+            "bytes": algorithmic_bytes(v, int((rows > 0).sum()), G, N, K, 1, 1, index_entries=m_total)}
+    return fn, info
+
+
+def bench_contig_int8_prefill(device, steps, warmup, peaks):
+    fn, info = make_contig_int8_prefill(device)
+    sampler = ClockSampler(device.index or 0, period_s=0.002)
+    sampler.start()
+    ms, t0, t1 = time_launches(fn, steps, warmup)
+    sampler.stop()
+    tops = info["ops"] * steps / (ms * 1e-3) / 1e12
+    peak = 2.0 * peaks["bf16_tflops"]
+    return {"workload": info["workload"], "ms": ms / steps, "tops": tops, "peak_tops": peak,
+            "peak_note": "2 x %s dense bf16 cuBLAS burst TFLOP/s (8-bit tcgen05 rate is twice bf16)" % peaks["source"],
+            "frac_of_tensor_peak": tops / peak, "clocks": sampler.summary(t0, t1)}
+
+
+def make_masked_w4a8(device, small=False):
+    """Masked W4A8 down projection: 32 experts, N=7168, K=2048, max_m=256, masked_m uniform in
+    [0,256]; int4 source bytes low-nibble-first.  Returns (launch function, info)."""
+    import deepgemm
+    from deepgemm.quant_utils import (algorithmic_bytes, pack_int4_pairs, per_channel_quant_int4,
+                                      per_token_quant_int8)
+    G, N, K, max_m = 32, 7168, 2048, 256
+    cpu_gen = torch.Generator().manual_seed(4)
+    mm = torch.randint(0, max_m + 1, (G,), generator=cpu_gen).to(torch.int32)
+    gen = torch.Generator(device=device).manual_seed(4)
+    a, a_s = per_token_quant_int8(torch.randn(G, max_m, K, device=device, generator=gen))
+    fw = torch.empty(G, N, K // 2, dtype=torch.int8, device=device)
+    b_s = torch.empty(G, N, dtype=torch.float32, device=device)
+    for g in range(G):
+        q, s = per_channel_quant_int4(torch.randn(N, K, device=device, generator=gen))
+        fw[g], b_s[g] = pack_int4_pairs(q, "low_first"), s.reshape(N) / 16.0
+    bp = deepgemm.pack_w4a8_moe_hipc_weight(fw, nibble_order="low_first")
+    d = torch.zeros(G, max_m, N, dtype=torch.bfloat16, device=device)
+    a_s = a_s.reshape(G, max_m).contiguous()
+    mmd = mm.to(device)
+    fn = lambda: deepgemm.m_grouped_w4a8_gemm_nt_masked((a, a_s), (bp, b_s), d, mmd, max_m)
+    v = int(mm.sum())
+    info = {"workload": "masked_w4a8 G=32 N=7168 K=2048 max_m=256 V=%d" % v,
+            "ops": 2.0 * v * N * K, "bytes": algorithmic_bytes(v, int((mm > 0).sum()), G, N, K, 1, 0.5)}
+    return fn, info
+
+
+def bench_masked_w4a8(device, steps, warmup, peaks):
+    fn, info = make_masked_w4a8(device)
+    ms, _, _ = time_launches(fn, steps, warmup)
+    sec = ms * 1e-3 / steps
+    return {"workload": info["workload"], "ms": ms / steps, "gbs": info["bytes"] / sec / 1e9,
+            "frac_of_hbm_peak": info["bytes"] / sec / 1e9 / peaks["hbm_gbs"],
+            "tops": info["ops"] / sec / 1e12}
+
+
+def bench_ep_prefill(device, rank, world, steps, warmup, peaks):
+    """Expert-parallel FP8 contiguous gate/up: 256 experts sharded over the ranks, 4096 tokens
+    per rank routed top-8, NCCL all-to-all dispatch timed apart from the GEMM."""
+    from deepgemm import expert_parallel as ep
+    return ep.benchmark_ep_prefill(device, rank, world, steps=steps, warmup=warmup, peaks=peaks)
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 120.0):
+    """The reference's CPU path (torch fp32 dequant-matmul, via the oracle) on a bounded sample
+    of the headline workload: `ge` experts x `nc` output channels, same K, same routing."""
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import dg_oracle as O
+    from deepgemm.quant_utils import algorithmic_bytes
+    cfg = C2
+    K, max_m = cfg["K"], cfg["max_m"]
+    cpu_gen = torch.Generator().manual_seed(0)
+    picks = torch.rand(cfg["tokens"], cfg["G"], generator=cpu_gen).topk(cfg["top_k"], dim=1).indices
+    masked_m = torch.bincount(picks.flatten(), minlength=cfg["G"]).clamp(max=max_m)
+
+    def build(ge, nc):
+        g = torch.Generator().manual_seed(1)
+        a, a_s = O.per_token_quant_fp8(torch.randn(ge, max_m, K, generator=g))
+        b, b_s = O.per_token_quant_fp8(torch.randn(ge, nc, K, generator=g))
+        return a, a_s, b, b_s
+
+    def run(t, ge):
+        a, a_s, b, b_s = t
+        for e in range(ge):  # one expert at a time, valid rows only, like the reference tests compare
+            m = int(masked_m[e])
+            if m:
+                O.ref_masked_scaled(a[e:e + 1, :m], b[e:e + 1], a_s[e:e + 1, :m], b_s[e:e + 1])
+
+    # calibrate on one expert x 512 channels, then size the sample to fit the time budget
+    probe = build(1, 512)
+    run(probe, 1)
+    t0 = time.perf_counter()
+    run(probe, 1)
+    per_unit = max(time.perf_counter() - t0, 1e-4)          # seconds per (expert x 512 channels)
+    units = max(1.0, budget_s / max(steps + warmup, 1) / per_unit)
+    ge = int(min(cfg["G"], max(1, units // 8)))              # 8 units = one full expert (N=4096)
+    nc = cfg["N"] if units >= 8 else int(max(1, min(8, units))) * 512
+    t = build(ge, nc)
+    for _ in range(warmup):
+        run(t, ge)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run(t, ge)
+    sec = (time.perf_counter() - t0) / max(steps, 1)
+    mm = masked_m[:ge]
+    by = algorithmic_bytes(int(mm.sum()), int((mm > 0).sum()), ge, nc, K, 1, 1)
+    return {"value": by / sec / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": "port",
+            "sample": "%d of %d experts x %d of %d output channels, K=%d, valid rows only; "
+                      "torch fp32 dequant-matmul" % (ge, cfg["G"], nc, cfg["N"], K),
+            "seconds_per_step": sec}
+
+
+# ----------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations")
+    ap.add_argument("--small", action="store_true", help="reduced problem (8 experts) for profiler captures")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiler run: one workload's timed region only, bracketed by cudaProfilerStart/Stop")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_int8", "w4a8"],
+                    help="with --profile: which configuration to run (the JSON line is always decode)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    warmup = max(args.warmup, 3)
+    cfg = dict(C2, G=8) if args.small else C2
+    config = {"workload": "masked_fp8_decode G=%d K=%d N=%d max_m=%d tokens=%d top%d per GPU" % (
+        cfg["G"], cfg["K"], cfg["N"], cfg["max_m"], cfg["tokens"], cfg["top_k"]),
+        "sharding": "expert parallel, %d local experts per GPU" % cfg["G"],
+        "l2": "inputs (%.0f MB per GPU) exceed the 126 MB L2; no flush" % (
+            cfg["G"] * cfg["N"] * cfg["K"] / 1e6)}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        torch.set_num_threads(os.cpu_count() or 1)
+        cb = cpu_reference_arm(args.steps, args.warmup)
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT,
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": cb["seconds_per_step"] * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path. "
+                         "Use --impl reference for the CPU baseline.")
+    import deepgemm
+    from deepgemm import _cabi
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    barrier = (lambda: dist.barrier()) if dist else None
+    peaks = _peaks()
+
+    if args.profile and args.workload != "decode":
+        fn, info = (make_contig_int8_prefill if args.workload == "prefill_int8" else make_masked_w4a8)(
+            device, args.small)
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        ms, _, _ = time_launches(fn, args.steps, 0)
+        torch.cuda.profiler.stop()
+        sec = ms * 1e-3 / args.steps
+        print(json.dumps({"profile_run": True, "workload": info["workload"], "ms_per_step": ms / args.steps,
+                          "steps": args.steps, "tops": info["ops"] / sec / 1e12,
+                          "gbs": info["bytes"] / sec / 1e9, "bytes_per_launch": info["bytes"],
+                          "ops_per_launch": info["ops"]}))
+        return
+
+    w = make_decode_workload(device, seed=rank, cfg=cfg)
+    bytes_per_step = decode_bytes(w)
+    step = lambda: run_decode(w)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = _cabi.query(_cabi.QUERY_LAUNCH_COUNT)
+    if args.profile:
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        ms, t0, t1 = time_launches(step, args.steps, 0, barrier)
+        torch.cuda.profiler.stop()
+    else:
+        ms, t0, t1 = time_launches(step, args.steps, warmup, barrier)
+    launches = _cabi.query(_cabi.QUERY_LAUNCH_COUNT) - launches0
+    sampler.stop()
+    clocks = sampler.summary(t0, t1)
+    if args.profile:
+        print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps, "steps": args.steps,
+                          "gbs": bytes_per_step / (ms * 1e-3 / args.steps) / 1e9,
+                          "bytes_per_launch": bytes_per_step, "clocks": clocks}))
+        return
+
+    # ---- end to end: host buffers in, host buffer out, through the public API
+    host_in = [t.cpu().pin_memory() for t in (w["a"], w["a_scale"], w["masked_m"])]
+    dev_in = [w["a"], w["a_scale"], w["masked_m"]]
+    host_out = torch.empty(w["d"].shape, dtype=w["d"].dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        for h, dv in zip(host_in, dev_in):
+            dv.copy_(h, non_blocking=True)
+        run_decode(w)
+        host_out.copy_(w["d"], non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 100))
+    ms_e2e, _, _ = time_launches(e2e_step, e2e_steps, 3, barrier)
+
+    t_ms, t_e2e = torch.tensor([ms], device=device), torch.tensor([ms_e2e], device=device)
+    tot = torch.tensor([bytes_per_step], device=device, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    sec_step = float(t_ms) * 1e-3 / args.steps
+    value = float(tot) / sec_step / 1e9
+    e2e_value = float(tot) / (float(t_e2e) * 1e-3 / e2e_steps) / 1e9
+    own_gbs = bytes_per_step / (ms * 1e-3 / args.steps) / 1e9
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": float(t_ms) / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate, bf16 out)",
+            "data": "synthetic", "config": config,
+            "roofline": {"bound": "hbm", "achieved": own_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": own_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                         "traffic": NCU_DECODE_DRAM_BYTES_PER_EXPERT * cfg["G"],
+                         "traffic_note": "ncu dram bytes of an 8-expert launch scaled by experts",
+                         "kernel": "grouped_gemm_kernel<E4M3,BN=128> (rank 0)",
+                         "algorithmic_bytes_per_launch": bytes_per_step},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "tflops": 2.0 * int(w["masked_m_cpu"].sum()) * cfg["N"] * cfg["K"] / sec_step / 1e12 * world}
+
+    if not args.no_extras and not args.small:
+        extras = {}
+        del host_in, host_out
+        try:
+            if world == 1:
+                wt = make_decode_workload(device, seed=rank, cfg=cfg, tensor_wise=True)
+                ms_t, _, _ = time_launches(lambda: run_decode(wt), 200, 10)
+                gb = decode_bytes(wt) / (ms_t * 1e-3 / 200) / 1e9
+                extras["masked_fp8_decode_tensor_wise"] = {"ms": ms_t / 200, "gbs": gb,
+                                                           "frac_of_hbm_peak": gb / peaks["hbm_gbs"]}
+                del wt
+                extras["contiguous_int8_prefill"] = bench_contig_int8_prefill(device, 20, 3, peaks)
+                extras["masked_w4a8"] = bench_masked_w4a8(device, 200, 10, peaks)
+            del w
+            torch.cuda.empty_cache()
+            extras["ep_prefill"] = bench_ep_prefill(device, rank, world, 10, 3, peaks)
+        except Exception as exc:  # an extra must never cost the headline line
+            extras["error"] = "%s: %s" % (type(exc).__name__, exc)
+        line["other_configs"] = extras
+
+    if rank == 0 and world == 1 and not args.small:
+        torch.set_num_threads(os.cpu_count() or 1)
+        line["cpu_baseline"] = cpu_reference_arm(3, 1, budget_s=20.0)
+    elif rank == 0:
+        line["cpu_baseline"] = None
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,210 @@
+"""Expert-parallel harness around the contiguous FP8 grouped GEMM.
+
+The reference library is single-GPU and has no communication layer; serving frameworks
+shard its experts across GPUs themselves.  This module is that harness for one box: experts
+are partitioned contiguously over the ranks (expert e lives on rank e // (E / world)), every
+rank routes its own tokens top-k, rows travel to the owning ranks with NCCL all-to-all
+(counts first, payload second; ``torch.distributed``, one process per GPU), and each rank
+then quantises per token to e4m3, groups the received rows by local expert padded to 256
+rows with an ``m_indices`` array, and runs ``m_grouped_fp8_gemm_nt_contiguous`` on its own
+weights with ordinary local TMA loads.  Nothing here reads another GPU's memory from a
+kernel.  The same code runs on CPU tensors with the gloo backend for everything except the
+GEMM call, which is how the multi-rank logic is tested without GPUs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from .quant_utils import per_token_quant_fp8
+
+
+@dataclass
+class DispatchPlan:
+    send_token: torch.Tensor      # [S] index of the token each sent row copies, ordered by expert
+    send_expert: torch.Tensor     # [S] global expert id of each sent row (non-decreasing)
+    send_splits: list             # rows sent to each rank
+    counts_per_expert: torch.Tensor  # [E] rows this rank sends to each global expert
+
+
+def route_topk(logits: torch.Tensor, top_k: int) -> torch.Tensor:
+    """[T, E] routing scores -> [T, top_k] distinct expert ids per token."""
+    return logits.topk(top_k, dim=1).indices
+
+
+def build_dispatch_plan(topk_ids: torch.Tensor, num_experts: int, world: int) -> DispatchPlan:
+    """Orders the (token, expert) pairs by expert so that rows for one rank are contiguous."""
+    t, k = topk_ids.shape
+    flat = topk_ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    send_expert = flat[order]
+    send_token = torch.div(order, k, rounding_mode="floor")
+    counts = torch.bincount(flat, minlength=num_experts)
+    per_rank = counts.view(world, num_experts // world).sum(dim=1)
+    return DispatchPlan(send_token, send_expert, [int(x) for x in per_rank.tolist()], counts)
+
+
+def dispatch_tokens(hidden: torch.Tensor, plan: DispatchPlan, num_experts: int, rank: int,
+                    world: int, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All-to-all of the routed rows.  Returns (rows [R, H] received by this rank, in source-rank
+    order, local expert id [R] of each)."""
+    e_local = num_experts // world
+    send_rows = hidden.index_select(0, plan.send_token)
+    if world == 1:
+        return send_rows, plan.send_expert.clone()
+    import torch.distributed as dist
+    # 1) counts: rank r receives, from every source, its rows-per-local-expert vector
+    send_counts = plan.counts_per_expert.to(torch.int64).contiguous()          # [world * e_local]
+    recv_counts = torch.empty_like(send_counts)                                 # [world, e_local]
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    recv_counts = recv_counts.view(world, e_local)
+    recv_splits = [int(x) for x in recv_counts.sum(dim=1).tolist()]
+    # 2) payload
+    recv_rows = torch.empty((sum(recv_splits), hidden.shape[1]), dtype=hidden.dtype,
+                            device=hidden.device)
+    dist.all_to_all_single(recv_rows, send_rows, output_split_sizes=recv_splits,
+                           input_split_sizes=plan.send_splits, group=group)
+    # local expert of every received row: per source rank, experts ascend with the given counts
+    ids = torch.arange(e_local, device=hidden.device).repeat(world)
+    recv_expert = torch.repeat_interleave(ids, recv_counts.reshape(-1).to(hidden.device))
+    return recv_rows, recv_expert
+
+
+def group_and_pad(rows: torch.Tensor, expert_local: torch.Tensor, e_local: int, align: int = 256
+                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Groups rows by local expert (stable), pads each group to a multiple of `align`.
+    Returns (padded rows [M_total, H] with zero padding, m_indices int32 [M_total],
+    dest int64 [R]: where each input row went)."""
+    order = torch.argsort(expert_local, stable=True)
+    counts = torch.bincount(expert_local, minlength=e_local)
+    padded = (counts + align - 1) // align * align
+    starts = torch.cumsum(padded, 0) - padded
+    m_total = int(padded.sum())
+    sorted_expert = expert_local[order]
+    first_of_group = torch.cumsum(counts, 0) - counts
+    within = torch.arange(order.numel(), device=rows.device) - first_of_group[sorted_expert]
+    dest_sorted = starts[sorted_expert] + within
+    out = torch.zeros((m_total, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+    out.index_copy_(0, dest_sorted, rows.index_select(0, order))
+    m_indices = torch.full((m_total,), -1, dtype=torch.int32, device=rows.device)
+    m_indices.index_copy_(0, dest_sorted, sorted_expert.to(torch.int32))
+    dest = torch.empty_like(dest_sorted)
+    dest[order] = dest_sorted
+    return out, m_indices, dest
+
+
+def ep_gate_up_forward(hidden: torch.Tensor, topk_ids: torch.Tensor, b_packed: torch.Tensor,
+                       b_scale: torch.Tensor, num_experts: int, rank: int, world: int,
+                       group=None):
+    """Dispatch -> quantise -> group -> contiguous FP8 grouped GEMM on this rank's experts.
+    Returns (out bf16 [M_total, N], m_indices, recv_expert, dest)."""
+    from .m_group_gemm_nt_contiguous import m_grouped_fp8_gemm_nt_contiguous
+    plan = build_dispatch_plan(topk_ids, num_experts, world)
+    rows, recv_expert = dispatch_tokens(hidden, plan, num_experts, rank, world, group)
+    padded, m_indices, dest = group_and_pad(rows, recv_expert, num_experts // world)
+    a, a_scale = per_token_quant_fp8(padded)
+    out = torch.zeros((padded.shape[0], b_scale.shape[1]), dtype=torch.bfloat16, device=hidden.device)
+    m_grouped_fp8_gemm_nt_contiguous((a, a_scale.reshape(-1)), (b_packed, b_scale), out, m_indices)
+    return out, m_indices, recv_expert, dest
+
+
+def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup: int = 3,
+                         peaks: Optional[dict] = None, num_experts: int = 256, hidden_k: int = 7168,
+                         n: int = 4096, tokens: int = 4096, top_k: int = 8) -> dict:
+    """Times the all-to-all dispatch and the grouped GEMM separately (CUDA events, max over
+    ranks) for the expert-parallel prefill configuration; returns a JSON-able dict."""
+    from . import marlin_fp8_contiguous_weight
+    from .m_group_gemm_nt_contiguous import m_grouped_fp8_gemm_nt_contiguous
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+    e_local = num_experts // world
+    gen = torch.Generator(device=device).manual_seed(100 + rank)
+    shared = torch.Generator().manual_seed(7)                     # same expert bias on every rank
+    bias = (torch.randn(num_experts, generator=shared) * 0.5).to(device)
+    hidden = torch.randn(tokens, hidden_k, device=device, generator=gen).to(torch.bfloat16)
+    logits = torch.randn(tokens, num_experts, device=device, generator=gen) + bias
+    topk_ids = route_topk(logits, top_k)
+    b = torch.empty(e_local, n, hidden_k, dtype=torch.float8_e4m3fn, device=device)
+    b_scale = torch.empty(e_local, n, dtype=torch.float32, device=device)
+    for g in range(e_local):
+        q, s = per_token_quant_fp8(torch.randn(n, hidden_k, device=device, generator=gen))
+        b[g], b_scale[g] = q, s.reshape(n)
+    b_packed = marlin_fp8_contiguous_weight(b)
+
+    plan = build_dispatch_plan(topk_ids, num_experts, world)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def sync():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # all-to-all (counts + payload)
+    for _ in range(warmup):
+        rows, recv_expert = dispatch_tokens(hidden, plan, num_experts, rank, world)
+    sync()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        rows, recv_expert = dispatch_tokens(hidden, plan, num_experts, rank, world)
+    e1.record()
+    sync()
+    a2a_ms = e0.elapsed_time(e1) / steps
+
+    # quantise + group (torch ops; reported, not part of either headline figure)
+    e0, e1 = ev(), ev()
+    e0.record()
+    padded, m_indices, _ = group_and_pad(rows, recv_expert, e_local)
+    a, a_scale = per_token_quant_fp8(padded)
+    a_scale = a_scale.reshape(-1).contiguous()
+    e1.record()
+    torch.cuda.synchronize()
+    prep_ms = e0.elapsed_time(e1)
+    del padded, rows
+
+    out = torch.zeros((a.shape[0], n), dtype=torch.bfloat16, device=device)
+    gemm = lambda: m_grouped_fp8_gemm_nt_contiguous((a, a_scale), (b_packed, b_scale), out, m_indices)
+    for _ in range(warmup):
+        gemm()
+    sync()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        gemm()
+    e1.record()
+    sync()
+    gemm_ms = e0.elapsed_time(e1) / steps
+
+    valid = int((m_indices >= 0).sum())
+    stats = torch.tensor([a2a_ms, gemm_ms, prep_ms], device=device, dtype=torch.float64)
+    flops = torch.tensor([2.0 * valid * n * hidden_k], device=device, dtype=torch.float64)
+    sent_remote = sum(s for r, s in enumerate(plan.send_splits) if r != rank) * hidden_k * 2
+    sent = torch.tensor([float(sent_remote)], device=device, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(flops, op=dist.ReduceOp.SUM)
+        dist.all_reduce(sent, op=dist.ReduceOp.MAX)
+    a2a_ms, gemm_ms, prep_ms = (float(x) for x in stats.tolist())
+    tflops = float(flops) / (gemm_ms * 1e-3) / 1e12
+    res = {"workload": "ep_fp8_contiguous experts=%d K=%d N=%d tokens/rank=%d top%d" % (
+        num_experts, hidden_k, n, tokens, top_k), "world": world,
+        "gemm_ms_max_over_ranks": gemm_ms, "gemm_tflops_aggregate": tflops,
+        "gemm_tflops_per_gpu": tflops / world,
+        "all_to_all_ms_max_over_ranks": a2a_ms, "quantise_group_ms_max_over_ranks": prep_ms,
+        "all_to_all_remote_bytes_max_per_rank": float(sent),
+        "valid_rows_this_rank": valid, "m_total_this_rank": int(a.shape[0])}
+    if float(sent) > 0:
+        res["all_to_all_gbs_per_rank"] = float(sent) / (a2a_ms * 1e-3) / 1e9
+    if peaks:
+        weight_bytes = e_local * n * hidden_k
+        t_hbm = (weight_bytes + valid * hidden_k + valid * n * 2) / (peaks["hbm_gbs"] * 1e9)
+        t_tc = 2.0 * valid * n * hidden_k / (2.0 * peaks["bf16_tflops"] * 1e12)
+        res["gemm_roofline_ms"] = max(t_hbm, t_tc) * 1e3
+        res["gemm_bound"] = "hbm" if t_hbm > t_tc else "tensor"
+        res["gemm_frac_of_roofline"] = max(t_hbm, t_tc) * 1e3 / gemm_ms
+    return res
