@@ -35,6 +35,7 @@ import torch  # noqa: E402
 # 8-expert case summarised in profiles/grouped_gemm_e4m3_bn128_masked_fp8_decode.md
 # (246.03 MB per launch); traffic grows in proportion to the number of experts.
 NCU_DECODE_DRAM_BYTES_PER_EXPERT = 246.03e6 / 8
+PREHEAT_S = 0.5
 METRIC = "masked_fp8_decode_hbm_bandwidth"
 UNIT = "GB/s"
 C2 = dict(G=32, K=7168, N=4096, max_m=128, tokens=256, top_k=8)
@@ -325,7 +326,8 @@ def main():
         cfg["G"], cfg["K"], cfg["N"], cfg["max_m"], cfg["tokens"], cfg["top_k"]),
         "sharding": "expert parallel, %d local experts per GPU" % cfg["G"],
         "l2": "inputs (%.0f MB per GPU) exceed the 126 MB L2; no flush" % (
-            cfg["G"] * cfg["N"] * cfg["K"] / 1e6)}
+            cfg["G"] * cfg["N"] * cfg["K"] / 1e6),
+        "preheat_s": PREHEAT_S}
 
     if args.impl == "reference":
         if rank != 0:
@@ -375,6 +377,15 @@ def main():
     w = make_decode_workload(device, seed=rank, cfg=cfg)
     bytes_per_step = decode_bytes(w)
     step = lambda: run_decode(w)
+
+    # Bring the SM clock up from idle before the W warm-up steps (a freshly acquired GPU sits
+    # at its idle clock and a few milliseconds of warm-up do not ramp it): untimed launches
+    # of the same step for PREHEAT_S seconds.
+    t_pre = time.perf_counter()
+    while time.perf_counter() - t_pre < PREHEAT_S:
+        for _ in range(50):
+            step()
+        torch.cuda.synchronize()
 
     sampler = ClockSampler(local_rank)
     sampler.start()

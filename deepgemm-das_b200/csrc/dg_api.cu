@@ -8,6 +8,7 @@
 
 #include "deepgemm_b200.h"
 #include "dg_grouped_gemm.cuh"
+#include "dg_grouped_gemm_pair.cuh"
 #include "dg_pack.cuh"
 
 namespace {
@@ -221,6 +222,104 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   return DG_OK;
 }
 
+// Two-CTA (cta_group::2) 256x256 tiles for compute-bound shapes; one cluster per TPC.
+template <int KIND>
+int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
+  using L = PairSmem;
+  auto kernel = grouped_gemm_pair_kernel<KIND>;
+  const int esize = (KIND == DG_KIND_BF16) ? 2 : 1;
+  const int elems_per_row = kRowBytes / esize;
+  KernelParams p{};
+  p.mode = pr.mode;
+  p.scale_mode = pr.scale_mode;
+  p.G = pr.G;
+  p.M = pr.M;
+  p.N = pr.N;
+  p.K = pr.K;
+  p.kblocks = pr.K / elems_per_row;
+  p.n_tiles = (pr.N + kPairBN - 1) / kPairBN;
+  p.m_blocks = (pr.M + 255) / 256;  // super blocks of 256 rows
+  p.sched = pr.sched;
+  p.a_scale = pr.a_scale;
+  p.b_scale = pr.b_scale;
+  p.d = static_cast<__nv_bfloat16*>(pr.d);
+  p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
+  p.status = pr.status;
+
+  const long long max_items =
+      (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : 2LL * p.m_blocks) * p.n_tiles;
+  if (max_items <= 0) return DG_OK;
+  const int table_bytes = (pr.mode == MODE_MASKED) ? (2 * pr.G + 1) * 4 : 2 * p.m_blocks * 4;
+  const int smem_bytes = L::total(table_bytes);
+  if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
+
+  const CUtensorMapDataType dt_a =
+      (KIND == DG_KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if (pr.mode == MODE_MASKED) {
+    const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
+    const uint64_t strides[2] = {(uint64_t)pr.K * esize, (uint64_t)pr.M * pr.K * esize};
+    const uint32_t box[3] = {(uint32_t)elems_per_row, 128u, 1u};
+    rc = encode_map(&tm_a, dt_a, 3, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
+    const uint64_t strides[1] = {(uint64_t)pr.K * esize};
+    const uint32_t box[2] = {(uint32_t)elems_per_row, 128u};
+    rc = encode_map(&tm_a, dt_a, 2, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc != DG_OK) return rc;
+  {
+    const uint64_t rows = (uint64_t)pr.G * p.kblocks * pr.N;
+    const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
+    const uint64_t strides[1] = {(uint64_t)kRowBytes};
+    const uint32_t box[2] = {(uint32_t)elems_per_row, 128u};  // each block loads half the tile
+    rc = encode_map(&tm_b, dt_a, 2, pr.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc != DG_OK) return rc;
+
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(L::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+
+  // Once per device: opt in to the shared-memory size and ask how many pairs fit at once
+  // (a persistent kernel must not be given more clusters than can be resident together).
+  static std::mutex mu;
+  static int max_pairs[kMaxDevices] = {0};
+  int devid = 0;
+  cudaGetDevice(&devid);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (max_pairs[devid] == 0) {
+      cudaError_t e =
+          cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+      if (e != cudaSuccess) return cuda_fail(e);
+      cudaLaunchConfig_t q = cfg;
+      q.gridDim = dim3(dev.sm_count & ~1, 1, 1);
+      q.dynamicSmemBytes = kMaxSmem;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, kernel, &q);
+      if (e != cudaSuccess) return cuda_fail(e);
+      if (n < 1) return DG_ERR_TOO_LARGE;
+      max_pairs[devid] = n < dev.sm_count / 2 ? n : dev.sm_count / 2;
+    }
+  }
+  long long pairs = max_items < max_pairs[devid] ? max_items : max_pairs[devid];
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, p);
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int validate_and_launch(const Problem& pr, cudaStream_t stream) {
@@ -241,24 +340,42 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
   if (!aligned16(pr.a) || !aligned16(pr.b) || !aligned16(pr.d)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.scale_mode == DG_SCALE_PER_CHANNEL && !aligned16(pr.b_scale)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.debug_acc && !aligned16(pr.debug_acc)) return DG_ERR_BAD_ALIGNMENT;
-  if (pr.block_n != 0 && pr.block_n != 128 && pr.block_n != 256) return DG_ERR_BAD_ARGUMENT;
+  if (pr.block_n != 0 && pr.block_n != 128 && pr.block_n != 256 && pr.block_n != 512)
+    return DG_ERR_BAD_ARGUMENT;
 
   const DeviceInfo* dev = nullptr;
   int rc = device_info(&dev);
   if (rc != DG_OK) return rc;
 
-  // Tile width.  Weight-streaming shapes (few rows per group) want many equal items so the
-  // 148 SMs stay balanced: BN = 128.  Compute-bound shapes want the larger tile, which
-  // halves the shared-memory traffic per flop: BN = 256.
+  // Tile choice.  Weight-streaming shapes (few rows per group) want many equal items so the
+  // 148 SMs stay balanced: one-CTA tiles, BN = 128.  Compute-bound shapes want the least
+  // operand traffic per flop: two-CTA 256x256 tiles when there are enough of them to fill
+  // every SM pair twice, else one-CTA 128x256 tiles.
   int bn = pr.block_n;
   if (bn == 0) {
-    if (pr.mode == MODE_CONTIG)
-      bn = (pr.N >= 256) ? 256 : 128;
+    const long long rows = (pr.mode == MODE_CONTIG) ? (long long)pr.M
+                                                    : (long long)pr.G * (pr.expected_m > 0 ? pr.expected_m : 0);
+    // rows per group decide whether a 256-row super block is mostly real rows
+    const bool big_groups = (pr.mode == MODE_CONTIG) ? (rows / pr.G >= 512) : (pr.expected_m >= 256);
+    const long long pair_items = (rows / 256) * (pr.N / 256);
+    if (big_groups && pr.N >= 256 && pair_items >= 2LL * (dev->sm_count / 2))
+      bn = 512;
+    else if (pr.mode == MODE_CONTIG)
+      bn = (pr.N >= 256 && (rows / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
     else
       bn = (pr.expected_m > 256 && pr.N >= 256) ? 256 : 128;
   }
   if (pr.kind == DG_KIND_W4A8) bn = 128;
+  if (bn == 512 && pr.N < 256) bn = 128;
 
+  if (bn == 512) {  // two-CTA 256x256 tiles
+    switch (pr.kind) {
+      case DG_KIND_I8: return launch_pair<DG_KIND_I8>(pr, *dev, stream);
+      case DG_KIND_E4M3: return launch_pair<DG_KIND_E4M3>(pr, *dev, stream);
+      case DG_KIND_BF16: return launch_pair<DG_KIND_BF16>(pr, *dev, stream);
+      default: return DG_ERR_BAD_KIND;
+    }
+  }
   switch (pr.kind) {
     case DG_KIND_I8:
       return bn == 256 ? launch<DG_KIND_I8, 256>(pr, *dev, stream)

@@ -92,6 +92,63 @@ struct SmemLayout {
   }
 };
 
+// Per-thread output-row context of the epilogue.
+struct EpiRow {
+  float as;              // a_scale of this row (1 when unscaled)
+  float bs_g;            // per-group weight scale (TENSOR_WISE)
+  const float* bs_row;   // b_scale[g] + n0 (PER_CHANNEL)
+  __nv_bfloat16* d_row;  // &D[row][n0]
+  uint32_t* dbg_row;     // &debug_acc[row][n0] or nullptr
+};
+
+// Scales, converts and stores 32 accumulator columns of one row: out = bf16_rne((float(acc) *
+// a_scale) * b_scale), two separate fp32 multiplications in the reference's order
+// (m_grouped_fp8_gemm_nt_maksed_low_latency.cu:584), 16-byte stores, columns >= N skipped.
+template <bool kIntAcc>
+__device__ __forceinline__ void epilogue_store32(const uint32_t (&r)[32], const EpiRow& e,
+                                                 int scale_mode, int col, int cols_left) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    if (j + 8 <= cols_left) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = kIntAcc ? __int2float_rn(static_cast<int>(r[j + i])) : __uint_as_float(r[j + i]);
+      if (scale_mode == DG_SCALE_PER_CHANNEL) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(e.bs_row + col + j));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(e.bs_row + col + j + 4));
+        v[0] = (v[0] * e.as) * b0.x;
+        v[1] = (v[1] * e.as) * b0.y;
+        v[2] = (v[2] * e.as) * b0.z;
+        v[3] = (v[3] * e.as) * b0.w;
+        v[4] = (v[4] * e.as) * b1.x;
+        v[5] = (v[5] * e.as) * b1.y;
+        v[6] = (v[6] * e.as) * b1.z;
+        v[7] = (v[7] * e.as) * b1.w;
+      } else if (scale_mode == DG_SCALE_TENSOR_WISE) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (v[i] * e.as) * e.bs_g;
+      }
+      uint4 o;
+      __nv_bfloat162 h;
+      h = __floats2bfloat162_rn(v[0], v[1]);
+      o.x = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2bfloat162_rn(v[2], v[3]);
+      o.y = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2bfloat162_rn(v[4], v[5]);
+      o.z = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2bfloat162_rn(v[6], v[7]);
+      o.w = *reinterpret_cast<uint32_t*>(&h);
+      *reinterpret_cast<uint4*>(e.d_row + col + j) = o;
+      if (e.dbg_row != nullptr) {
+        *reinterpret_cast<uint4*>(e.dbg_row + col + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        *reinterpret_cast<uint4*>(e.dbg_row + col + j + 4) =
+            make_uint4(r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
+      }
+    }
+  }
+}
+
 struct TileCoord {
   int g;           // group
   int row0;        // first row: within the group (masked) or global (contiguous)
@@ -345,11 +402,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         const size_t grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 +
                             row_in_tile;
         if (p.mode == MODE_CONTIG && rv) rv = p.sched[grow] >= 0;
-        const float as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
-        const float bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
-        const float* bs_row = p.b_scale + (size_t)t.g * p.N + t.n0;  // PER_CHANNEL only
-        __nv_bfloat16* d_row = p.d + grow * p.N + t.n0;
-        uint32_t* dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
+        EpiRow row;
+        row.as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
+        row.bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
+        row.bs_row = p.b_scale + (size_t)t.g * p.N + t.n0;  // PER_CHANNEL only
+        row.d_row = p.d + grow * p.N + t.n0;
+        row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -358,51 +416,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
-          if (rv) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (j + 8 <= cols_left) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  v[i] = kIntAcc ? __int2float_rn(static_cast<int>(r[j + i]))
-                                 : __uint_as_float(r[j + i]);
-                if (p.scale_mode == DG_SCALE_PER_CHANNEL) {
-                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(bs_row + c * 32 + j));
-                  const float4 b1 =
-                      __ldg(reinterpret_cast<const float4*>(bs_row + c * 32 + j + 4));
-                  v[0] = (v[0] * as) * b0.x;
-                  v[1] = (v[1] * as) * b0.y;
-                  v[2] = (v[2] * as) * b0.z;
-                  v[3] = (v[3] * as) * b0.w;
-                  v[4] = (v[4] * as) * b1.x;
-                  v[5] = (v[5] * as) * b1.y;
-                  v[6] = (v[6] * as) * b1.z;
-                  v[7] = (v[7] * as) * b1.w;
-                } else if (p.scale_mode == DG_SCALE_TENSOR_WISE) {
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] = (v[i] * as) * bs_g;
-                }
-                uint4 o;
-                __nv_bfloat162 h;
-                h = __floats2bfloat162_rn(v[0], v[1]);
-                o.x = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(v[2], v[3]);
-                o.y = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(v[4], v[5]);
-                o.z = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(v[6], v[7]);
-                o.w = *reinterpret_cast<uint32_t*>(&h);
-                *reinterpret_cast<uint4*>(d_row + c * 32 + j) = o;
-                if (dbg_row != nullptr) {
-                  *reinterpret_cast<uint4*>(dbg_row + c * 32 + j) =
-                      make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                  *reinterpret_cast<uint4*>(dbg_row + c * 32 + j + 4) =
-                      make_uint4(r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
-                }
-              }
-            }
-          }
+          if (rv) epilogue_store32<kIntAcc>(r, row, p.scale_mode, c * 32, cols_left);
         }
       }
       // hand the accumulator back to the UMMA issuer

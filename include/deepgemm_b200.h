@@ -110,7 +110,7 @@ typedef struct dg_masked_args {
   int32_t n;                  /* N, multiple of 16 */
   int32_t k;                  /* K, multiple of 128 (64 for bf16) */
   int32_t expected_m;         /* hint only: typical masked_m; never limits the rows computed */
-  int32_t block_n;            /* 0 = choose; else 128 or 256 (tile width override, for tuning) */
+  int32_t block_n;            /* 0 = choose; 128 / 256 = one-CTA tile width; 512 = two-CTA 256x256 tiles */
   void*          debug_acc;   /* NULL, or [G][max_m][N] of raw 32-bit accumulators (s32 / f32) */
   int32_t*       status;      /* NULL, or int32[DG_STATUS_WORDS] device status words */
 } dg_masked_args;
@@ -134,7 +134,7 @@ typedef struct dg_contig_args {
   int32_t m_total;            /* <= DG_MAX_CONTIG_ROWS */
   int32_t n;
   int32_t k;
-  int32_t block_n;            /* 0 = choose; else 128 or 256 */
+  int32_t block_n;            /* 0 = choose; 128 / 256 = one-CTA tile width; 512 = two-CTA 256x256 tiles */
   int32_t reserved;
   void*          debug_acc;   /* NULL, or [M_total][N] raw accumulators */
   int32_t*       status;

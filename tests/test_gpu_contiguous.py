@@ -43,7 +43,7 @@ def _check_int8_contig(c, rows_per_group, block_n=0, what=""):
     assert_bf16_within_ulp(d[~pad], ref[~pad], 1, f"{what} vs reference formula")
 
 
-@pytest.mark.parametrize("bn", [0, 128, 256])
+@pytest.mark.parametrize("bn", [0, 128, 256, 512])
 def test_contiguous_int8_ragged_groups(bn):
     rows = [300, 0, 511, 101, 256, 1]
     c = gen_contig("int8", rows, 512, 512, seed=20)
@@ -58,7 +58,15 @@ def test_contiguous_int8_align_128_and_ragged_tail():
     assert int(c["m_indices"][cut - 1]) < 0
     c = dict(a=c["a"][:cut].contiguous(), a_scale=c["a_scale"][:cut].contiguous(), b=c["b"],
              b_scale=c["b_scale"], m_indices=c["m_indices"][:cut].contiguous())
-    _check_int8_contig(c, rows, what="align 128")
+    for bn in (0, 512):      # 512: super blocks whose halves belong to different groups
+        _check_int8_contig(c, rows, block_n=bn, what=f"align 128 BN={bn}")
+
+
+def test_contiguous_pair_kernel_many_super_blocks():
+    """Two-CTA tiles: more work items than SM pairs, several column tiles, ragged N."""
+    rows = [700, 256, 1, 0, 900, 130, 512, 255, 257, 64, 300, 1024]
+    c = gen_contig("int8", rows, 1312, 256, seed=27)
+    _check_int8_contig(c, rows, block_n=512, what="pair kernel")
 
 
 def test_contiguous_public_api_int64_indices_and_golden():
@@ -90,11 +98,15 @@ def test_contiguous_fp8_golden_and_random():
     out = torch.full((c["a"].shape[0], 512), SENTINEL, dtype=torch.bfloat16, device=DEV)
     deepgemm.m_grouped_fp8_gemm_nt_contiguous((c["a"].to(DEV), c["a_scale"].to(DEV)),
                                               (bp, c["b_scale"].to(DEV)), out, c["m_indices"].to(DEV))
-    out = out.cpu()
+    out2 = torch.full_like(out, SENTINEL)
+    _core.grouped_gemm_contiguous(_cabi.KIND_E4M3, _cabi.SCALE_PER_CHANNEL, c["a"].to(DEV), bp, out2,
+                                  c["a_scale"].to(DEV), c["b_scale"].to(DEV), c["m_indices"].to(DEV),
+                                  block_n=512)
     ref = O.ref_contiguous(c["a"], c["b"], c["a_scale"], c["b_scale"], c["m_indices"])
     pad = c["m_indices"] < 0
-    assert_calc_diff(out[~pad], ref[~pad], 1e-3, "contig fp8")                   # calc_diff < 1e-3
-    assert torch.all(out[pad].float() == SENTINEL)
+    for o, name in ((out.cpu(), "contig fp8"), (out2.cpu(), "contig fp8 two-CTA")):
+        assert_calc_diff(o[~pad], ref[~pad], 1e-3, name)                          # calc_diff < 1e-3
+        assert torch.all(o[pad].float() == SENTINEL)
 
 
 def test_contiguous_fp8_tensor_wise():

@@ -105,7 +105,7 @@ def test_skewed_routing_and_empty_groups():
     mm = torch.tensor([0, 0, 700, 0, 1, 0, 0, 129, 0, 0, 0, 31, 0, 0, 0, 0, 256, 0, 0, 3])
     c = gen_masked_int8(len(mm), 704, 256, 256, mm, seed=3)
     bp = P.marlin_i8_masked_weight(c["b"].clone())
-    for bn in (128, 256):
+    for bn in (128, 256, 512):
         _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn, what=f"skew BN={bn}")
 
 
@@ -120,7 +120,7 @@ def test_ragged_n_and_deep_k(N, K):
     """N not a multiple of the tile width; K long enough to wrap the stage ring many times."""
     c = gen_masked_int8(2, 128, N, K, [77, 128], seed=5)
     bp = P.marlin_i8_masked_weight(c["b"].clone())
-    for bn in (128, 256):
+    for bn in (128, 256, 512):
         _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn, what=f"N={N} K={K} BN={bn}")
 
 
@@ -169,7 +169,7 @@ def test_masked_fp8_random(tensor_wise):
         assert torch.all(d[g, m:].float() == SENTINEL)
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 def test_masked_fp8_integer_inputs_are_bit_exact(bn):
     """Small-integer e4m3 operands (as the reference's unified tests use): every partial sum is
     exact in fp32, so the result must equal the oracle's bit for bit."""
@@ -240,10 +240,13 @@ def test_masked_bf16():
     r = deepgemm.m_grouped_bf16_gemm_nt_masked(a.to(DEV), packed, d,
                                                torch.tensor(mm, dtype=torch.int32, device=DEV), 128, cfg)
     assert r is d
-    d = d.cpu()
+    d2 = torch.zeros(G, M, N, dtype=torch.bfloat16, device=DEV)          # two-CTA tiles
+    _core.grouped_gemm_masked(_cabi.KIND_BF16, _cabi.SCALE_NONE, a.to(DEV), packed, d2, None, None,
+                              torch.tensor(mm, dtype=torch.int32, device=DEV), 128, block_n=512)
     ref = O.ref_masked_bf16(a, w)
-    for g, m in enumerate(mm):
-        if m:
-            assert_calc_diff(d[g, :m], ref[g, :m], 1e-3, f"bf16 group {g}")      # calc_diff < 1e-3
-            assert torch.allclose(d[g, :m].float(), ref[g, :m].float(), rtol=1e-2, atol=1e-2)
-        assert torch.all(d[g, m:] == 0), "tail rows of a zero-initialised output must stay zero"
+    for out in (d.cpu(), d2.cpu()):
+        for g, m in enumerate(mm):
+            if m:
+                assert_calc_diff(out[g, :m], ref[g, :m], 1e-3, f"bf16 group {g}")      # calc_diff < 1e-3
+                assert torch.allclose(out[g, :m].float(), ref[g, :m].float(), rtol=1e-2, atol=1e-2)
+            assert torch.all(out[g, m:] == 0), "tail rows of a zero-initialised output must stay zero"
