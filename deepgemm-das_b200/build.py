@@ -22,7 +22,8 @@ LIB_PATH = os.path.join(LIB_DIR, "libdeepgemm_b200.so")
 STAMP_PATH = LIB_PATH + ".stamp"
 
 SOURCES = ["dg_api.cu"]
-HEADERS = ["dg_ptx.cuh", "dg_grouped_gemm.cuh", "dg_grouped_gemm_pair.cuh", "dg_pack.cuh"]
+HEADERS = ["dg_ptx.cuh", "dg_grouped_gemm.cuh", "dg_grouped_gemm_pair.cuh", "dg_grouped_gemm_w4.cuh",
+           "dg_pack.cuh"]
 
 
 def _nvcc() -> str:

@@ -9,6 +9,7 @@
 #include "deepgemm_b200.h"
 #include "dg_grouped_gemm.cuh"
 #include "dg_grouped_gemm_pair.cuh"
+#include "dg_grouped_gemm_w4.cuh"
 #include "dg_pack.cuh"
 
 namespace {
@@ -112,8 +113,7 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* b
 // ---- kernel instantiations: (kind, BN) -> stages so the ring holds ~192-200 KB
 template <int KIND, int BN>
 struct StagesFor {
-  static constexpr int per_stage =
-      kATileBytes + BN * kRowBytes + (KIND == DG_KIND_W4A8 ? BN * 64 : 0);
+  static constexpr int per_stage = kATileBytes + BN * kRowBytes;
   static constexpr int value = (200 * 1024) / per_stage;
 };
 
@@ -182,23 +182,14 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
     rc = encode_map(&tm_a, dt_a, 2, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc != DG_OK) return rc;
-  // B (packed): a flat list of G*kblocks*N rows, 128 bytes each (64 for W4A8), so a
-  // BN-row box is one contiguous span.  W4A8 rows land unswizzled; the unpack warps
-  // write the swizzled int8 tile themselves.
+  // B (packed): a flat list of G*kblocks*N rows of 128 bytes, so a BN-row box is one
+  // contiguous span.
   {
     const uint64_t rows = (uint64_t)pr.G * p.kblocks * pr.N;
-    if (KIND == DG_KIND_W4A8) {
-      const uint64_t dims[2] = {64, rows};
-      const uint64_t strides[1] = {64};
-      const uint32_t box[2] = {64, (uint32_t)BN};
-      rc = encode_map(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.b, dims, strides, box,
-                      CU_TENSOR_MAP_SWIZZLE_NONE);
-    } else {
-      const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
-      const uint64_t strides[1] = {(uint64_t)kRowBytes};
-      const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)BN};
-      rc = encode_map(&tm_b, dt_a, 2, pr.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-    }
+    const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
+    const uint64_t strides[1] = {(uint64_t)kRowBytes};
+    const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)BN};
+    rc = encode_map(&tm_b, dt_a, 2, pr.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc != DG_OK) return rc;
 
@@ -320,6 +311,78 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   return DG_OK;
 }
 
+// W4A8: swapped orientation, unpacked weights handed to the UMMA through tensor memory.
+int launch_w4(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
+  using L = W4Smem;
+  auto kernel = grouped_gemm_w4_kernel;
+  KernelParams p{};
+  p.mode = pr.mode;
+  p.scale_mode = pr.scale_mode;
+  p.G = pr.G;
+  p.M = pr.M;
+  p.N = pr.N;
+  p.K = pr.K;
+  p.kblocks = pr.K / 256;  // packed-weight stages per item (two 128-value K blocks each)
+  p.n_tiles = (pr.N + 127) / 128;
+  p.m_blocks = (pr.M + kBM - 1) / kBM;
+  p.sched = pr.sched;
+  p.a_scale = pr.a_scale;
+  p.b_scale = pr.b_scale;
+  p.d = static_cast<__nv_bfloat16*>(pr.d);
+  p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
+  p.status = pr.status;
+  const long long max_items =
+      (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : (long long)p.m_blocks) * p.n_tiles;
+  if (max_items <= 0) return DG_OK;
+  const int table_bytes = (pr.mode == MODE_MASKED) ? (2 * pr.G + 1) * 4 : p.m_blocks * 4;
+  const int smem_bytes = L::total(table_bytes);
+  if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
+
+  CUtensorMap tm_tok, tm_w;
+  int rc;
+  if (pr.mode == MODE_MASKED) {
+    const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
+    const uint64_t strides[2] = {(uint64_t)pr.K, (uint64_t)pr.M * pr.K};
+    const uint32_t box[3] = {128u, 128u, 1u};
+    rc = encode_map(&tm_tok, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, pr.a, dims, strides, box,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
+    const uint64_t strides[1] = {(uint64_t)pr.K};
+    const uint32_t box[2] = {128u, 128u};
+    rc = encode_map(&tm_tok, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.a, dims, strides, box,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc != DG_OK) return rc;
+  {
+    // packed weights: G*(K/256)*N rows of 128 bytes (256 int4 values); a 128-row box is one
+    // contiguous 16 KB span
+    const uint64_t dims[2] = {128, (uint64_t)pr.G * p.kblocks * pr.N};
+    const uint64_t strides[1] = {128};
+    const uint32_t box[2] = {128u, 128u};
+    rc = encode_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.b, dims, strides, box,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc != DG_OK) return rc;
+
+  static std::atomic<unsigned long long> configured{0};
+  int devid = 0;
+  cudaGetDevice(&devid);
+  const unsigned long long bit = 1ull << (devid & 63);
+  if ((configured.load(std::memory_order_acquire) & bit) == 0) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    if (e != cudaSuccess) return cuda_fail(e);
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  const int grid = static_cast<int>(max_items < dev.sm_count ? max_items : dev.sm_count);
+  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_tok, tm_w, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int validate_and_launch(const Problem& pr, cudaStream_t stream) {
@@ -331,7 +394,7 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
   if (pr.G > DG_MAX_GROUPS) return DG_ERR_TOO_LARGE;
   if (pr.mode == MODE_CONTIG && pr.M > DG_MAX_CONTIG_ROWS) return DG_ERR_TOO_LARGE;
   if (pr.N % 16 != 0) return DG_ERR_BAD_SHAPE;
-  const int kq = (pr.kind == DG_KIND_BF16) ? 64 : 128;
+  const int kq = (pr.kind == DG_KIND_BF16) ? 64 : (pr.kind == DG_KIND_W4A8 ? 256 : 128);
   if (pr.K % kq != 0) return DG_ERR_BAD_SHAPE;
   if ((long long)pr.G * (pr.K / kq) * pr.N > 0x7fffffffLL) return DG_ERR_TOO_LARGE;
   if (pr.M == 0) return DG_OK;
@@ -365,8 +428,8 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
     else
       bn = (pr.expected_m > 256 && pr.N >= 256) ? 256 : 128;
   }
-  if (pr.kind == DG_KIND_W4A8) bn = 128;
   if (bn == 512 && pr.N < 256) bn = 128;
+  if (pr.kind == DG_KIND_W4A8) return launch_w4(pr, *dev, stream);
 
   if (bn == 512) {  // two-CTA 256x256 tiles
     switch (pr.kind) {
@@ -386,8 +449,8 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
     case DG_KIND_BF16:
       return bn == 256 ? launch<DG_KIND_BF16, 256>(pr, *dev, stream)
                        : launch<DG_KIND_BF16, 128>(pr, *dev, stream);
-    case DG_KIND_W4A8:
-      return launch<DG_KIND_W4A8, 128>(pr, *dev, stream);
+    default:
+      break;
   }
   return DG_ERR_BAD_KIND;
 }
@@ -447,7 +510,7 @@ static int pack_common(bool unpack, int32_t kind, const void* src, void* dst, in
   if (kind < DG_KIND_I8 || kind > DG_KIND_BF16) return DG_ERR_BAD_KIND;
   if (!src || !dst) return DG_ERR_NULL_POINTER;
   if (G < 1 || n < 1 || k < 1) return DG_ERR_BAD_SHAPE;
-  const int kq = (kind == DG_KIND_BF16) ? 64 : 128;
+  const int kq = (kind == DG_KIND_BF16) ? 64 : (kind == DG_KIND_W4A8 ? 256 : 128);
   if (k % kq != 0) return DG_ERR_BAD_SHAPE;
   if (!aligned16(src) || !aligned16(dst)) return DG_ERR_BAD_ALIGNMENT;
   if (nibble_order != DG_NIBBLE_HIGH_FIRST && nibble_order != DG_NIBBLE_LOW_FIRST)
@@ -493,7 +556,7 @@ const char* dg_strerror(int code) {
     case DG_ERR_NULL_POINTER: return "a required pointer is NULL";
     case DG_ERR_BAD_KIND: return "unknown operand kind";
     case DG_ERR_BAD_SHAPE:
-      return "bad shape: need N % 16 == 0, K % 128 == 0 (K % 64 for bf16), groups >= 1";
+      return "bad shape: need N % 16 == 0, K % 128 == 0 (K % 64 for bf16, K % 256 for W4A8), groups >= 1";
     case DG_ERR_BAD_ALIGNMENT: return "a base pointer is not 16-byte aligned";
     case DG_ERR_BAD_SCALE_MODE: return "scale mode does not fit the operand kind";
     case DG_ERR_NO_DEVICE: return "no current CUDA device of compute capability 10.x (B200)";

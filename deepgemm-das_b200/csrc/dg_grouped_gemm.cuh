@@ -16,8 +16,7 @@
 //   warps 2..5  epilogue: tcgen05.ld of the accumulator, scale, bf16 convert, predicated
 //               16-byte stores; overlaps the next item's main loop through the second
 //               TMEM accumulator.
-//   warps 6..9  (W4A8 only) unpack: expand the packed int4 stage to an int8 tile in the
-//               128-byte-swizzled layout the UMMA descriptor expects.
+// (W4A8 has its own kernel, dg_grouped_gemm_w4.cuh.)
 //
 // Every wait on an mbarrier is bounded; on expiry the block records a status word and
 // leaves through the common tear-down path (TMEM is always released).
@@ -25,7 +24,6 @@
 // Semantics follow the reference kernels
 //   csrc/arch/gfx936_gfx938_shared/m_grouped_fp8_gemm_nt_maksed_low_latency.cu:272-604 (masked)
 //   csrc/include/m_grouped_i8_gemm_nt_contiguous/bm128_bn256_bk64_nloop4.inc.cuh:206-652 (contiguous)
-//   csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_masked_hipc.cu:678-963 (W4A8 unpack rule)
 // but none of their structure: those stream operands through registers on wave64 hardware.
 #pragma once
 
@@ -74,18 +72,16 @@ struct KernelParams {
 
 template <int KIND, int BN, int STAGES>
 struct SmemLayout {
-  static constexpr bool kW4 = (KIND == DG_KIND_W4A8);
-  static constexpr int kBBytes = BN * kRowBytes;         // int8/fp8/bf16 weight tile
-  static constexpr int kPBytes = kW4 ? BN * 64 : 0;      // packed int4 weight tile
+  static_assert(KIND != DG_KIND_W4A8, "W4A8 uses grouped_gemm_w4_kernel");
+  static constexpr int kBBytes = BN * kRowBytes;  // weight tile
   static constexpr int off_a = 0;
   static constexpr int off_b = off_a + STAGES * kATileBytes;
-  static constexpr int off_p = off_b + STAGES * kBBytes;
-  static constexpr int off_bar = off_p + STAGES * kPBytes;
-  // full[S], empty[S], unpacked[S], acc_full[2], acc_empty[2], drain
-  static constexpr int kNumBars = 3 * STAGES + 5;
+  static constexpr int off_bar = off_b + STAGES * kBBytes;
+  // full[S], empty[S], acc_full[2], acc_empty[2], drain
+  static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;  // tmem slot, abort, n_items, pad
   static constexpr int off_table = off_misc + 16;
-  static constexpr int kThreads = kW4 ? 320 : 192;
+  static constexpr int kThreads = 192;
   static constexpr int kTmemCols = 2 * BN;
   __host__ __device__ static constexpr int total(int table_bytes) {
     return off_table + table_bytes + 1024;  // + slack to align the base to 1024 bytes
@@ -193,10 +189,9 @@ __global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_b, const KernelParams p) {
   using L = SmemLayout<KIND, BN, STAGES>;
-  constexpr bool kW4 = L::kW4;
   constexpr int kUmmaKind =
       (KIND == DG_KIND_E4M3) ? UMMA_F8F6F4 : (KIND == DG_KIND_BF16 ? UMMA_F16 : UMMA_I8);
-  constexpr bool kIntAcc = (KIND == DG_KIND_I8 || KIND == DG_KIND_W4A8);
+  constexpr bool kIntAcc = (KIND == DG_KIND_I8);
   constexpr int kElemsPerRow = (KIND == DG_KIND_BF16) ? 64 : 128;  // A elements per 128 bytes
   constexpr uint32_t kIdesc =
       umma_idesc(kIntAcc ? 2u : 1u, (KIND == DG_KIND_E4M3) ? 0u : 1u, kBM, BN);
@@ -212,10 +207,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   auto bar_full = [&](int s) { return base + L::off_bar + 8u * s; };
   auto bar_empty = [&](int s) { return base + L::off_bar + 8u * (STAGES + s); };
-  auto bar_unp = [&](int s) { return base + L::off_bar + 8u * (2 * STAGES + s); };
-  auto bar_acc_full = [&](int b) { return base + L::off_bar + 8u * (3 * STAGES + b); };
-  auto bar_acc_empty = [&](int b) { return base + L::off_bar + 8u * (3 * STAGES + 2 + b); };
-  const uint32_t bar_drain = base + L::off_bar + 8u * (3 * STAGES + 4);
+  auto bar_acc_full = [&](int b) { return base + L::off_bar + 8u * (2 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return base + L::off_bar + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t bar_drain = base + L::off_bar + 8u * (2 * STAGES + 4);
 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
@@ -228,7 +222,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
       mbar_init(bar_empty(s), 1);
-      mbar_init(bar_unp(s), 4);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full(b), 1);
@@ -319,15 +312,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_full(s), kATileBytes + (kW4 ? L::kPBytes : L::kBBytes));
+          mbar_arrive_expect_tx(bar_full(s), kATileBytes + L::kBBytes);
           const uint32_t a_dst = base + L::off_a + s * kATileBytes;
           if (p.mode == MODE_MASKED)
             tma_load_3d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, t.g, pol_a);
           else
             tma_load_2d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, pol_a);
-          const uint32_t b_dst =
-              kW4 ? base + L::off_p + s * L::kPBytes : base + L::off_b + s * L::kBBytes;
-          tma_load_2d(b_dst, &tm_b, bar_full(s), 0, b_row0 + kb * p.N, pol_b);
+          tma_load_2d(base + L::off_b + s * L::kBBytes, &tm_b, bar_full(s), 0, b_row0 + kb * p.N,
+                      pol_b);
         }
       }
       // Do not leave while a copy into this block's shared memory is still in flight:
@@ -358,10 +350,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_MMA_FULL)) {
-            ok = false;
-            break;
-          }
-          if (kW4 && !mbar_wait_bounded(bar_unp(s), ph, abort_flag, SITE_MMA_UNPACKED)) {
             ok = false;
             break;
           }
@@ -423,42 +411,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty(buf));
-    }
-  } else {
-    if constexpr (kW4) {
-      // ---- W4A8 unpack: packed stage [BN][64 bytes] -> int8 stage [BN][128 bytes], swizzled.
-      // Byte i of 16-byte chunk j of a packed row carries w[32j+i] (high nibble) and
-      // w[32j+16+i] (low nibble); `& 0xF0` / `<< 4` turn each into the int8 value 16*w, the
-      // reference's rule (m_grouped_w4a8_gemm_nt_masked_hipc.cu:378-381).
-      const int ut = tid - 192;
-      uint32_t it = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_UNPACK_FULL)) {
-            ok = false;
-            break;
-          }
-          const uint4* src = reinterpret_cast<const uint4*>(smem + L::off_p + s * L::kPBytes);
-          uint8_t* dst = smem + L::off_b + s * L::kBBytes;
-#pragma unroll 4
-          for (int i = ut; i < BN * 4; i += 128) {
-            const uint4 v = src[i];
-            const int r = i >> 2, j = i & 3, sw = r & 7;
-            const uint4 hi = make_uint4(v.x & 0xF0F0F0F0u, v.y & 0xF0F0F0F0u, v.z & 0xF0F0F0F0u,
-                                        v.w & 0xF0F0F0F0u);
-            const uint4 lo = make_uint4((v.x << 4) & 0xF0F0F0F0u, (v.y << 4) & 0xF0F0F0F0u,
-                                        (v.z << 4) & 0xF0F0F0F0u, (v.w << 4) & 0xF0F0F0F0u);
-            *reinterpret_cast<uint4*>(dst + r * kRowBytes + (((2 * j) ^ sw) << 4)) = hi;
-            *reinterpret_cast<uint4*>(dst + r * kRowBytes + (((2 * j + 1) ^ sw) << 4)) = lo;
-          }
-          fence_proxy_async_smem();  // generic-proxy writes -> visible to the UMMA (async proxy)
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_unp(s));
-        }
-      }
     }
   }
 

@@ -1,5 +1,5 @@
 // Weight re-layout kernels: row-major [G][N][K] <-> packed [G][K/BK][N][128 bytes]
-// (64 bytes per row and a nibble re-pairing for int4).  One thread moves one 16-byte
+// (plus a nibble re-pairing inside every 16-byte chunk for int4).  One thread moves one 16-byte
 // chunk; the work is a pure byte permutation bound by HBM bandwidth and runs once at
 // model-load time, like the torch re-layout code it replaces
 // (deepgemm/m_group_gemm.py:826-863, deepgemm/group_gemm_weight_pack.py:594-714).
@@ -45,13 +45,12 @@ __device__ __forceinline__ uint4 w4_pair_for_framework(uint4 s, int nibble_order
   return *reinterpret_cast<uint4*>(out);
 }
 
-// chunks_per_row: 16-byte chunks per packed row (8, or 4 for int4); row_bytes: bytes per
-// row-major source row.
+// row_bytes: bytes per row-major source row; every packed row is 128 bytes = 8 chunks.
 template <bool UNPACK, bool W4>
 __global__ void relayout_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                 long long total_chunks, int n, int kblocks, int row_bytes,
                                 int nibble_order) {
-  constexpr int CPR = W4 ? 4 : 8;
+  constexpr int CPR = 8;
   for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < total_chunks;
        c += (long long)gridDim.x * blockDim.x) {
     const int j = static_cast<int>(c % CPR);
@@ -78,7 +77,7 @@ inline cudaError_t launch_pack(bool unpack, int kind, const void* src, void* dst
                                int k, int nibble_order, cudaStream_t stream) {
   const bool w4 = (kind == DG_KIND_W4A8);
   const int row_bytes = (kind == DG_KIND_BF16) ? k * 2 : (w4 ? k / 2 : k);
-  const int kblocks = row_bytes / (w4 ? 64 : 128);
+  const int kblocks = row_bytes / 128;
   const long long total = (long long)G * n * row_bytes / 16;
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;

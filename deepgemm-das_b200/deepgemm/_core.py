@@ -20,8 +20,8 @@ from ._cabi import (KIND_BF16, KIND_E4M3, KIND_I8, KIND_W4A8, SCALE_NONE, SCALE_
 _FP8 = torch.float8_e4m3fn
 
 # bytes of K per packed row, and elements per row, by kind
-_ROW_ELEMS = {KIND_I8: 128, KIND_E4M3: 128, KIND_BF16: 64, KIND_W4A8: 64}
-_K_PER_BLOCK = {KIND_I8: 128, KIND_E4M3: 128, KIND_BF16: 64, KIND_W4A8: 128}
+_ROW_ELEMS = {KIND_I8: 128, KIND_E4M3: 128, KIND_BF16: 64, KIND_W4A8: 128}
+_K_PER_BLOCK = {KIND_I8: 128, KIND_E4M3: 128, KIND_BF16: 64, KIND_W4A8: 256}
 _A_DTYPES = {KIND_I8: (torch.int8,), KIND_E4M3: (_FP8,), KIND_W4A8: (torch.int8,),
              KIND_BF16: (torch.bfloat16,)}
 _B_DTYPES = {KIND_I8: (torch.int8, torch.uint8), KIND_E4M3: (_FP8, torch.int8, torch.uint8),
@@ -38,8 +38,8 @@ def packed_weight_dims(b: torch.Tensor, kind: int, k_hint: Optional[int] = None
                        ) -> Tuple[int, int, int]:
     """(G, N, K) of a packed weight tensor; rejects tensors that do not carry the packed shape.
 
-    Packed weights are 4-D ``[G, K/BK, N, row]`` with row = 128 (8-bit), 64 (bf16 elements, or
-    int4 bytes).  W4A8 weights may also be the 3-D ``[G, N, K/2]`` tensor that the reference's
+    Packed weights are 4-D ``[G, K/BK, N, row]`` with row = 128 (8-bit elements, or int4 bytes
+    holding 256 values) or 64 (bf16 elements).  W4A8 weights may also be the 3-D ``[G, N, K/2]`` tensor that the reference's
     in-place packer returns (deepgemm/group_gemm_weight_pack.py:691-714) -- that shape cannot
     be told apart from an unpacked one, exactly as in the reference.
     """

@@ -9,7 +9,7 @@ marlin / marlin2 / HIPC-N32 family:
     packed[e][kb][n][0:128 bytes] = bytes of row n of expert e covering K block kb
 
 i.e. ``[E, K/128, N, 128]`` for int8 / fp8, ``[E, K/64, N, 64]`` for bf16 and, for int4,
-``[E, K/128, N, 64]`` bytes where byte ``i`` of 16-byte chunk ``j`` holds ``w[32j+i]`` in the
+``[E, K/256, N, 128]`` bytes where byte ``i`` of 16-byte chunk ``j`` holds ``w[32j+i]`` in the
 high and ``w[32j+16+i]`` in the low nibble.  A (K-block, n-range) tile is one contiguous
 span, fetched by a single TMA box.  The ``arch`` / ``mode`` / ``shuffle_unique`` /
 ``low_memory`` arguments selected among Hygon layouts; they are validated like the reference
@@ -108,13 +108,13 @@ def _nibble_order(order) -> int:
 def _torch_pack_rows(rows_u8: torch.Tensor, w4: bool, nibble_order: int) -> torch.Tensor:
     """CPU/any-device twin of dg_pack_weight for one expert: uint8 [N, row_bytes] -> packed."""
     n, row_bytes = rows_u8.shape
-    blk = 64 if w4 else _ROW_BYTES
+    blk = _ROW_BYTES
     x = rows_u8.view(n, row_bytes // blk, blk)
     if w4:
-        x = x.reshape(n, row_bytes // blk, 4, 16)
+        x = x.reshape(n, row_bytes // blk, 8, 16)
         hi, lo = x >> 4, x & 0xF
         first, second = (hi, lo) if nibble_order == NIBBLE_HIGH_FIRST else (lo, hi)
-        w = torch.stack((first, second), dim=-1).reshape(n, row_bytes // blk, 4, 2, 16)
+        w = torch.stack((first, second), dim=-1).reshape(n, row_bytes // blk, 8, 2, 16)
         x = ((w[..., 0, :] << 4) | w[..., 1, :]).reshape(n, row_bytes // blk, blk)
     return x.permute(1, 0, 2).contiguous()
 
@@ -124,8 +124,8 @@ def _torch_unpack_rows(packed_u8: torch.Tensor, w4: bool, nibble_order: int) -> 
     kb, n, blk = packed_u8.shape
     x = packed_u8.permute(1, 0, 2)
     if w4:
-        x = x.reshape(n, kb, 4, 16)
-        w = torch.stack((x >> 4, x & 0xF), dim=-2).reshape(n, kb, 4, 16, 2)  # value index 2t+h
+        x = x.reshape(n, kb, 8, 16)
+        w = torch.stack((x >> 4, x & 0xF), dim=-2).reshape(n, kb, 8, 16, 2)  # value index 2t+h
         first, second = w[..., 0], w[..., 1]
         x = ((first << 4) | second) if nibble_order == NIBBLE_HIGH_FIRST else ((second << 4) | first)
     return x.reshape(n, kb * blk).contiguous()
@@ -142,7 +142,7 @@ def _pack_inplace(weight: torch.Tensor, kind: int, nibble_order: int = NIBBLE_HI
     e, n, last = (int(v) for v in weight.shape)
     w4 = kind == KIND_W4A8
     row_bytes = last * weight.element_size()
-    blk = 64 if w4 else _ROW_BYTES
+    blk = _ROW_BYTES
     kb = row_bytes // blk
     k = last * 2 if w4 else last
     for ei in range(e):
@@ -170,11 +170,11 @@ def unpack_weight(packed: torch.Tensor, kind: int, *, nibble_order="high_first")
     w4 = kind == KIND_W4A8
     if w4 and packed.dim() == 3:
         e, n, kh = (int(v) for v in packed.shape)
-        packed = packed.view(e, kh // 64, n, 64)
+        packed = packed.view(e, kh // 128, n, 128)
     if packed.dim() != 4:
         raise ValueError(f"packed weight must be 4-D [E, KB, N, row], got {tuple(packed.shape)}")
     e, kb, n, row = (int(v) for v in packed.shape)
-    k = kb * (128 if kind != KIND_BF16 else 64)
+    k = kb * {KIND_BF16: 64, KIND_W4A8: 256}.get(kind, 128)
     out = torch.empty((e, n, kb * row), dtype=packed.dtype, device=packed.device)
     if packed.is_cuda:
         src = packed.contiguous()
@@ -325,8 +325,8 @@ def pack_w4a8_moe_hipc_weight_inplace(packed_k_contiguous: torch.Tensor, *,
         packed_k_contiguous = packed_k_contiguous.contiguous()
     original_shape = packed_k_contiguous.shape
     _, n, k_half = (int(v) for v in original_shape)
-    if k_half % 64 != 0:
-        raise ValueError(f"K/2 must be divisible by 64 for the W4A8 tile layout, got {k_half}")
+    if k_half % 128 != 0:
+        raise ValueError(f"K/2 must be divisible by 128 for the W4A8 tile layout, got {k_half}")
     if n % 16 != 0:
         raise ValueError(f"N must be divisible by 16 for the W4A8 tile layout, got {n}")
     _pack_inplace(packed_k_contiguous, KIND_W4A8, _nibble_order(nibble_order))
@@ -340,17 +340,17 @@ def pack_w4a8_moe_hipc_weight(packed_k_contiguous: torch.Tensor, *,
 
 
 def view_w4a8_moe_hipc_weight_n32_layout(packed_hipc_weight: torch.Tensor) -> torch.Tensor:
-    """The packed int4 tensor seen in kernel order ``[E, K/128, N, 64]`` (reference :717-727
+    """The packed int4 tensor seen in kernel order ``[E, K/256, N, 128]`` (reference :717-727
     returned its N32 6-D order)."""
     if packed_hipc_weight.dim() != 3:
         raise ValueError(
             f"packed_hipc_weight must be [E,N,K/2], got shape {tuple(packed_hipc_weight.shape)}")
     experts, n, k_half = (int(v) for v in packed_hipc_weight.shape)
-    if k_half % 64 != 0 or n % 16 != 0:
+    if k_half % 128 != 0 or n % 16 != 0:
         raise ValueError(
             f"packed_hipc_weight shape [E,N,K/2]={tuple(packed_hipc_weight.shape)} must satisfy "
-            "N%16==0 and K/2%64==0")
-    return packed_hipc_weight.view(experts, k_half // 64, n, 64)
+            "N%16==0 and K/2%128==0")
+    return packed_hipc_weight.view(experts, k_half // 128, n, 128)
 
 
 def weight4bit_nt_kpack2_marlin2_qqq_from_packed(packed_w: torch.Tensor) -> torch.Tensor:

@@ -81,10 +81,10 @@ typedef enum dg_status {
  *   packed[g][kb][n][0..127]  =  the 128 bytes of row n of group g that cover
  *                                K-range [kb*BK, (kb+1)*BK)
  *
- * BK = 128 elements for 8-bit kinds, 64 for bf16, 128 int4 values (64 bytes per row)
- * for W4A8.  Each (kb, n-range) tile a thread block needs is one contiguous span, so a
- * single TMA box fetches it.  Same byte count as the row-major [G][N][K] source.
- * For W4A8 each 16-byte chunk j (of 4) of a 64-byte row holds, in byte i, value
+ * BK = 128 elements for 8-bit kinds, 64 for bf16, 256 int4 values for W4A8: every packed
+ * row is 128 bytes.  Each (kb, n-range) tile a thread block needs is one contiguous span, so
+ * a single TMA box fetches it.  Same byte count as the row-major [G][N][K] source.
+ * For W4A8 each 16-byte chunk j (of 8) of a 128-byte row holds, in byte i, value
  * w[32j+i] in the high nibble and w[32j+16+i] in the low nibble (two's-complement
  * nibbles), so that `x & 0xF0` and `(x << 4) & 0xF0` each yield 16 consecutive int8
  * values equal to 16*w.  Replaces the reference's W6 / marlin / HIPC-N32 layouts
@@ -108,7 +108,7 @@ typedef struct dg_masked_args {
   int32_t num_groups;         /* G, 1..DG_MAX_GROUPS */
   int32_t max_m;              /* rows allocated per group */
   int32_t n;                  /* N, multiple of 16 */
-  int32_t k;                  /* K, multiple of 128 (64 for bf16) */
+  int32_t k;                  /* K, multiple of 128 (64 for bf16, 256 for W4A8) */
   int32_t expected_m;         /* hint only: typical masked_m; never limits the rows computed */
   int32_t block_n;            /* 0 = choose; 128 / 256 = one-CTA tile width; 512 = two-CTA 256x256 tiles */
   void*          debug_acc;   /* NULL, or [G][max_m][N] of raw 32-bit accumulators (s32 / f32) */

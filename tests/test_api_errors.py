@@ -94,8 +94,8 @@ def test_unpacked_weights_are_rejected():
 
 
 def test_contiguous_w4a8_shape_errors():
-    a2 = (torch.zeros(8, 128, dtype=torch.int8), torch.ones(8))
-    bw = (torch.zeros(2, 32, 64, dtype=torch.int8), torch.ones(2, 32))
+    a2 = (torch.zeros(8, 256, dtype=torch.int8), torch.ones(8))
+    bw = (torch.zeros(2, 32, 128, dtype=torch.int8), torch.ones(2, 32))
     out = torch.zeros(8, 32, dtype=torch.bfloat16)
     mi = torch.zeros(8, dtype=torch.int32)
     with pytest.raises(ValueError, match=r"\[M,K\]"):

@@ -64,7 +64,8 @@ def test_calls_validate_before_touching_the_device():
     assert _cabi.lib.dg_pack_weight(7, 16, 32, 1, 16, 128, 0, None) == -2
     assert _cabi.lib.dg_pack_weight(0, 16, 32, 1, 16, 100, 0, None) == -3
     assert _cabi.lib.dg_pack_weight(0, 17, 32, 1, 16, 128, 0, None) == -4
-    assert _cabi.lib.dg_pack_weight(2, 16, 32, 1, 16, 128, 5, None) == -9
+    assert _cabi.lib.dg_pack_weight(2, 16, 32, 1, 16, 128, 0, None) == -3   # int4 needs K % 256
+    assert _cabi.lib.dg_pack_weight(2, 16, 32, 1, 16, 256, 5, None) == -9
 
 
 def test_missing_library_is_a_loud_import_error(tmp_path, monkeypatch):

@@ -35,7 +35,7 @@ def test_gpu_pack_matches_cpu_pack_bf16_and_int4():
     assert torch.equal(gpu.cpu().view(torch.int16), cpu.view(torch.int16))
     assert torch.equal(P.unpack_weight(gpu, _cabi.KIND_BF16).cpu().view(torch.int16), w.view(torch.int16))
     for order in ("high_first", "low_first"):
-        fw = torch.randint(-128, 128, (3, 48, 192), dtype=torch.int8)
+        fw = torch.randint(-128, 128, (3, 48, 384), dtype=torch.int8)
         cpu = P.pack_w4a8_moe_hipc_weight(fw.clone(), nibble_order=order)
         gpu = P.pack_w4a8_moe_hipc_weight(fw.clone().to(DEV), nibble_order=order)
         assert torch.equal(gpu.cpu(), cpu)

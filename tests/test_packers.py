@@ -49,7 +49,7 @@ def test_bf16_pack_returns_config_and_inverts():
 @pytest.mark.parametrize("order", ["high_first", "low_first"])
 def test_int4_layout_pairs_nibbles_for_the_unpack_rule(order):
     g = torch.Generator().manual_seed(3)
-    u4 = torch.randint(0, 16, (2, 32, 256), generator=g).to(torch.int8)
+    u4 = torch.randint(0, 16, (2, 32, 512), generator=g).to(torch.int8)
     fw = P.pack_w4a8_weight_k_contiguous(u4)          # high nibble = even k
     if order == "low_first":
         b = fw.view(torch.uint8)
@@ -58,12 +58,12 @@ def test_int4_layout_pairs_nibbles_for_the_unpack_rule(order):
     pk = P.pack_w4a8_moe_hipc_weight(fw, nibble_order=order)
     assert pk.shape == fw0.shape and pk.data_ptr() == fw.data_ptr()
     v = P.view_w4a8_moe_hipc_weight_n32_layout(pk).view(torch.uint8)
-    assert v.shape == (2, 2, 32, 64)
+    assert v.shape == (2, 2, 32, 128)
     # applying the kernel's two-instruction unpack to the packed bytes must give 16 x w in K order
-    hi = (v & 0xF0).view(2, 2, 32, 4, 16)
-    lo = ((v << 4) & 0xF0).view(2, 2, 32, 4, 16)
-    int8_tile = torch.stack((hi, lo), dim=-2).reshape(2, 2, 32, 128)      # [e][kb][n][k in block]
-    k_major = int8_tile.permute(0, 2, 1, 3).reshape(2, 32, 256).view(torch.int8)
+    hi = (v & 0xF0).view(2, 2, 32, 8, 16)
+    lo = ((v << 4) & 0xF0).view(2, 2, 32, 8, 16)
+    int8_tile = torch.stack((hi, lo), dim=-2).reshape(2, 2, 32, 256)      # [e][kb][n][k in block]
+    k_major = int8_tile.permute(0, 2, 1, 3).reshape(2, 32, 512).view(torch.int8)
     assert torch.equal(k_major.to(torch.int16), O.signed_int4(u4).to(torch.int16) * 16)
     assert torch.equal(k_major, O.unpack_int4_to_int8_x16(fw0, order))
     assert torch.equal(P.unpack_weight(pk, _cabi.KIND_W4A8, nibble_order=order), fw0)
@@ -93,10 +93,10 @@ def test_packer_argument_errors():
     with pytest.raises(ValueError):
         P.pack_w4a8_weight_k_contiguous(torch.zeros(2, 32, 7, dtype=torch.int8))
     with pytest.raises(ValueError):
-        P.pack_w4a8_moe_hipc_weight(torch.zeros(2, 32, 32, dtype=torch.int8))      # K/2 % 64
+        P.pack_w4a8_moe_hipc_weight(torch.zeros(2, 32, 64, dtype=torch.int8))      # K/2 % 128
     with pytest.raises(ValueError):
-        P.pack_w4a8_moe_hipc_weight(torch.zeros(2, 32, 64, dtype=torch.int16))
+        P.pack_w4a8_moe_hipc_weight(torch.zeros(2, 32, 128, dtype=torch.int16))
     with pytest.raises(ValueError):
-        P.pack_w4a8_moe_hipc_weight(torch.zeros(2, 32, 64, dtype=torch.int8), nibble_order="middle")
+        P.pack_w4a8_moe_hipc_weight(torch.zeros(2, 32, 128, dtype=torch.int8), nibble_order="middle")
     with pytest.raises(ValueError):
         P.view_w4a8_moe_hipc_weight_n32_layout(torch.zeros(32, 64, dtype=torch.int8))
