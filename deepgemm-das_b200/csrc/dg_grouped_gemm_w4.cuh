@@ -36,12 +36,13 @@ constexpr int kW4Rounds = 4;    // token stages = TMEM weight slots
 constexpr int kW4TmemCols = 512;
 constexpr int kW4AccCols = 128;
 constexpr int kW4SlotBase = 256;
-// The unpack role is instruction-latency bound with one warp per scheduler, so it has two
-// groups of four warps that alternate rounds.
+// The unpack and epilogue roles are instruction-latency bound with one warp per scheduler, so
+// each has two groups of four warps: unpack groups alternate rounds, epilogue groups alternate
+// work items (group e owns accumulator e).
 constexpr int kW4Groups = 2;
-constexpr int kW4EpiWarp0 = 2;                            // warps 2..5
-constexpr int kW4UnpWarp0 = kW4EpiWarp0 + 4;              // warps 6..13
-constexpr int kW4TokWarp = kW4UnpWarp0 + 4 * kW4Groups;   // warp 14
+constexpr int kW4EpiWarp0 = 2;                            // warps 2..9
+constexpr int kW4UnpWarp0 = kW4EpiWarp0 + 4 * kW4Groups;  // warps 10..17
+constexpr int kW4TokWarp = kW4UnpWarp0 + 4 * kW4Groups;   // warp 18
 
 enum : int { SITE_W4_WEMPTY = 8, SITE_W4_TEMPTY = 9, SITE_W4_SLOT_EMPTY = 10 };
 
@@ -278,45 +279,59 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
       }
     }
   } else if (warp < kW4UnpWarp0) {
-    // ---- epilogue: thread = one output channel (TMEM lane), columns = tokens
+    // ---- epilogue: thread = one output channel (TMEM lane), columns = tokens; this warp's
+    // group handles every second item of the block (the ones accumulated in its buffer)
     const int q = warp & 3;
+    const uint32_t group = static_cast<uint32_t>(warp - kW4EpiWarp0) >> 2;
     ItemDecoder dec(p, tbl, 128);
     uint32_t tile = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
       const uint32_t buf = tile & 1u;
+      if (buf != group) continue;
       const TileCoord t = dec.get(item);
       const uint32_t aph = (tile >> 1) & 1u;
-      if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
-      tc_fence_after_sync();
+      // Everything that depends only on the item's coordinates is fetched before waiting for
+      // the accumulator, so that the global-load latency hides behind the main loop: this
+      // channel's weight scale, and (lane l) the activation scale and validity of tokens
+      // l, 32+l, 64+l, 96+l.
       const int chan = t.n0 + q * 32 + lane;
       const bool chan_ok = chan < p.N;
       const float bs = !chan_ok ? 0.0f
                        : (p.scale_mode == DG_SCALE_TENSOR_WISE ? p.b_scale[t.g]
                                                                 : p.b_scale[(size_t)t.g * p.N + chan]);
       const size_t row_base = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0;
-      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kW4AccCols;
-#pragma unroll 1
-      for (int t0 = 0; t0 < t.rows_valid; t0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_lane + t0, r);
-        // lane l fetches the scale (and, contiguous layout, the validity) of token t0 + l
-        float as_l = 0.0f;
-        bool tok_ok_l = false;
-        if (t0 + lane < t.rows_valid) {
-          const size_t row = row_base + t0 + lane;
-          tok_ok_l = (p.mode == MODE_MASKED) || (p.sched[row] >= 0);
-          as_l = p.a_scale[row];
-        }
-        const unsigned tok_mask = __ballot_sync(0xffffffffu, tok_ok_l);
-        tmem_ld_wait();
+      float as_l[4];
+      unsigned tok_mask[4];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float as_j = __shfl_sync(0xffffffffu, as_l, j);
-          if (((tok_mask >> j) & 1u) && chan_ok) {
-            const size_t o = (row_base + t0 + j) * p.N + chan;
-            const float v = (__int2float_rn(static_cast<int>(r[j])) * as_j) * bs;
-            p.d[o] = __float2bfloat16_rn(v);
-            if (p.debug_acc != nullptr) p.debug_acc[o] = r[j];
+      for (int c = 0; c < 4; ++c) {
+        bool okl = false;
+        as_l[c] = 0.0f;
+        if (c * 32 + lane < t.rows_valid) {
+          const size_t row = row_base + c * 32 + lane;
+          okl = (p.mode == MODE_MASKED) || (p.sched[row] >= 0);
+          as_l[c] = p.a_scale[row];
+        }
+        tok_mask[c] = __ballot_sync(0xffffffffu, okl);
+      }
+      if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
+      tc_fence_after_sync();
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kW4AccCols;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (c * 32 < t.rows_valid) {  // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(t_lane + c * 32, r);
+          tmem_ld_wait();
+          __nv_bfloat16* d_col = p.d + (row_base + c * 32) * p.N + chan;
+          uint32_t* dbg_col = p.debug_acc + (row_base + c * 32) * p.N + chan;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float as_j = __shfl_sync(0xffffffffu, as_l[c], j);
+            if (((tok_mask[c] >> j) & 1u) && chan_ok) {
+              const float v = (__int2float_rn(static_cast<int>(r[j])) * as_j) * bs;
+              d_col[(size_t)j * p.N] = __float2bfloat16_rn(v);
+              if (p.debug_acc != nullptr) dbg_col[(size_t)j * p.N] = r[j];
+            }
           }
         }
       }
