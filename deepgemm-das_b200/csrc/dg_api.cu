@@ -11,6 +11,7 @@
 #include "dg_grouped_gemm_pair.cuh"
 #include "dg_grouped_gemm_w4.cuh"
 #include "dg_pack.cuh"
+#include "dg_quant_group.cuh"
 
 namespace {
 
@@ -533,6 +534,56 @@ int dg_pack_weight(int32_t kind, const void* src, void* dst, int32_t G, int32_t 
 int dg_unpack_weight(int32_t kind, const void* src, void* dst, int32_t G, int32_t n, int32_t k,
                      int32_t nibble_order, void* stream) {
   return pack_common(true, kind, src, dst, G, n, k, nibble_order, stream);
+}
+
+size_t dg_quant_group_scratch_bytes(int32_t num_rows, int32_t num_groups) {
+  if (num_rows < 0 || num_groups < 1 || num_groups > DG_MAX_GROUPS) return 0;
+  const size_t chunks = (static_cast<size_t>(num_rows) + dg::kQgChunk - 1) / dg::kQgChunk;
+  return (chunks * num_groups + num_groups) * sizeof(int32_t) + 256;
+}
+
+// Shared by dg_quant_group_rows and its variant with library-owned scratch.
+static int quant_group_common(const dg_quant_group_args* a, int32_t* scratch, void* stream) {
+  if (a->kind != DG_KIND_E4M3 && a->kind != DG_KIND_I8) return DG_ERR_BAD_KIND;
+  if (a->num_rows < 0 || a->hidden < 8 || a->hidden % 8 != 0 || a->num_groups < 1 ||
+      a->align < 1 || a->m_cap < 0)
+    return DG_ERR_BAD_SHAPE;
+  if (a->num_groups > DG_MAX_GROUPS || a->hidden > DG_MAX_QUANT_HIDDEN) return DG_ERR_TOO_LARGE;
+  if (!a->a_out || !a->a_scale_out || !a->m_indices_out || !scratch) return DG_ERR_NULL_POINTER;
+  if (a->num_rows > 0 && (!a->rows || !a->expert)) return DG_ERR_NULL_POINTER;
+  if (!aligned16(a->rows) || !aligned16(a->a_out) || !aligned16(scratch)) return DG_ERR_BAD_ALIGNMENT;
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != DG_OK) return rc;
+  dg::QuantGroupParams p{};
+  p.rows = static_cast<const __nv_bfloat16*>(a->rows);
+  p.expert = a->expert;
+  p.a_out = a->a_out;
+  p.a_scale_out = a->a_scale_out;
+  p.m_indices_out = a->m_indices_out;
+  p.dest_out = a->dest_out;
+  p.m_total_out = a->m_total_out;
+  p.R = a->num_rows;
+  p.H = a->hidden;
+  p.G = a->num_groups;
+  p.align = a->align;
+  p.m_cap = a->m_cap;
+  p.chunks = (a->num_rows + dg::kQgChunk - 1) / dg::kQgChunk;
+  p.kind = a->kind;
+  p.hist = scratch;
+  p.starts = scratch + static_cast<size_t>(p.chunks) * p.G;
+  cudaError_t e = dg::launch_quant_group(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(a->num_rows > 0 ? 4 : 1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
+int dg_quant_group_rows(const dg_quant_group_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->num_groups >= 1 && a->num_groups <= DG_MAX_GROUPS && a->num_rows >= 0 &&
+      a->scratch_bytes < dg_quant_group_scratch_bytes(a->num_rows, a->num_groups))
+    return DG_ERR_BAD_ARGUMENT;
+  return quant_group_common(a, static_cast<int32_t*>(a->scratch), stream);
 }
 
 int64_t dg_query(int32_t what) {

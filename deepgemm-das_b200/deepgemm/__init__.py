@@ -56,4 +56,6 @@ from .m_group_gemm_nt_masked import (
     m_grouped_w8a8_gemm_nt_masked_impl,
 )
 
+from .quant_group import quant_group_capacity, quantize_group_rows
+
 __version__ = "0.1.0"

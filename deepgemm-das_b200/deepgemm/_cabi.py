@@ -22,6 +22,8 @@ ERR_CUDA = -7
 EXPORTED_SYMBOLS = (
     "dg_masked_gemm",
     "dg_contig_gemm",
+    "dg_quant_group_rows",
+    "dg_quant_group_scratch_bytes",
     "dg_pack_weight",
     "dg_unpack_weight",
     "dg_query",
@@ -72,6 +74,26 @@ class ContigArgs(C.Structure):
     ]
 
 
+class QuantGroupArgs(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("num_rows", C.c_int32),
+        ("hidden", C.c_int32),
+        ("num_groups", C.c_int32),
+        ("align", C.c_int32),
+        ("m_cap", C.c_int32),
+        ("rows", C.c_void_p),
+        ("expert", C.c_void_p),
+        ("a_out", C.c_void_p),
+        ("a_scale_out", C.c_void_p),
+        ("m_indices_out", C.c_void_p),
+        ("dest_out", C.c_void_p),
+        ("m_total_out", C.c_void_p),
+        ("scratch", C.c_void_p),
+        ("scratch_bytes", C.c_size_t),
+    ]
+
+
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -88,6 +110,10 @@ def _load() -> C.CDLL:
         fn.argtypes = [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                        C.c_int32, C.c_void_p]
         fn.restype = C.c_int
+    lib.dg_quant_group_rows.argtypes = [C.POINTER(QuantGroupArgs), C.c_void_p]
+    lib.dg_quant_group_rows.restype = C.c_int
+    lib.dg_quant_group_scratch_bytes.argtypes = [C.c_int32, C.c_int32]
+    lib.dg_quant_group_scratch_bytes.restype = C.c_size_t
     lib.dg_query.argtypes = [C.c_int32]
     lib.dg_query.restype = C.c_int64
     lib.dg_strerror.argtypes = [C.c_int]

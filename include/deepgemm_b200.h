@@ -184,6 +184,43 @@ DG_API int dg_pack_weight(int32_t kind, const void* src, void* dst, int32_t num_
 DG_API int dg_unpack_weight(int32_t kind, const void* src, void* dst, int32_t num_groups, int32_t n,
                      int32_t k, int32_t nibble_order, void* stream);
 
+/* Arguments of the producer that feeds dg_contig_gemm: per-token quantisation of bf16 rows
+ * fused with grouping the rows by expert, each expert's block padded to `align` rows.
+ *   a_out[dest[r]][:] = quantise(rows[r][:]),  a_scale_out[dest[r]] = absmax(rows[r]) / qmax,
+ *   m_indices_out[i]  = expert of the row stored at i, -1 for every other i in [0, m_cap)
+ * Rows keep their input order inside an expert.  Rows with expert[r] outside [0, num_groups)
+ * or that would land beyond m_cap are dropped (dest -1).  m_cap >= num_rows + num_groups *
+ * (align - 1) always fits everything.  Nothing is returned to the host: launch the GEMM on
+ * m_cap rows, it skips blocks whose first m_indices entry is -1. */
+typedef struct dg_quant_group_args {
+  int32_t kind;              /* element type of a_out: DG_KIND_E4M3 (qmax 448) or DG_KIND_I8 (qmax 127) */
+  int32_t num_rows;          /* R */
+  int32_t hidden;            /* H, multiple of 8, <= DG_MAX_QUANT_HIDDEN */
+  int32_t num_groups;        /* 1..DG_MAX_GROUPS */
+  int32_t align;             /* block alignment of each expert's rows, e.g. 256 */
+  int32_t m_cap;             /* rows allocated in a_out / a_scale_out / m_indices_out */
+  const void*    rows;       /* [R][H] bf16 */
+  const int32_t* expert;     /* [R] group of each row */
+  void*          a_out;      /* [m_cap][H] e4m3 or int8 */
+  float*         a_scale_out;   /* [m_cap] */
+  int32_t*       m_indices_out; /* [m_cap] */
+  int32_t*       dest_out;      /* NULL, or [R] output row of each input row (-1 = dropped) */
+  int32_t*       m_total_out;   /* NULL, or one int: rows in use (multiple of align, <= m_cap) */
+  void*          scratch;       /* device scratch of dg_quant_group_scratch_bytes() bytes */
+  size_t         scratch_bytes;
+} dg_quant_group_args;
+
+#define DG_MAX_QUANT_HIDDEN 16384
+
+/* Scratch bytes dg_quant_group_rows needs for the given problem (0 on bad arguments). */
+DG_API size_t dg_quant_group_scratch_bytes(int32_t num_rows, int32_t num_groups);
+
+/* Quantise + group + pad (four small launches on `stream`).  The reference has no kernel for
+ * this step: its callers and tests do it with framework tensor ops
+ * (op_test/contiguous_w8a8_int8_common.py:38-62 builds the layout, op_test/quant_utils.py:4-19
+ * quantises); the arithmetic of the latter is reproduced bit for bit. */
+DG_API int dg_quant_group_rows(const dg_quant_group_args* args, void* stream);
+
 /* dg_query() selectors. */
 #define DG_QUERY_ABI_VERSION   0
 #define DG_QUERY_SM_COUNT      1 /* multiprocessors of the current device (cached per device) */
