@@ -586,6 +586,42 @@ int dg_quant_group_rows(const dg_quant_group_args* a, void* stream) {
   return quant_group_common(a, static_cast<int32_t*>(a->scratch), stream);
 }
 
+// ---- library-owned scratch for dg_quant_group_rows_noalloc.  In host code the array's name
+// is only a handle: its device address is looked up once per device with
+// cudaGetSymbolAddress and that pointer is what the kernels receive.
+static __device__ __align__(256) int32_t g_noalloc_scratch[DG_NOALLOC_MAX_SCRATCH_INTS];
+static std::mutex g_noalloc_mu;
+static int32_t* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+int dg_quant_group_rows_noalloc(const dg_quant_group_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->num_rows < 0 || a->num_groups < 1) return DG_ERR_BAD_SHAPE;
+  if (a->num_groups > DG_MAX_GROUPS) return DG_ERR_TOO_LARGE;
+  const long long chunks = (static_cast<long long>(a->num_rows) + dg::kQgChunk - 1) / dg::kQgChunk;
+  if (chunks * a->num_groups + a->num_groups > static_cast<long long>(DG_NOALLOC_MAX_SCRATCH_INTS))
+    return DG_ERR_TOO_LARGE;  // does not fit the built-in scratch array
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    tl_last_cuda_error = static_cast<int>(e);
+    (void)cudaGetLastError();
+    return DG_ERR_NO_DEVICE;
+  }
+  if (dev < 0 || dev >= kMaxDevices) return DG_ERR_NO_DEVICE;
+  int32_t* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {  // first call on this device (which is current)
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (e != cudaSuccess) return cuda_fail(e);
+      g_noalloc_ptr[dev] = static_cast<int32_t*>(ptr);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  return quant_group_common(a, scratch, stream);
+}
+
 int64_t dg_query(int32_t what) {
   if (what == DG_QUERY_ABI_VERSION) return DG_ABI_VERSION;
   if (what == DG_QUERY_LAUNCH_COUNT) return g_launch_count.load(std::memory_order_relaxed);

@@ -16,6 +16,7 @@ KIND_I8, KIND_E4M3, KIND_W4A8, KIND_BF16 = 0, 1, 2, 3
 SCALE_PER_CHANNEL, SCALE_TENSOR_WISE, SCALE_NONE = 0, 1, 2
 NIBBLE_HIGH_FIRST, NIBBLE_LOW_FIRST = 0, 1
 STATUS_WORDS = 4
+NOALLOC_MAX_SCRATCH_INTS = 262144 + 1024
 QUERY_ABI_VERSION, QUERY_SM_COUNT, QUERY_MAX_SMEM, QUERY_CC, QUERY_LAUNCH_COUNT = 0, 1, 2, 3, 4
 ERR_CUDA = -7
 
@@ -24,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "dg_contig_gemm",
     "dg_quant_group_rows",
     "dg_quant_group_scratch_bytes",
+    "dg_quant_group_rows_noalloc",
     "dg_pack_weight",
     "dg_unpack_weight",
     "dg_query",
@@ -112,6 +114,8 @@ def _load() -> C.CDLL:
         fn.restype = C.c_int
     lib.dg_quant_group_rows.argtypes = [C.POINTER(QuantGroupArgs), C.c_void_p]
     lib.dg_quant_group_rows.restype = C.c_int
+    lib.dg_quant_group_rows_noalloc.argtypes = [C.POINTER(QuantGroupArgs), C.c_void_p]
+    lib.dg_quant_group_rows_noalloc.restype = C.c_int
     lib.dg_quant_group_scratch_bytes.argtypes = [C.c_int32, C.c_int32]
     lib.dg_quant_group_scratch_bytes.restype = C.c_size_t
     lib.dg_query.argtypes = [C.c_int32]

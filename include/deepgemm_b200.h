@@ -221,6 +221,28 @@ DG_API size_t dg_quant_group_scratch_bytes(int32_t num_rows, int32_t num_groups)
  * quantises); the arithmetic of the latter is reproduced bit for bit. */
 DG_API int dg_quant_group_rows(const dg_quant_group_args* args, void* stream);
 
+/* Same operation as dg_quant_group_rows, for callers that may not allocate device memory at
+ * all: code that runs inside a serving engine after its memory pool has been frozen, plugins
+ * that are handed fixed buffers by a host framework, or anything that must not disturb a
+ * caching allocator.  Such callers cannot provide the scratch buffer either, so this entry
+ * point keeps it inside the library: a fixed array that lives in every GPU that loads the
+ * library, for as long as the process runs.  `scratch` and `scratch_bytes` of the argument
+ * struct are ignored; inputs and outputs are still the caller's.  The call itself never
+ * allocates or frees anything, on the host or on the device.
+ *
+ * Limit: ceil(num_rows / 32) * num_groups + num_groups <= DG_NOALLOC_MAX_SCRATCH_INTS
+ * (about 1 MiB of scratch; e.g. 32768 rows x 256 groups, or 65536 rows x 127 groups).
+ * Larger problems return DG_ERR_TOO_LARGE and launch nothing.
+ * The first call on each device looks up the array's device address (once, with that device
+ * current); make that first call outside any CUDA stream capture.
+ * All calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ * (different streams without an ordering between them) race on it.  Calls on one stream are
+ * safe; the kernels re-initialise every scratch word they read, so nothing needs clearing
+ * between calls.
+ * This function has no counterpart in the reference. */
+#define DG_NOALLOC_MAX_SCRATCH_INTS (262144 + 1024)
+DG_API int dg_quant_group_rows_noalloc(const dg_quant_group_args* args, void* stream);
+
 /* dg_query() selectors. */
 #define DG_QUERY_ABI_VERSION   0
 #define DG_QUERY_SM_COUNT      1 /* multiprocessors of the current device (cached per device) */
