@@ -35,7 +35,7 @@ import torch  # noqa: E402
 # 8-expert case summarised in profiles/grouped_gemm_e4m3_bn128_masked_fp8_decode.md
 # (246.03 MB per launch); traffic grows in proportion to the number of experts.
 NCU_DECODE_DRAM_BYTES_PER_EXPERT = 246.03e6 / 8
-PREHEAT_S = 0.5
+PREHEAT_S = 0.1
 METRIC = "masked_fp8_decode_hbm_bandwidth"
 UNIT = "GB/s"
 C2 = dict(G=32, K=7168, N=4096, max_m=128, tokens=256, top_k=8)

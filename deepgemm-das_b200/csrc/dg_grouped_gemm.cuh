@@ -9,7 +9,9 @@
 // Roles inside a block
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A tile
 //               (128 rows x 128 bytes of K) and the weight tile (BN rows x 128 bytes of K,
-//               one contiguous span of the packed weight) into a STAGES-deep ring.
+//               one contiguous span of the packed weight) into a STAGES-deep ring; a stage
+//               holds KPS consecutive K blocks (one wait and one commit of the UMMA thread
+//               per stage).
 //   warp 1      UMMA issuer: one lane issues four tcgen05.mma (K = 32 bytes each) per
 //               ring stage into one of two TMEM accumulators (128 lanes x BN columns),
 //               and owns TMEM allocation.
@@ -70,13 +72,15 @@ struct KernelParams {
   int32_t* status;
 };
 
-template <int KIND, int BN, int STAGES>
+template <int KIND, int BN, int STAGES, int KPS = 1>
 struct SmemLayout {
   static_assert(KIND != DG_KIND_W4A8, "W4A8 uses grouped_gemm_w4_kernel");
-  static constexpr int kBBytes = BN * kRowBytes;  // weight tile
+  static constexpr int kBBytes = BN * kRowBytes;  // weight tile of one K block
+  static constexpr int kAStage = KPS * kATileBytes;
+  static constexpr int kBStage = KPS * kBBytes;
   static constexpr int off_a = 0;
-  static constexpr int off_b = off_a + STAGES * kATileBytes;
-  static constexpr int off_bar = off_b + STAGES * kBBytes;
+  static constexpr int off_b = off_a + STAGES * kAStage;
+  static constexpr int off_bar = off_b + STAGES * kBStage;
   // full[S], empty[S], acc_full[2], acc_empty[2], drain
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;  // tmem slot, abort, n_items, pad
@@ -184,11 +188,11 @@ struct ItemDecoder {
   }
 };
 
-template <int KIND, int BN, int STAGES>
-__global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads, 1)
+template <int KIND, int BN, int STAGES, int KPS>
+__global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES, KPS>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_b, const KernelParams p) {
-  using L = SmemLayout<KIND, BN, STAGES>;
+  using L = SmemLayout<KIND, BN, STAGES, KPS>;
   constexpr int kUmmaKind =
       (KIND == DG_KIND_E4M3) ? UMMA_F8F6F4 : (KIND == DG_KIND_BF16 ? UMMA_F16 : UMMA_I8);
   constexpr bool kIntAcc = (KIND == DG_KIND_I8);
@@ -305,21 +309,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
         const TileCoord t = dec.get(item);
         const int b_row0 = t.g * p.kblocks * p.N + t.n0;
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        for (int kb0 = 0; kb0 < p.kblocks; kb0 += KPS, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_full(s), kATileBytes + L::kBBytes);
-          const uint32_t a_dst = base + L::off_a + s * kATileBytes;
-          if (p.mode == MODE_MASKED)
-            tma_load_3d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, t.g, pol_a);
-          else
-            tma_load_2d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, pol_a);
-          tma_load_2d(base + L::off_b + s * L::kBBytes, &tm_b, bar_full(s), 0, b_row0 + kb * p.N,
-                      pol_b);
+          const int nb = min(KPS, p.kblocks - kb0);
+          mbar_arrive_expect_tx(bar_full(s), nb * (kATileBytes + L::kBBytes));
+#pragma unroll
+          for (int j = 0; j < KPS; ++j) {
+            if (j < nb) {
+              const int kb = kb0 + j;
+              const uint32_t a_dst = base + L::off_a + s * L::kAStage + j * kATileBytes;
+              if (p.mode == MODE_MASKED)
+                tma_load_3d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, t.g, pol_a);
+              else
+                tma_load_2d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, pol_a);
+              tma_load_2d(base + L::off_b + s * L::kBStage + j * L::kBBytes, &tm_b, bar_full(s), 0,
+                          b_row0 + kb * p.N, pol_b);
+            }
+          }
         }
       }
       // Do not leave while a copy into this block's shared memory is still in flight:
@@ -346,7 +357,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        for (int kb0 = 0; kb0 < p.kblocks; kb0 += KPS, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_MMA_FULL)) {
@@ -354,13 +365,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             break;
           }
           tc_fence_after_sync();
-          const uint64_t a_desc = umma_desc_sw128(base + L::off_a + s * kATileBytes);
-          const uint64_t b_desc = umma_desc_sw128(base + L::off_b + s * L::kBBytes);
+          const int nb = min(KPS, p.kblocks - kb0);
 #pragma unroll
-          for (int k = 0; k < kRowBytes / 32; ++k) {
-            // +2 in the start-address field = +32 bytes along K inside the swizzled row
-            umma_ss<kUmmaKind>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc,
-                               (kb | k) != 0 ? 1u : 0u);
+          for (int j = 0; j < KPS; ++j) {
+            if (j < nb) {
+              const uint64_t a_desc = umma_desc_sw128(base + L::off_a + s * L::kAStage + j * kATileBytes);
+              const uint64_t b_desc = umma_desc_sw128(base + L::off_b + s * L::kBStage + j * L::kBBytes);
+#pragma unroll
+              for (int k = 0; k < kRowBytes / 32; ++k) {
+                // +2 in the start-address field = +32 bytes along K inside the swizzled row
+                umma_ss<kUmmaKind>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc,
+                                   (kb0 | j | k) != 0 ? 1u : 0u);
+              }
+            }
           }
           umma_commit(bar_empty(s));  // frees the stage once these UMMAs have read it
         }
