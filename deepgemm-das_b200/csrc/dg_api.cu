@@ -130,6 +130,7 @@ struct Problem {
   const float* a_scale;
   const float* b_scale;
   const int32_t* sched;
+  const int32_t* offsets;
   int G, M, N, K, block_n, expected_m;
   void* debug_acc;
   int32_t* status;
@@ -156,17 +157,21 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.n_tiles = (pr.N + BN - 1) / BN;
   p.m_blocks = (pr.M + kBM - 1) / kBM;
   p.sched = pr.sched;
+  p.offsets = pr.offsets;
   p.a_scale = pr.a_scale;
   p.b_scale = pr.b_scale;
   p.d = static_cast<__nv_bfloat16*>(pr.d);
   p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
   p.status = pr.status;
 
-  const long long max_items =
-      (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : (long long)p.m_blocks) * p.n_tiles;
+  const long long max_blocks = pr.mode == MODE_MASKED    ? (long long)pr.G * p.m_blocks
+                               : pr.mode == MODE_COMPACT ? (long long)p.m_blocks + pr.G
+                                                         : (long long)p.m_blocks;
+  const long long max_items = max_blocks * p.n_tiles;
   if (max_items <= 0) return DG_OK;
-  const int table_bytes =
-      (pr.mode == MODE_MASKED) ? (2 * pr.G + 1) * 4 : p.m_blocks * 4;
+  const int table_bytes = pr.mode == MODE_MASKED    ? (2 * pr.G + 1) * 4
+                          : pr.mode == MODE_COMPACT ? (3 * pr.G + 1) * 4
+                                                    : p.m_blocks * 4;
   const int smem_bytes = L::total(table_bytes);
   if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
 
@@ -398,13 +403,15 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
   if ((pr.kind == DG_KIND_BF16) != (pr.scale_mode == DG_SCALE_NONE)) return DG_ERR_BAD_SCALE_MODE;
   if (pr.G < 1 || pr.M < 0 || pr.N < 16 || pr.K < 1) return DG_ERR_BAD_SHAPE;
   if (pr.G > DG_MAX_GROUPS) return DG_ERR_TOO_LARGE;
-  if (pr.mode == MODE_CONTIG && pr.M > DG_MAX_CONTIG_ROWS) return DG_ERR_TOO_LARGE;
+  if (pr.mode != MODE_MASKED && pr.M > DG_MAX_CONTIG_ROWS) return DG_ERR_TOO_LARGE;
+  if (pr.mode == MODE_COMPACT && pr.kind == DG_KIND_W4A8) return DG_ERR_BAD_KIND;
   if (pr.N % 16 != 0) return DG_ERR_BAD_SHAPE;
   const int kq = (pr.kind == DG_KIND_BF16) ? 64 : (pr.kind == DG_KIND_W4A8 ? 256 : 128);
   if (pr.K % kq != 0) return DG_ERR_BAD_SHAPE;
   if ((long long)pr.G * (pr.K / kq) * pr.N > 0x7fffffffLL) return DG_ERR_TOO_LARGE;
   if (pr.M == 0) return DG_OK;
   if (!pr.a || !pr.b || !pr.d || !pr.sched) return DG_ERR_NULL_POINTER;
+  if (pr.mode == MODE_COMPACT && !pr.offsets) return DG_ERR_NULL_POINTER;
   if (pr.scale_mode != DG_SCALE_NONE && (!pr.a_scale || !pr.b_scale)) return DG_ERR_NULL_POINTER;
   if (!aligned16(pr.a) || !aligned16(pr.b) || !aligned16(pr.d)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.scale_mode == DG_SCALE_PER_CHANNEL && !aligned16(pr.b_scale)) return DG_ERR_BAD_ALIGNMENT;
@@ -422,19 +429,21 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
   // every SM pair twice, else one-CTA 128x256 tiles.
   int bn = pr.block_n;
   if (bn == 0) {
-    const long long rows = (pr.mode == MODE_CONTIG) ? (long long)pr.M
+    const long long rows = (pr.mode != MODE_MASKED) ? (long long)pr.M
                                                     : (long long)pr.G * (pr.expected_m > 0 ? pr.expected_m : 0);
     // rows per group decide whether a 256-row super block is mostly real rows
     const bool big_groups = (pr.mode == MODE_CONTIG) ? (rows / pr.G >= 512) : (pr.expected_m >= 256);
     const long long pair_items = (rows / 256) * (pr.N / 256);
-    if (big_groups && pr.N >= 256 && pair_items >= 2LL * (dev->sm_count / 2))
+    if (pr.mode == MODE_COMPACT)
+      bn = (pr.N >= 256 && (rows / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
+    else if (big_groups && pr.N >= 256 && pair_items >= 2LL * (dev->sm_count / 2))
       bn = 512;
     else if (pr.mode == MODE_CONTIG)
       bn = (pr.N >= 256 && (rows / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
     else
       bn = (pr.expected_m > 256 && pr.N >= 256) ? 256 : 128;
   }
-  if (bn == 512 && pr.N < 256) bn = 128;
+  if (bn == 512 && (pr.N < 256 || pr.mode == MODE_COMPACT)) bn = 128;
   if (pr.kind == DG_KIND_W4A8) return launch_w4(pr, *dev, stream);
 
   if (bn == 512) {  // two-CTA 256x256 tiles
@@ -479,6 +488,30 @@ int dg_masked_gemm(const dg_masked_args* a, void* stream) {
   pr.sched = a->masked_m;
   pr.G = a->num_groups;
   pr.M = a->max_m;
+  pr.N = a->n;
+  pr.K = a->k;
+  pr.block_n = a->block_n;
+  pr.expected_m = a->expected_m;
+  pr.debug_acc = a->debug_acc;
+  pr.status = a->status;
+  return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
+}
+
+int dg_compact_gemm(const dg_compact_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  Problem pr{};
+  pr.kind = a->kind;
+  pr.scale_mode = a->scale_mode;
+  pr.mode = MODE_COMPACT;
+  pr.a = a->a;
+  pr.b = a->b_packed;
+  pr.d = a->d;
+  pr.a_scale = a->a_scale;
+  pr.b_scale = a->b_scale;
+  pr.sched = a->counts;
+  pr.offsets = a->offsets;
+  pr.G = a->num_groups;
+  pr.M = a->capacity;
   pr.N = a->n;
   pr.K = a->k;
   pr.block_n = a->block_n;

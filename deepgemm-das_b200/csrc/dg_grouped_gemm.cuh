@@ -41,7 +41,7 @@ constexpr int kRowBytes = 128;   // bytes of K per shared-memory row (one swizzl
 constexpr int kATileBytes = kBM * kRowBytes;
 constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per block on sm_100
 
-enum : int { MODE_MASKED = 0, MODE_CONTIG = 1 };
+enum : int { MODE_MASKED = 0, MODE_CONTIG = 1, MODE_COMPACT = 2 };
 
 // Where a bounded wait gave up (reported in status[2]).
 enum : int {
@@ -64,7 +64,8 @@ struct KernelParams {
   int kblocks;     // K / (elements per 128 bytes)
   int n_tiles;     // ceil(N / BN)
   int m_blocks;    // masked: ceil(max_m/128); contiguous: ceil(M_total/128)
-  const int32_t* sched;  // masked_m[G] or m_indices[M_total]
+  const int32_t* sched;  // masked_m[G], m_indices[M_total], or (compact) rows per group [G]
+  const int32_t* offsets;  // compact layout only: first row of each group in the flat [M][K] tensor
   const float* a_scale;
   const float* b_scale;
   __nv_bfloat16* d;
@@ -166,7 +167,7 @@ struct ItemDecoder {
       : p(p_), tbl(tbl_), bn(bn_), cursor(0) {}
   __device__ __forceinline__ TileCoord get(int item) {
     TileCoord t;
-    if (p.mode == MODE_MASKED) {
+    if (p.mode != MODE_CONTIG) {
       const int32_t* cnt = tbl;
       const int32_t* pref = tbl + p.G;
       while (item >= pref[cursor + 1]) ++cursor;  // items only grow, so the cursor persists
@@ -176,6 +177,10 @@ struct ItemDecoder {
       t.row0 = mt * kBM;
       t.n0 = (local - mt * p.n_tiles) * bn;
       t.rows_valid = min(kBM, cnt[cursor] - t.row0);
+      if (p.mode == MODE_COMPACT) {  // rows of group g start at offsets[g] in the flat tensor
+        t.row0 += tbl[2 * p.G + 1 + cursor];
+        t.rows_valid = min(t.rows_valid, p.M - t.row0);
+      }
     } else {
       const int bi = item / p.n_tiles;
       const int e = tbl[bi];
@@ -237,13 +242,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     tma_prefetch_desc(&tm_b);
   }
 
-  // Schedule table.  Masked: cnt[G] (clamped masked_m) and pref[G+1] (running number of
-  // work items).  Contiguous: the list of 128-row blocks whose first row belongs to a
-  // group, as (group << 16 | block).
-  if (p.mode == MODE_MASKED) {
+  // Schedule table.  Masked / compact: cnt[G] (clamped rows per group), pref[G+1] (running
+  // number of work items) and, compact, off[G] (first row of each group).  Contiguous: the
+  // list of 128-row blocks whose first row belongs to a group, as (group << 16 | block).
+  if (p.mode != MODE_CONTIG) {
     int32_t* cnt = tbl;
     int32_t* pref = tbl + p.G;
-    for (int g = tid; g < p.G; g += blockDim.x) cnt[g] = max(0, min(p.sched[g], p.M));
+    for (int g = tid; g < p.G; g += blockDim.x) {
+      cnt[g] = max(0, min(p.sched[g], p.M));
+      if (p.mode == MODE_COMPACT) tbl[2 * p.G + 1 + g] = max(0, min(p.offsets[g], p.M));
+    }
     __syncthreads();
     if (warp == 0) {
       int running = 0;

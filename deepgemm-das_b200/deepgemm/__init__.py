@@ -39,6 +39,8 @@ from .m_group_gemm import (
 )
 from .m_group_gemm_nt_contiguous import (
     get_m_grouped_fp8_contiguous_config,
+    m_grouped_bf16_gemm_nt_contiguous,
+    m_grouped_i8_gemm_nt_contiguous_nopad,
     m_grouped_fp8_gemm_nt_contiguous,
     m_grouped_fp8_gemm_nt_contiguous_tensor_wise,
     m_grouped_i8_gemm_nt_contiguous,
@@ -50,12 +52,14 @@ from .m_group_gemm_nt_masked import (
     m_grouped_i8_gemm_nt_masked,
     m_grouped_w4a8_gemm_nt_masked,
     m_grouped_w4a8_gemm_nt_masked_hipc,
+    m_grouped_w8a8_gemm_nt_compact_masked,
     m_grouped_w8a8_gemm_nt_masked,
     m_grouped_w8a8_gemm_nt_masked_gfx936,
     m_grouped_w8a8_gemm_nt_masked_gfx936_pack_permute,
     m_grouped_w8a8_gemm_nt_masked_impl,
 )
 
+from .legacy_compat import *  # noqa: F401,F403  (old names, as the reference re-exports them)
 from .quant_group import quant_group_capacity, quantize_group_rows
 
 __version__ = "0.1.0"

@@ -23,6 +23,7 @@ ERR_CUDA = -7
 EXPORTED_SYMBOLS = (
     "dg_masked_gemm",
     "dg_contig_gemm",
+    "dg_compact_gemm",
     "dg_quant_group_rows",
     "dg_quant_group_scratch_bytes",
     "dg_quant_group_rows_noalloc",
@@ -76,6 +77,28 @@ class ContigArgs(C.Structure):
     ]
 
 
+class CompactArgs(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("scale_mode", C.c_int32),
+        ("a", C.c_void_p),
+        ("b_packed", C.c_void_p),
+        ("d", C.c_void_p),
+        ("a_scale", C.c_void_p),
+        ("b_scale", C.c_void_p),
+        ("counts", C.c_void_p),
+        ("offsets", C.c_void_p),
+        ("num_groups", C.c_int32),
+        ("capacity", C.c_int32),
+        ("n", C.c_int32),
+        ("k", C.c_int32),
+        ("expected_m", C.c_int32),
+        ("block_n", C.c_int32),
+        ("debug_acc", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 class QuantGroupArgs(C.Structure):
     _fields_ = [
         ("kind", C.c_int32),
@@ -108,6 +131,8 @@ def _load() -> C.CDLL:
     lib.dg_masked_gemm.restype = C.c_int
     lib.dg_contig_gemm.argtypes = [C.POINTER(ContigArgs), C.c_void_p]
     lib.dg_contig_gemm.restype = C.c_int
+    lib.dg_compact_gemm.argtypes = [C.POINTER(CompactArgs), C.c_void_p]
+    lib.dg_compact_gemm.restype = C.c_int
     for fn in (lib.dg_pack_weight, lib.dg_unpack_weight):
         fn.argtypes = [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                        C.c_int32, C.c_void_p]

@@ -168,6 +168,44 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
     return d
 
 
+def grouped_gemm_compact(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Tensor,
+                         d: torch.Tensor, a_scale: Optional[torch.Tensor],
+                         b_scale: Optional[torch.Tensor], counts: torch.Tensor,
+                         offsets: torch.Tensor, expected_m: int, *, block_n: int = 0,
+                         debug_acc: Optional[torch.Tensor] = None,
+                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """d[offsets[g] + m] = bf16((A[offsets[g] + m] @ B[g]^T) * a_scale * b_scale[g]) for
+    m < counts[g], via dg_compact_gemm; checks follow the reference's
+    (csrc/arch/gfx936_gfx938_shared/m_grouped_w8a8_gemm_nt_masked.cu:1778-1838)."""
+    what = f"compact {KIND_NAMES[kind]} grouped GEMM"
+    _chk(a.dim() == 2, f"{what}: input must be [capacity, K], got {tuple(a.shape)}")
+    _chk(d.dim() == 2, f"{what}: output must be [capacity, N], got {tuple(d.shape)}")
+    cap, k = (int(x) for x in a.shape)
+    g, n, bk = packed_weight_dims(b, kind)
+    _common_checks(kind, a, b, d, counts, what)
+    _chk(bk == k, f"{what}: weight K={bk} does not match activation K={k}")
+    _chk(tuple(d.shape) == (cap, n), f"{what}: output must be {(cap, n)}, got {tuple(d.shape)}")
+    _chk(counts.dim() == 1 and counts.numel() == g, f"{what}: masked_m must be int32 [{g}]")
+    _chk(offsets.is_cuda and offsets.dtype == torch.int32 and offsets.is_contiguous()
+         and offsets.shape == counts.shape, f"{what}: expert_offsets must be contiguous CUDA int32 [{g}]")
+    if scale_mode == SCALE_NONE:
+        a_s = b_s = None
+    else:
+        _chk(a_scale is not None and b_scale is not None, f"{what}: scales are required")
+        a_s = _scale(a_scale, (cap,), "a_scale", what)
+        b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
+    _debug_and_status(debug_acc, status, cap, n, a.device, what)
+    args = _cabi.CompactArgs(
+        kind=kind, scale_mode=scale_mode, a=a.data_ptr(), b_packed=b.data_ptr(), d=d.data_ptr(),
+        a_scale=_ptr(a_s), b_scale=_ptr(b_s), counts=counts.data_ptr(), offsets=offsets.data_ptr(),
+        num_groups=g, capacity=cap, n=n, k=k, expected_m=int(expected_m), block_n=int(block_n),
+        debug_acc=_ptr(debug_acc), status=_ptr(status))
+    with torch.cuda.device(a.device):
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        _cabi.check(_cabi.lib.dg_compact_gemm(C.byref(args), C.c_void_p(stream)), what)
+    return d
+
+
 def kind_of_activation(a: torch.Tensor) -> int:
     """INT8 or FP8 from the activation dtype, as the reference's low-latency op does
     (m_grouped_fp8_gemm_nt_maksed_low_latency.cu:1150-1161)."""
@@ -179,7 +217,7 @@ def kind_of_activation(a: torch.Tensor) -> int:
 
 
 __all__ = [
-    "grouped_gemm_masked", "grouped_gemm_contiguous", "packed_weight_dims", "kind_of_activation",
+    "grouped_gemm_masked", "grouped_gemm_contiguous", "grouped_gemm_compact", "packed_weight_dims", "kind_of_activation",
     "KIND_I8", "KIND_E4M3", "KIND_W4A8", "KIND_BF16",
     "SCALE_PER_CHANNEL", "SCALE_TENSOR_WISE", "SCALE_NONE",
 ]

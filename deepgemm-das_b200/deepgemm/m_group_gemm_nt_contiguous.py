@@ -107,6 +107,40 @@ def m_grouped_i8_gemm_nt_contiguous(
     return output
 
 
+def m_grouped_i8_gemm_nt_contiguous_nopad(
+    a: tuple[torch.Tensor, torch.Tensor],
+    b: tuple[torch.Tensor, torch.Tensor],
+    output: torch.Tensor,
+    m_indices: torch.Tensor,
+    token_per_expert: torch.Tensor,
+) -> torch.Tensor:
+    """INT8 contiguous grouped GEMM without padding rows (reference :312-323): the rows of
+    expert e follow those of expert e-1 directly, ``token_per_expert[e]`` of them."""
+    input, a_scale = a
+    b_qweight, b_scale = b
+    b_scale = _normalize_contiguous_b_scale(b_scale, "int8")
+    return op.m_grouped_w8a8_gemm_nt_nopad_contiguous(
+        input, b_qweight, output, a_scale, b_scale, m_indices, token_per_expert)
+
+
+def m_grouped_bf16_gemm_nt_contiguous(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    output: torch.Tensor,
+    m_indices: torch.Tensor,
+    config: Optional[Dict[str, Any]] = {"MODE": 1000},
+) -> torch.Tensor:
+    """BF16 contiguous grouped GEMM, no scales (reference :504-518); ``b`` from
+    ``pack_bf16_masked_weight``."""
+    mode = config["MODE"]
+    if b.dim() != 4:
+        raise ValueError("BF16 contiguous kernels require weights packed by pack_bf16_masked_weight")
+    if m_indices.dtype != torch.int32:
+        m_indices = m_indices.to(torch.int32)
+    ones = torch.empty(0, device=a.device)      # the reference passed unit scales; none are needed
+    return op.m_grouped_w16a16_gemm_nt_contiguous(a, b, output, ones, ones, m_indices.contiguous(), mode)
+
+
 def m_grouped_fp8_gemm_nt_contiguous(
     a: tuple[torch.Tensor, torch.Tensor],
     b: tuple[torch.Tensor, torch.Tensor],

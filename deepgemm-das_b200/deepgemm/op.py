@@ -137,6 +137,33 @@ _define("m_grouped_w8a8_gemm_nt_contiguous", _CONTIG_MODE_SCHEMA,
 _define("m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc", _CONTIG_MODE_SCHEMA,
         _contig_mode_impl(KIND_W4A8, SCALE_PER_CHANNEL))
 
+def _compact_impl(input, b_qweight, output, a_scale, b_scale, masked_m, expert_offsets,
+                  expected_m_per_group):
+    return _core.grouped_gemm_compact(KIND_I8, SCALE_PER_CHANNEL, input, b_qweight, output, a_scale,
+                                      b_scale, masked_m, expert_offsets, expected_m_per_group)
+
+
+def _nopad_impl(input, b_qweight, output, a_scale, b_scale, m_indices, token_per_expert):
+    # rows of each expert follow one another without padding: offsets = running sum of counts
+    counts = token_per_expert.to(torch.int32).contiguous()
+    offsets = (torch.cumsum(counts, 0, dtype=torch.int32) - counts).contiguous()
+    return _core.grouped_gemm_compact(KIND_I8, SCALE_PER_CHANNEL, input, b_qweight, output, a_scale,
+                                      b_scale, counts, offsets, 0)
+
+
+def _contig_bf16_impl(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
+    return _core.grouped_gemm_contiguous(KIND_BF16, SCALE_NONE, input, b_qweight, output, None, None,
+                                         m_indices)
+
+
+_define("m_grouped_marlin_w8a8_gemm_nt_compact_masked",
+        "(Tensor input, Tensor b_qweight, Tensor(a!) output, Tensor a_scale, Tensor b_scale, "
+        "Tensor masked_m, Tensor expert_offsets, int expected_m_per_group) -> Tensor(a!)", _compact_impl)
+_define("m_grouped_w8a8_gemm_nt_nopad_contiguous",
+        "(Tensor input, Tensor b_qweight, Tensor(a!) output, Tensor a_scale, Tensor b_scale, "
+        "Tensor m_indices, Tensor token_per_expert) -> Tensor(a!)", _nopad_impl)
+_define("m_grouped_w16a16_gemm_nt_contiguous", _CONTIG_MODE_SCHEMA, _contig_bf16_impl)
+
 _ops = getattr(torch.ops, _NS)
 
 
@@ -204,6 +231,24 @@ def m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc(input, b_qweight, output, a_sc
                                                   m_indices, mode):
     return _ops.m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc(input, b_qweight, output, a_scale,
                                                               b_scale, m_indices, int(mode))
+
+
+def m_grouped_marlin_w8a8_gemm_nt_compact_masked(input, b_qweight, output, a_scale, b_scale,
+                                                 masked_m, expert_offsets, expected_m_per_group):
+    return _ops.m_grouped_marlin_w8a8_gemm_nt_compact_masked(
+        input, b_qweight, output, a_scale, b_scale, masked_m, expert_offsets,
+        int(expected_m_per_group))
+
+
+def m_grouped_w8a8_gemm_nt_nopad_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices,
+                                            token_per_expert):
+    return _ops.m_grouped_w8a8_gemm_nt_nopad_contiguous(input, b_qweight, output, a_scale, b_scale,
+                                                        m_indices, token_per_expert)
+
+
+def m_grouped_w16a16_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
+    return _ops.m_grouped_w16a16_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
+                                                    m_indices, int(mode))
 
 
 def m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):

@@ -140,6 +140,30 @@ typedef struct dg_contig_args {
   int32_t*       status;
 } dg_contig_args;
 
+/* Arguments of the compact-layout grouped GEMM: rows of all groups in one flat tensor, group g
+ * owning rows [offsets[g], offsets[g] + counts[g]) with no alignment or padding between groups.
+ *   D[offsets[g] + m][n] = bf16_rne((float(sum_k A[offsets[g] + m][k] * B[g][n][k]) * a_scale[.]) * b_scale[g][n])
+ * for m < counts[g]; no other row of D is written.  INT8, FP8 and BF16 kinds. */
+typedef struct dg_compact_args {
+  int32_t kind;
+  int32_t scale_mode;
+  const void*    a;           /* [capacity][K] */
+  const void*    b_packed;
+  void*          d;           /* [capacity][N] bf16 */
+  const float*   a_scale;     /* [capacity] */
+  const float*   b_scale;     /* [G][N] or [G] */
+  const int32_t* counts;      /* [G] rows per group */
+  const int32_t* offsets;     /* [G] first row of each group */
+  int32_t num_groups;
+  int32_t capacity;           /* rows of a / d, <= DG_MAX_CONTIG_ROWS */
+  int32_t n;
+  int32_t k;
+  int32_t expected_m;         /* hint only */
+  int32_t block_n;            /* 0 = choose; 128 / 256 */
+  void*          debug_acc;
+  int32_t*       status;
+} dg_compact_args;
+
 #define DG_MAX_GROUPS      1024
 #define DG_MAX_CONTIG_ROWS (4096 * 128)
 
@@ -163,6 +187,12 @@ DG_API int dg_masked_gemm(const dg_masked_args* args, void* stream);
  *   m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc
  *                                          csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_contiguous_hipc.cu:861-915 */
 DG_API int dg_contig_gemm(const dg_contig_args* args, void* stream);
+
+/* Compact grouped GEMM.  Stands in for, in the reference:
+ *   m_grouped_marlin_w8a8_gemm_nt_compact_masked   csrc/arch/gfx936_gfx938_shared/m_grouped_w8a8_gemm_nt_masked.cu:1767-1838
+ *   m_grouped_w8a8_gemm_nt_nopad_contiguous        csrc/arch/gfx936_gfx938_shared/asm_m_grouped_w8a8_gemm_nt_contiguous.cu:595-607
+ *     (rows per group given as token_per_expert; the caller passes their running sum as offsets) */
+DG_API int dg_compact_gemm(const dg_compact_args* args, void* stream);
 
 /* Nibble order of a row-major int4 source [G][N][K/2]:
  *   DG_NIBBLE_HIGH_FIRST: byte j holds w[2j] in its high nibble (the reference's
