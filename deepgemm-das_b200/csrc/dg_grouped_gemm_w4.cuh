@@ -316,22 +316,27 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
       if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kW4AccCols;
+      // 16 tokens per step; the step loop stays rolled to keep the code small (the fully
+      // unrolled form stalled on instruction fetch)
+#pragma unroll 1
+      for (int c = 0; c * 16 < t.rows_valid; ++c) {
+        const int w = c >> 1;  // which of the four prefetched 32-token groups
+        const float as_w = w == 0 ? as_l[0] : (w == 1 ? as_l[1] : (w == 2 ? as_l[2] : as_l[3]));
+        const unsigned m_w =
+            (w == 0 ? tok_mask[0] : (w == 1 ? tok_mask[1] : (w == 2 ? tok_mask[2] : tok_mask[3]))) >>
+            ((c & 1) * 16);
+        uint32_t r[16];
+        tmem_ld_32x16(t_lane + c * 16, r);
+        tmem_ld_wait();
+        __nv_bfloat16* d_col = p.d + (row_base + c * 16) * p.N + chan;
+        uint32_t* dbg_col = p.debug_acc + (row_base + c * 16) * p.N + chan;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        if (c * 32 < t.rows_valid) {  // warp-uniform
-          uint32_t r[32];
-          tmem_ld_32x32(t_lane + c * 32, r);
-          tmem_ld_wait();
-          __nv_bfloat16* d_col = p.d + (row_base + c * 32) * p.N + chan;
-          uint32_t* dbg_col = p.debug_acc + (row_base + c * 32) * p.N + chan;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float as_j = __shfl_sync(0xffffffffu, as_l[c], j);
-            if (((tok_mask[c] >> j) & 1u) && chan_ok) {
-              const float v = (__int2float_rn(static_cast<int>(r[j])) * as_j) * bs;
-              d_col[(size_t)j * p.N] = __float2bfloat16_rn(v);
-              if (p.debug_acc != nullptr) dbg_col[(size_t)j * p.N] = r[j];
-            }
+        for (int j = 0; j < 16; ++j) {
+          const float as_j = __shfl_sync(0xffffffffu, as_w, (c & 1) * 16 + j);
+          if (((m_w >> j) & 1u) && chan_ok) {
+            const float v = (__int2float_rn(static_cast<int>(r[j])) * as_j) * bs;
+            d_col[(size_t)j * p.N] = __float2bfloat16_rn(v);
+            if (p.debug_acc != nullptr) dbg_col[(size_t)j * p.N] = r[j];
           }
         }
       }
