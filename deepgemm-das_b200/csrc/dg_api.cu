@@ -431,8 +431,10 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
   if (bn == 0) {
     const long long rows = (pr.mode != MODE_MASKED) ? (long long)pr.M
                                                     : (long long)pr.G * (pr.expected_m > 0 ? pr.expected_m : 0);
-    // rows per group decide whether a 256-row super block is mostly real rows
-    const bool big_groups = (pr.mode == MODE_CONTIG) ? (rows / pr.G >= 512) : (pr.expected_m >= 256);
+    // rows per group (padding included) decide whether 256-row super blocks are mostly real
+    // rows; measured on 32768 routed rows over 256 / 128 / 64 / 32 groups the two-CTA tiles win
+    // from about 380 allocated rows per group upwards and lose at 256
+    const bool big_groups = (pr.mode == MODE_CONTIG) ? (rows / pr.G >= 320) : (pr.expected_m >= 256);
     const long long pair_items = (rows / 256) * (pr.N / 256);
     if (pr.mode == MODE_COMPACT)
       bn = (pr.N >= 256 && (rows / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
