@@ -114,11 +114,9 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* b
 // ---- kernel instantiations: (kind, BN) -> stages so the ring holds ~192-200 KB
 template <int KIND, int BN>
 struct StagesFor {
-  // K blocks per stage.  Two per stage (three 64 KB stages for BN = 128) halves the barrier
-  // work of the UMMA thread but measured 7 % slower on the decode workload at full SM clock
-  // than six 32 KB stages, so every instantiation uses one.
-  static constexpr int kps = 1;
-  static constexpr int per_stage = kps * (kATileBytes + BN * kRowBytes);
+  // One K block per stage: two per stage (three 64 KB stages for BN = 128) measured 7 % slower
+  // on the decode workload at full SM clock than six 32 KB stages.
+  static constexpr int per_stage = kATileBytes + BN * kRowBytes;
   static constexpr int value = (200 * 1024) / per_stage;
 };
 
@@ -132,6 +130,7 @@ struct Problem {
   const int32_t* sched;
   const int32_t* offsets;
   int G, M, N, K, block_n, expected_m;
+  int narrow;  // filled by validate_and_launch: KernelParams::narrow for the BN = 128 tile
   void* debug_acc;
   int32_t* status;
 };
@@ -139,10 +138,9 @@ struct Problem {
 template <int KIND, int BN>
 int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   constexpr int STAGES = StagesFor<KIND, BN>::value;
-  constexpr int KPS = StagesFor<KIND, BN>::kps;
-  using L = SmemLayout<KIND, BN, STAGES, KPS>;
+  using L = SmemLayout<KIND, BN, STAGES>;
   static_assert(STAGES >= 2, "ring too shallow");
-  auto kernel = grouped_gemm_kernel<KIND, BN, STAGES, KPS>;
+  auto kernel = grouped_gemm_kernel<KIND, BN, STAGES>;
 
   const int esize = (KIND == DG_KIND_BF16) ? 2 : 1;
   const int elems_per_row = kRowBytes / esize;  // A elements per 128-byte K block
@@ -179,18 +177,25 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // group; contiguous: (K, M_total).  Rows past the extent read as zero.
   const CUtensorMapDataType dt_a =
       (KIND == DG_KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  CUtensorMap tm_a, tm_b;
+  // tm_a32 fetches one 32-row slice of it, for tiles with fewer than 97 valid rows.
+  CUtensorMap tm_a, tm_a32, tm_b;
   int rc;
   if (pr.mode == MODE_MASKED) {
     const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
     const uint64_t strides[2] = {(uint64_t)pr.K * esize, (uint64_t)pr.M * pr.K * esize};
     const uint32_t box[3] = {(uint32_t)elems_per_row, (uint32_t)kBM, 1u};
+    const uint32_t box32[3] = {(uint32_t)elems_per_row, 32u, 1u};
     rc = encode_map(&tm_a, dt_a, 3, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_a32, dt_a, 3, pr.a, dims, strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
     const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
     const uint64_t strides[1] = {(uint64_t)pr.K * esize};
     const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)kBM};
+    const uint32_t box32[2] = {(uint32_t)elems_per_row, 32u};
     rc = encode_map(&tm_a, dt_a, 2, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_a32, dt_a, 2, pr.a, dims, strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc != DG_OK) return rc;
   // B (packed): a flat list of G*kblocks*N rows of 128 bytes, so a BN-row box is one
@@ -203,6 +208,20 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
     rc = encode_map(&tm_b, dt_a, 2, pr.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc != DG_OK) return rc;
+  // Narrow weight boxes (64 and 32 rows) for sparse routing; only the BN = 128 tile uses them.
+  CUtensorMap tm_b64 = tm_b, tm_b32 = tm_b;
+  p.narrow = (BN == 128 && pr.mode != MODE_CONTIG) ? pr.narrow : 0;
+  if (p.narrow) {
+    const uint64_t rows = (uint64_t)pr.G * p.kblocks * pr.N;
+    const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
+    const uint64_t strides[1] = {(uint64_t)kRowBytes};
+    const uint32_t box64[2] = {(uint32_t)elems_per_row, 64u};
+    const uint32_t box32[2] = {(uint32_t)elems_per_row, 32u};
+    rc = encode_map(&tm_b64, dt_a, 2, pr.b, dims, strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_b32, dt_a, 2, pr.b, dims, strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != DG_OK) return rc;
+  }
 
   // Opt in to the large shared-memory carve-out once per device and instantiation.
   static std::atomic<unsigned long long> configured{0};
@@ -216,8 +235,10 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
     configured.fetch_or(bit, std::memory_order_release);
   }
 
-  const int grid = static_cast<int>(max_items < dev.sm_count ? max_items : dev.sm_count);
-  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_b, p);
+  // With narrowing allowed the item count can reach max_blocks * ceil(N / 32).
+  const long long grid_items = p.narrow ? max_blocks * ((pr.N + 31) / 32) : max_items;
+  const int grid = static_cast<int>(grid_items < dev.sm_count ? grid_items : dev.sm_count);
+  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_a32, tm_b, tm_b64, tm_b32, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -396,7 +417,7 @@ int launch_w4(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int validate_and_launch(const Problem& pr, cudaStream_t stream) {
+int validate_and_launch(Problem& pr, cudaStream_t stream) {
   if (pr.kind < DG_KIND_I8 || pr.kind > DG_KIND_BF16) return DG_ERR_BAD_KIND;
   if (pr.scale_mode < DG_SCALE_PER_CHANNEL || pr.scale_mode > DG_SCALE_NONE)
     return DG_ERR_BAD_SCALE_MODE;
@@ -416,7 +437,10 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
   if (!aligned16(pr.a) || !aligned16(pr.b) || !aligned16(pr.d)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.scale_mode == DG_SCALE_PER_CHANNEL && !aligned16(pr.b_scale)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.debug_acc && !aligned16(pr.debug_acc)) return DG_ERR_BAD_ALIGNMENT;
-  if (pr.block_n != 0 && pr.block_n != 128 && pr.block_n != 256 && pr.block_n != 512)
+  if (pr.block_n != 0 && pr.block_n != 32 && pr.block_n != 64 && pr.block_n != 128 &&
+      pr.block_n != 256 && pr.block_n != 512)
+    return DG_ERR_BAD_ARGUMENT;
+  if ((pr.block_n == 32 || pr.block_n == 64) && (pr.mode == MODE_CONTIG || pr.kind == DG_KIND_W4A8))
     return DG_ERR_BAD_ARGUMENT;
 
   const DeviceInfo* dev = nullptr;
@@ -428,6 +452,10 @@ int validate_and_launch(const Problem& pr, cudaStream_t stream) {
   // operand traffic per flop: two-CTA 256x256 tiles when there are enough of them to fill
   // every SM pair twice, else one-CTA 128x256 tiles.
   int bn = pr.block_n;
+  // 128-column tiles may narrow on the device when few groups have rows: always when the
+  // library chooses, never when the caller asked for exactly 128, to a fixed width for 32 / 64.
+  pr.narrow = (bn == 0) ? 1 : ((bn == 32 || bn == 64) ? bn : 0);
+  if (bn == 32 || bn == 64) bn = 128;
   if (bn == 0) {
     const long long rows = (pr.mode != MODE_MASKED) ? (long long)pr.M
                                                     : (long long)pr.G * (pr.expected_m > 0 ? pr.expected_m : 0);

@@ -9,9 +9,10 @@
 // Roles inside a block
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A tile
 //               (128 rows x 128 bytes of K) and the weight tile (BN rows x 128 bytes of K,
-//               one contiguous span of the packed weight) into a STAGES-deep ring; a stage
-//               holds KPS consecutive K blocks (one wait and one commit of the UMMA thread
-//               per stage).
+//               one contiguous span of the packed weight) into a STAGES-deep ring.  Only the
+//               32-row slices of A with valid rows are fetched.  With few items (sparse
+//               routing) the BN = 128 instantiation narrows its tiles to 64 or 32 columns so
+//               that every SM streams weights; a stage then holds several K blocks.
 //   warp 1      UMMA issuer: one lane issues four tcgen05.mma (K = 32 bytes each) per
 //               ring stage into one of two TMEM accumulators (128 lanes x BN columns),
 //               and owns TMEM allocation.
@@ -71,14 +72,40 @@ struct KernelParams {
   __nv_bfloat16* d;
   uint32_t* debug_acc;
   int32_t* status;
+  int narrow;  // BN = 128, masked / compact: 0 = tiles stay 128 columns wide, 1 = the kernel may
+               // narrow them to 64 / 32 columns when few groups have rows, 64 / 32 = forced width
 };
 
-template <int KIND, int BN, int STAGES, int KPS = 1>
+// Shape of one pipeline stage for a tile with `rows_valid` rows and `bn_eff` columns.  A tile
+// with at most 32 valid rows fetches only a 32-row slice of A (the UMMA still reads 128 rows;
+// what it reads beyond the slice is stale shared memory that only reaches accumulator rows
+// nobody stores).  Splitting A into several slices was measured 18 % slower on the decode
+// workload than one 128-row copy, so 33..128 rows fetch the whole tile.  When both operands
+// are narrow, several K blocks share one stage slot so the bytes in flight per stage stay
+// near 32 KB.
+struct StageShape {
+  int a_rows;         // rows of A fetched per K block: 32 or 128
+  int kps;            // K blocks per stage
+  uint32_t a_stride;  // bytes between the A sub-tiles of consecutive K blocks in a slot
+  uint32_t b_stride;  // same for the weight sub-tiles
+  uint32_t bytes;     // bytes fetched per K block
+};
+__device__ __forceinline__ StageShape stage_shape(int rows_valid, int bn_eff, int bn) {
+  StageShape sh;
+  sh.a_rows = rows_valid <= 32 ? 32 : kBM;
+  sh.kps = min(bn / bn_eff, kBM / sh.a_rows);
+  sh.a_stride = static_cast<uint32_t>(sh.a_rows) * kRowBytes;
+  sh.b_stride = static_cast<uint32_t>(bn_eff) * kRowBytes;
+  sh.bytes = static_cast<uint32_t>(sh.a_rows + bn_eff) * kRowBytes;
+  return sh;
+}
+
+template <int KIND, int BN, int STAGES>
 struct SmemLayout {
   static_assert(KIND != DG_KIND_W4A8, "W4A8 uses grouped_gemm_w4_kernel");
   static constexpr int kBBytes = BN * kRowBytes;  // weight tile of one K block
-  static constexpr int kAStage = KPS * kATileBytes;
-  static constexpr int kBStage = KPS * kBBytes;
+  static constexpr int kAStage = kATileBytes;
+  static constexpr int kBStage = kBBytes;
   static constexpr int off_a = 0;
   static constexpr int off_b = off_a + STAGES * kAStage;
   static constexpr int off_bar = off_b + STAGES * kBStage;
@@ -150,6 +177,9 @@ __device__ __forceinline__ void epilogue_store32(const uint32_t (&r)[32], const 
   }
 }
 
+struct FalseTag { static constexpr bool value = false; };
+struct TrueTag { static constexpr bool value = true; };
+
 struct TileCoord {
   int g;           // group
   int row0;        // first row: within the group (masked) or global (contiguous)
@@ -158,46 +188,54 @@ struct TileCoord {
 };
 
 // Maps a work-item number to its tile using the block's shared-memory schedule table.
+// Masked / compact table: cnt[G], pref[G+1] = running number of 128-row blocks, (compact)
+// off[G]; item = (global row block) * n_tiles + column tile.  Contiguous table: list of row
+// blocks as (group << 16 | block).  `bn` / `n_tiles` are the tile width in use and the number
+// of column tiles at that width.
 struct ItemDecoder {
   const KernelParams& p;
   const int32_t* tbl;
   int bn;
+  int n_tiles;
   int cursor;
-  __device__ ItemDecoder(const KernelParams& p_, const int32_t* tbl_, int bn_)
-      : p(p_), tbl(tbl_), bn(bn_), cursor(0) {}
+  __device__ ItemDecoder(const KernelParams& p_, const int32_t* tbl_, int bn_, int n_tiles_)
+      : p(p_), tbl(tbl_), bn(bn_), n_tiles(n_tiles_), cursor(0) {}
   __device__ __forceinline__ TileCoord get(int item) {
     TileCoord t;
     if (p.mode != MODE_CONTIG) {
       const int32_t* cnt = tbl;
       const int32_t* pref = tbl + p.G;
-      while (item >= pref[cursor + 1]) ++cursor;  // items only grow, so the cursor persists
-      const int local = item - pref[cursor];
-      const int mt = local / p.n_tiles;
+      const int blk = item / n_tiles;
+      while (blk >= pref[cursor + 1]) ++cursor;  // items only grow, so the cursor persists
+      const int mt = blk - pref[cursor];
       t.g = cursor;
       t.row0 = mt * kBM;
-      t.n0 = (local - mt * p.n_tiles) * bn;
+      t.n0 = (item - blk * n_tiles) * bn;
       t.rows_valid = min(kBM, cnt[cursor] - t.row0);
       if (p.mode == MODE_COMPACT) {  // rows of group g start at offsets[g] in the flat tensor
         t.row0 += tbl[2 * p.G + 1 + cursor];
         t.rows_valid = min(t.rows_valid, p.M - t.row0);
       }
     } else {
-      const int bi = item / p.n_tiles;
+      const int bi = item / n_tiles;
       const int e = tbl[bi];
       t.g = e >> 16;
       t.row0 = (e & 0xFFFF) * kBM;
-      t.n0 = (item - bi * p.n_tiles) * bn;
+      t.n0 = (item - bi * n_tiles) * bn;
       t.rows_valid = min(kBM, p.M - t.row0);
     }
     return t;
   }
 };
 
-template <int KIND, int BN, int STAGES, int KPS>
-__global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES, KPS>::kThreads, 1)
+template <int KIND, int BN, int STAGES>
+__global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
-                    const __grid_constant__ CUtensorMap tm_b, const KernelParams p) {
-  using L = SmemLayout<KIND, BN, STAGES, KPS>;
+                    const __grid_constant__ CUtensorMap tm_a32,
+                    const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_b64,
+                    const __grid_constant__ CUtensorMap tm_b32, const KernelParams p) {
+  using L = SmemLayout<KIND, BN, STAGES>;
   constexpr int kUmmaKind =
       (KIND == DG_KIND_E4M3) ? UMMA_F8F6F4 : (KIND == DG_KIND_BF16 ? UMMA_F16 : UMMA_I8);
   constexpr bool kIntAcc = (KIND == DG_KIND_I8);
@@ -223,6 +261,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
   volatile int* n_items_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 8);
+  volatile int* bn_eff_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 12);
   int32_t* tbl = reinterpret_cast<int32_t*>(smem + L::off_table);
 
   // ------------------------------------------------------------------ one-time set-up
@@ -257,7 +296,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       int running = 0;
       for (int g0 = 0; g0 < p.G; g0 += 32) {
         const int g = g0 + lane;
-        int x = (g < p.G) ? ((cnt[g] + kBM - 1) / kBM) * p.n_tiles : 0;
+        int x = (g < p.G) ? (cnt[g] + kBM - 1) / kBM : 0;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
           const int y = __shfl_up_sync(0xffffffffu, x, o);
@@ -268,7 +307,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       if (lane == 0) {
         pref[0] = 0;
-        *n_items_s = running;
+        // Sparse routing (few groups with rows): narrow the tiles until there is an item for
+        // every block, so that all SMs take part in streaming the few weight panels.
+        int bn_eff = BN;
+        if (BN == 128 && p.narrow > 1) {
+          bn_eff = p.narrow;
+        } else if (BN == 128 && p.narrow == 1) {
+          // Narrow only while every item still finds a block of its own: with more items
+          // than blocks the 128-column tiles win (measured: a second round of narrow items
+          // costs more than idle SMs do, as each item pays the same UMMA issue time).
+          for (int bn = 64; bn >= 32; bn >>= 1)
+            if (running * ((p.N + bn - 1) / bn) <= static_cast<int>(gridDim.x)) bn_eff = bn;
+        }
+        *bn_eff_s = bn_eff;
+        *n_items_s = running * ((p.N + bn_eff - 1) / bn_eff);
       }
     }
   } else {
@@ -288,7 +340,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         count += __popc(mask);
         __syncwarp();
       }
-      if (lane == 0) *n_items_s = count * p.n_tiles;
+      if (lane == 0) {
+        *bn_eff_s = BN;
+        *n_items_s = count * p.n_tiles;
+      }
       if (__any_sync(0xffffffffu, bad) && lane == 0 && blockIdx.x == 0 && p.status != nullptr)
         atomicCAS(p.status, DG_DEV_OK, DG_DEV_BAD_GROUP_INDEX);
     }
@@ -304,43 +359,50 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   const uint32_t tmem_base = *tmem_slot;
   const int n_items = *n_items_s;
+  const int bn_eff = *bn_eff_s;                      // tile width in use: BN, or 64 / 32 when narrowed
+  const int nt_eff = (p.N + bn_eff - 1) / bn_eff;    // column tiles at that width
 
   // ------------------------------------------------------------------ roles
   if (warp == 0) {
     if (lane == 0) {
-      // ---- TMA producer
+      // ---- TMA producer.  kNarrow = false is the straight-line loop for full-width tiles
+      // (one K block per stage); kNarrow = true handles 64 / 32-column tiles.
       const uint64_t pol_a = l2_policy_evict_last();   // A tiles are re-read by other n-tiles
       const uint64_t pol_b = l2_policy_evict_first();  // weights stream through once
-      ItemDecoder dec(p, tbl, BN);
       uint32_t it = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-        const TileCoord t = dec.get(item);
-        const int b_row0 = t.g * p.kblocks * p.N + t.n0;
-        for (int kb0 = 0; kb0 < p.kblocks; kb0 += KPS, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) {
-            ok = false;
-            break;
-          }
-          const int nb = min(KPS, p.kblocks - kb0);
-          mbar_arrive_expect_tx(bar_full(s), nb * (kATileBytes + L::kBBytes));
-#pragma unroll
-          for (int j = 0; j < KPS; ++j) {
-            if (j < nb) {
+      auto produce = [&](auto narrow_tag) {
+        constexpr bool kNarrow = decltype(narrow_tag)::value;
+        ItemDecoder dec(p, tbl, bn_eff, nt_eff);
+        const CUtensorMap* tm_w = !kNarrow ? &tm_b : (bn_eff == 64 ? &tm_b64 : &tm_b32);
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+          const TileCoord t = dec.get(item);
+          const StageShape sh = stage_shape(t.rows_valid, kNarrow ? bn_eff : BN, BN);
+          const CUtensorMap* tm_act = (sh.a_rows == kBM) ? &tm_a : &tm_a32;
+          const int kps = kNarrow ? sh.kps : 1;
+          const int b_row0 = t.g * p.kblocks * p.N + t.n0;
+          for (int kb0 = 0; kb0 < p.kblocks; kb0 += kps, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1u;
+            if (!mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) return;
+            const int nb = kNarrow ? min(kps, p.kblocks - kb0) : 1;
+            mbar_arrive_expect_tx(bar_full(s), nb * sh.bytes);
+            for (int j = 0; j < nb; ++j) {
               const int kb = kb0 + j;
-              const uint32_t a_dst = base + L::off_a + s * L::kAStage + j * kATileBytes;
+              const uint32_t a_dst = base + L::off_a + s * L::kAStage + j * sh.a_stride;
               if (p.mode == MODE_MASKED)
-                tma_load_3d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, t.g, pol_a);
+                tma_load_3d(a_dst, tm_act, bar_full(s), kb * kElemsPerRow, t.row0, t.g, pol_a);
               else
-                tma_load_2d(a_dst, &tm_a, bar_full(s), kb * kElemsPerRow, t.row0, pol_a);
-              tma_load_2d(base + L::off_b + s * L::kBStage + j * L::kBBytes, &tm_b, bar_full(s), 0,
+                tma_load_2d(a_dst, tm_act, bar_full(s), kb * kElemsPerRow, t.row0, pol_a);
+              tma_load_2d(base + L::off_b + s * L::kBStage + j * sh.b_stride, tm_w, bar_full(s), 0,
                           b_row0 + kb * p.N, pol_b);
             }
           }
         }
-      }
+      };
+      if (bn_eff == BN)
+        produce(FalseTag{});
+      else
+        produce(TrueTag{});
       // Do not leave while a copy into this block's shared memory is still in flight:
       // wait (bounded) for the last fill of every stage.
       int local_abort = 0;
@@ -353,44 +415,50 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // ---- UMMA issuer
-      uint32_t it = 0, tile = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++tile) {
-        const uint32_t buf = tile & 1u;
-        const uint32_t aph = (tile >> 1) & 1u;
-        if (!mbar_wait_bounded(bar_acc_empty(buf), aph ^ 1u, abort_flag, SITE_MMA_ACC_EMPTY)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb0 = 0; kb0 < p.kblocks; kb0 += KPS, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_MMA_FULL)) {
-            ok = false;
-            break;
-          }
+      // ---- UMMA issuer (same two variants as the producer)
+      auto issue = [&](auto narrow_tag) {
+        constexpr bool kNarrow = decltype(narrow_tag)::value;
+        const uint32_t idesc =
+            !kNarrow ? kIdesc
+                     : (kIdesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>(bn_eff >> 3) << 17);
+        ItemDecoder dec(p, tbl, bn_eff, nt_eff);
+        uint32_t it = 0, tile = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
+          StageShape sh;
+          if (kNarrow) sh = stage_shape(dec.get(item).rows_valid, bn_eff, BN);
+          const int kps = kNarrow ? sh.kps : 1;
+          const uint32_t buf = tile & 1u;
+          const uint32_t aph = (tile >> 1) & 1u;
+          if (!mbar_wait_bounded(bar_acc_empty(buf), aph ^ 1u, abort_flag, SITE_MMA_ACC_EMPTY)) return;
           tc_fence_after_sync();
-          const int nb = min(KPS, p.kblocks - kb0);
-#pragma unroll
-          for (int j = 0; j < KPS; ++j) {
-            if (j < nb) {
-              const uint64_t a_desc = umma_desc_sw128(base + L::off_a + s * L::kAStage + j * kATileBytes);
-              const uint64_t b_desc = umma_desc_sw128(base + L::off_b + s * L::kBStage + j * L::kBBytes);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          for (int kb0 = 0; kb0 < p.kblocks; kb0 += kps, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1u;
+            if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_MMA_FULL)) return;
+            tc_fence_after_sync();
+            const int nb = kNarrow ? min(kps, p.kblocks - kb0) : 1;
+            for (int j = 0; j < nb; ++j) {
+              const uint64_t a_desc = umma_desc_sw128(base + L::off_a + s * L::kAStage +
+                                                      (kNarrow ? j * sh.a_stride : 0u));
+              const uint64_t b_desc = umma_desc_sw128(base + L::off_b + s * L::kBStage +
+                                                      (kNarrow ? j * sh.b_stride : 0u));
 #pragma unroll
               for (int k = 0; k < kRowBytes / 32; ++k) {
                 // +2 in the start-address field = +32 bytes along K inside the swizzled row
-                umma_ss<kUmmaKind>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc,
+                umma_ss<kUmmaKind>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
                                    (kb0 | j | k) != 0 ? 1u : 0u);
               }
             }
+            umma_commit(bar_empty(s));  // frees the stage once these UMMAs have read it
           }
-          umma_commit(bar_empty(s));  // frees the stage once these UMMAs have read it
+          umma_commit(bar_acc_full(buf));
         }
-        if (ok) umma_commit(bar_acc_full(buf));
-      }
+      };
+      if (bn_eff == BN)
+        issue(FalseTag{});
+      else
+        issue(TrueTag{});
       if (*abort_flag) {
         // Abnormal exit: make sure no UMMA is still running before TMEM is released.
         int local_abort = 0;
@@ -402,7 +470,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     // ---- epilogue: this warp may touch TMEM lanes [32q, 32q+32)
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
-    ItemDecoder dec(p, tbl, BN);
+    ItemDecoder dec(p, tbl, bn_eff, nt_eff);
     uint32_t tile = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
       const TileCoord t = dec.get(item);
@@ -423,7 +491,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < bn_eff / 32; ++c) {
           const int cols_left = p.N - (t.n0 + c * 32);
           if (cols_left <= 0) break;  // warp-uniform
           uint32_t r[32];

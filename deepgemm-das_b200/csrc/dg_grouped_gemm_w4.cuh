@@ -122,7 +122,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
       int running = 0;
       for (int g0 = 0; g0 < p.G; g0 += 32) {
         const int g = g0 + lane;
-        int x = (g < p.G) ? ((cnt[g] + kBM - 1) / kBM) * p.n_tiles : 0;
+        int x = (g < p.G) ? (cnt[g] + kBM - 1) / kBM : 0;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
           const int y = __shfl_up_sync(0xffffffffu, x, o);
@@ -133,7 +133,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
       }
       if (lane == 0) {
         pref[0] = 0;
-        *n_items_s = running;
+        *n_items_s = running * p.n_tiles;
       }
     }
   } else {
@@ -175,7 +175,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
     if (lane == 0) {
       // ---- weight producer: one 16 KB packed tile (256 K values) per stage, streamed once
       const uint64_t pol_w = l2_policy_evict_first();
-      ItemDecoder dec(p, tbl, 128);
+      ItemDecoder dec(p, tbl, 128, p.n_tiles);
       uint32_t it = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
@@ -205,7 +205,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
     if (lane == 0) {
       // ---- token producer: two [128 tokens][128 B] tiles per round (L2 resident)
       const uint64_t pol_tok = l2_policy_evict_last();
-      ItemDecoder dec(p, tbl, 128);
+      ItemDecoder dec(p, tbl, 128, p.n_tiles);
       uint32_t it = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
@@ -239,7 +239,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- UMMA issuer: per round, A (weights) from TMEM slot s, B (tokens) from token stage s
-      ItemDecoder dec(p, tbl, 128);
+      ItemDecoder dec(p, tbl, 128, p.n_tiles);
       uint32_t it = 0, tile = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++tile) {
@@ -283,7 +283,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
     // group handles every second item of the block (the ones accumulated in its buffer)
     const int q = warp & 3;
     const uint32_t group = static_cast<uint32_t>(warp - kW4EpiWarp0) >> 2;
-    ItemDecoder dec(p, tbl, 128);
+    ItemDecoder dec(p, tbl, 128, p.n_tiles);
     uint32_t tile = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
       const uint32_t buf = tile & 1u;

@@ -110,7 +110,8 @@ typedef struct dg_masked_args {
   int32_t n;                  /* N, multiple of 16 */
   int32_t k;                  /* K, multiple of 128 (64 for bf16, 256 for W4A8) */
   int32_t expected_m;         /* hint only: typical masked_m; never limits the rows computed */
-  int32_t block_n;            /* 0 = choose; 128 / 256 = one-CTA tile width; 512 = two-CTA 256x256 tiles */
+  int32_t block_n;            /* 0 = choose; 128 / 256 = one-CTA tile width; 512 = two-CTA 256x256 tiles;
+                                 32 / 64 = 128-wide kernel narrowed to that width (sparse routing) */
   void*          debug_acc;   /* NULL, or [G][max_m][N] of raw 32-bit accumulators (s32 / f32) */
   int32_t*       status;      /* NULL, or int32[DG_STATUS_WORDS] device status words */
 } dg_masked_args;
@@ -159,7 +160,7 @@ typedef struct dg_compact_args {
   int32_t n;
   int32_t k;
   int32_t expected_m;         /* hint only */
-  int32_t block_n;            /* 0 = choose; 128 / 256 */
+  int32_t block_n;            /* 0 = choose; 128 / 256; 32 / 64 as in dg_masked_args */
   void*          debug_acc;
   int32_t*       status;
 } dg_compact_args;

@@ -250,3 +250,31 @@ def test_masked_bf16():
                 assert_calc_diff(out[g, :m], ref[g, :m], 1e-3, f"bf16 group {g}")      # calc_diff < 1e-3
                 assert torch.allclose(out[g, :m].float(), ref[g, :m].float(), rtol=1e-2, atol=1e-2)
             assert torch.all(out[g, m:] == 0), "tail rows of a zero-initialised output must stay zero"
+
+
+@pytest.mark.parametrize("active,n,k", [(1, 512, 512), (3, 4096, 384), (2, 1040, 896)])
+def test_sparse_routing_narrow_tiles_bit_exact(active, n, k):
+    """Few experts with rows: the 128-column kernel narrows its tiles to 64 or 32 columns so that
+    every SM streams weights, several K blocks then share a pipeline stage (K / 128 here is not
+    always a multiple of that number).  Same parity bar as the wide tiles at each forced width
+    and at the width the library picks; idle experts stay untouched."""
+    G, max_m = 8, 96
+    mm = torch.zeros(G, dtype=torch.int64)
+    gen = torch.Generator().manual_seed(40 + active)
+    mm[torch.randperm(G, generator=gen)[:active]] = torch.tensor([5, 40, 96])[:active]
+    c = gen_masked_int8(G, max_m, n, k, mm, seed=41)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    for bn in (32, 64, 0):
+        _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn,
+                        what=f"sparse: {active} active, N={n}, K={k}, block_n={bn}")
+
+
+def test_sparse_routing_fp8_narrow_tiles():
+    """FP8 at forced narrow widths: integer-valued inputs make the f32 sums order independent,
+    so the result must equal the 128-column result bit for bit."""
+    mm = [0, 7, 0, 0, 33, 0]
+    c = gen_masked_fp8(6, 64, 768, 640, mm, seed=42, integer=True)
+    outs = {bn: _run_fp8(c, False, None, block_n=bn) for bn in (128, 64, 32, 0)}
+    for bn in (64, 32, 0):
+        assert torch.equal(outs[bn].view(torch.int16), outs[128].view(torch.int16)), f"block_n={bn}"
+    assert torch.all(outs[32][0].float() == SENTINEL) and torch.all(outs[32][1, 7:].float() == SENTINEL)
