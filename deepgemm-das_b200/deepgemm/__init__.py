@@ -61,5 +61,8 @@ from .m_group_gemm_nt_masked import (
 
 from .legacy_compat import *  # noqa: F401,F403  (old names, as the reference re-exports them)
 from .quant_group import quant_group_capacity, quantize_group_rows
+from .print_size import install_op_size_printer
+
+install_op_size_printer(op)  # no-op unless DEEPGEMM_PRINT_OP_SIZE is set
 
 __version__ = "0.1.0"

@@ -115,3 +115,37 @@ def test_cpu_tensors_never_compute():
     with pytest.raises((NotImplementedError, RuntimeError)):
         deepgemm.m_grouped_fp8_gemm_nt_masked((a[0].view(torch.uint8).view(FP8), a[1]), b, d, mm, 8)
     assert torch.equal(before, d)
+
+
+def test_op_size_printer_reports_operands_without_touching_the_call(capsys, monkeypatch):
+    """DEEPGEMM_PRINT_OP_SIZE: one '[DeepGEMM][size] <op> ...' line per call, filter honoured,
+    the wrapped function still gets its arguments (reference deepgemm/print_size.py:97-118)."""
+    import types
+    from deepgemm import print_size
+
+    seen = []
+    mod = types.ModuleType("fake_op")
+
+    def m_grouped_fake_masked(input, b_qweight, output, a_scale, b_scale, masked_m, expected_m, mode):
+        seen.append((tuple(input.shape), mode))
+        return output
+    m_grouped_fake_masked.__module__ = "fake_op"
+    mod.m_grouped_fake_masked = m_grouped_fake_masked
+    print_size.install_op_size_printer(mod, force=True)
+    print_size.install_op_size_printer(mod, force=True)        # wrapping twice is a no-op
+
+    a = torch.zeros(4, 64, 256, dtype=torch.int8)
+    w = torch.zeros(4, 2, 512, 128, dtype=torch.int8)
+    d = torch.zeros(4, 64, 512, dtype=torch.bfloat16)
+    mm = torch.tensor([1, 2, 3, 4], dtype=torch.int32)
+    monkeypatch.setenv("DEEPGEMM_PRINT_OP_SIZE_STATS", "1")
+    assert mod.m_grouped_fake_masked(a, w, d, None, None, mm, 64, mode=1002) is d
+    line = capsys.readouterr().out.strip()
+    assert line.startswith("[DeepGEMM][size] m_grouped_fake_masked input=(4,64,256):int8:cpu")
+    for field in ("output=(4,64,512):bfloat16:cpu", "a_scale=None", "E=4", "M=64", "N=512", "K=256",
+                  "mode=1002", "masked_m_sum=10", "masked_m_max=4"):
+        assert field in line, field
+    monkeypatch.setenv("DEEPGEMM_PRINT_OP_SIZE_FILTER", "contiguous")
+    mod.m_grouped_fake_masked(a, w, d, None, None, mm, 64, mode=1)
+    assert capsys.readouterr().out == ""
+    assert seen == [((4, 64, 256), 1002), ((4, 64, 256), 1)]
