@@ -23,7 +23,7 @@ STAMP_PATH = LIB_PATH + ".stamp"
 
 SOURCES = ["dg_api.cu"]
 HEADERS = ["dg_ptx.cuh", "dg_grouped_gemm.cuh", "dg_grouped_gemm_pair.cuh", "dg_grouped_gemm_w4.cuh",
-           "dg_pack.cuh", "dg_quant_group.cuh"]
+           "dg_pack.cuh", "dg_quant_group.cuh", "dg_moe_chain.cuh"]
 
 
 def _nvcc() -> str:

@@ -11,6 +11,7 @@
 #include "dg_grouped_gemm_pair.cuh"
 #include "dg_grouped_gemm_w4.cuh"
 #include "dg_pack.cuh"
+#include "dg_moe_chain.cuh"
 #include "dg_quant_group.cuh"
 
 namespace {
@@ -626,6 +627,7 @@ static int quant_group_common(const dg_quant_group_args* a, int32_t* scratch, vo
   dg::QuantGroupParams p{};
   p.rows = static_cast<const __nv_bfloat16*>(a->rows);
   p.expert = a->expert;
+  p.src_index = a->src_index;
   p.a_out = a->a_out;
   p.a_scale_out = a->a_scale_out;
   p.m_indices_out = a->m_indices_out;
@@ -652,6 +654,53 @@ int dg_quant_group_rows(const dg_quant_group_args* a, void* stream) {
       a->scratch_bytes < dg_quant_group_scratch_bytes(a->num_rows, a->num_groups))
     return DG_ERR_BAD_ARGUMENT;
   return quant_group_common(a, static_cast<int32_t*>(a->scratch), stream);
+}
+
+int dg_silu_mul_quant_rows(const dg_act_quant_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->kind != DG_KIND_E4M3 && a->kind != DG_KIND_I8) return DG_ERR_BAD_KIND;
+  if (a->num_rows < 0 || a->hidden <= 0 || a->hidden % 8 != 0) return DG_ERR_BAD_SHAPE;
+  if (a->hidden > DG_MAX_QUANT_HIDDEN) return DG_ERR_TOO_LARGE;
+  if (a->masked_m != nullptr && (a->max_m <= 0 || a->num_rows % a->max_m != 0)) return DG_ERR_BAD_SHAPE;
+  if (a->num_rows == 0) return DG_OK;
+  if (!a->x || !a->q_out || !a->scale_out) return DG_ERR_NULL_POINTER;
+  if (!aligned16(a->x) || ((uintptr_t)a->q_out & 7) != 0) return DG_ERR_BAD_ALIGNMENT;
+  ActQuantParams p{};
+  p.kind = a->kind;
+  p.rows = a->num_rows;
+  p.H = a->hidden;
+  p.max_m = a->max_m;
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.m_indices = a->m_indices;
+  p.masked_m = a->masked_m;
+  p.q_out = a->q_out;
+  p.scale_out = a->scale_out;
+  cudaError_t e = launch_act_quant(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
+int dg_combine_rows(const dg_combine_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->num_tokens < 0 || a->top_k <= 0 || a->n <= 0 || a->n % 8 != 0 || a->num_rows < 0)
+    return DG_ERR_BAD_SHAPE;
+  if (a->num_tokens == 0) return DG_OK;
+  if (!a->y || !a->src_row || !a->out) return DG_ERR_NULL_POINTER;
+  if (!aligned16(a->y) || !aligned16(a->out)) return DG_ERR_BAD_ALIGNMENT;
+  CombineParams p{};
+  p.tokens = a->num_tokens;
+  p.top_k = a->top_k;
+  p.n = a->n;
+  p.rows = a->num_rows;
+  p.y = static_cast<const __nv_bfloat16*>(a->y);
+  p.src_row = a->src_row;
+  p.weights = a->weights;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  cudaError_t e = launch_combine(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
 }
 
 // ---- library-owned scratch for dg_quant_group_rows_noalloc.  In host code the array's name

@@ -42,6 +42,7 @@ constexpr int kQgMaxVec = 8;        // 16-byte vectors per thread -> H <= 256 * 
 struct QuantGroupParams {
   const __nv_bfloat16* rows;
   const int32_t* expert;
+  const int32_t* src_index;  // nullable: input row r is rows[src_index[r]] instead of rows[r]
   void* a_out;
   float* a_scale_out;
   int32_t* m_indices_out;
@@ -149,7 +150,8 @@ __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGrou
   if (dest < 0) return;
 
   const int nvec = p.H / 8;  // 16-byte vectors of 8 bf16
-  const uint4* src = reinterpret_cast<const uint4*>(p.rows + (size_t)r * p.H);
+  const size_t src_row = p.src_index ? static_cast<size_t>(p.src_index[r]) : static_cast<size_t>(r);
+  const uint4* src = reinterpret_cast<const uint4*>(p.rows + src_row * p.H);
   uint4 v[kQgMaxVec];
   float amax = 0.0f;
 #pragma unroll

@@ -27,6 +27,8 @@ EXPORTED_SYMBOLS = (
     "dg_quant_group_rows",
     "dg_quant_group_scratch_bytes",
     "dg_quant_group_rows_noalloc",
+    "dg_silu_mul_quant_rows",
+    "dg_combine_rows",
     "dg_pack_weight",
     "dg_unpack_weight",
     "dg_query",
@@ -116,6 +118,34 @@ class QuantGroupArgs(C.Structure):
         ("m_total_out", C.c_void_p),
         ("scratch", C.c_void_p),
         ("scratch_bytes", C.c_size_t),
+        ("src_index", C.c_void_p),
+    ]
+
+
+class ActQuantArgs(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("num_rows", C.c_int32),
+        ("hidden", C.c_int32),
+        ("max_m", C.c_int32),
+        ("x", C.c_void_p),
+        ("m_indices", C.c_void_p),
+        ("masked_m", C.c_void_p),
+        ("q_out", C.c_void_p),
+        ("scale_out", C.c_void_p),
+    ]
+
+
+class CombineArgs(C.Structure):
+    _fields_ = [
+        ("num_tokens", C.c_int32),
+        ("top_k", C.c_int32),
+        ("n", C.c_int32),
+        ("num_rows", C.c_int32),
+        ("y", C.c_void_p),
+        ("src_row", C.c_void_p),
+        ("weights", C.c_void_p),
+        ("out", C.c_void_p),
     ]
 
 
@@ -143,6 +173,10 @@ def _load() -> C.CDLL:
     lib.dg_quant_group_rows_noalloc.restype = C.c_int
     lib.dg_quant_group_scratch_bytes.argtypes = [C.c_int32, C.c_int32]
     lib.dg_quant_group_scratch_bytes.restype = C.c_size_t
+    lib.dg_silu_mul_quant_rows.argtypes = [C.POINTER(ActQuantArgs), C.c_void_p]
+    lib.dg_silu_mul_quant_rows.restype = C.c_int
+    lib.dg_combine_rows.argtypes = [C.POINTER(CombineArgs), C.c_void_p]
+    lib.dg_combine_rows.restype = C.c_int
     lib.dg_query.argtypes = [C.c_int32]
     lib.dg_query.restype = C.c_int64
     lib.dg_strerror.argtypes = [C.c_int]

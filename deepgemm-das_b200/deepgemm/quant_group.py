@@ -25,16 +25,24 @@ def quant_group_capacity(num_rows: int, num_groups: int, align: int = 256) -> in
 
 def quantize_group_rows(rows: torch.Tensor, expert: torch.Tensor, num_groups: int, *,
                         kind: str = "fp8", align: int = 256, m_cap: Optional[int] = None,
-                        scratch: Optional[torch.Tensor] = None
+                        scratch: Optional[torch.Tensor] = None,
+                        src_index: Optional[torch.Tensor] = None
                         ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """rows bf16 [R, H] (CUDA), expert int32 [R] -> (a [m_cap, H] e4m3 / int8, a_scale fp32
     [m_cap], m_indices int32 [m_cap], dest int32 [R], m_total int32 [1]); all on the device,
-    no synchronisation.  Pass the results to the contiguous grouped GEMM as they are."""
+    no synchronisation.  Pass the results to the contiguous grouped GEMM as they are.  With
+    ``src_index`` (int32 [R], entries in [0, rows.shape[0])) row r is read from
+    ``rows[src_index[r]]``, so the top-k copies of a token need not be materialised."""
     if not rows.is_cuda:
         raise RuntimeError("quantize_group_rows: rows must be a CUDA tensor (there is no CPU implementation)")
     if rows.dim() != 2 or rows.dtype != torch.bfloat16 or not rows.is_contiguous():
         raise ValueError(f"rows must be a contiguous bf16 [R, H] tensor, got {rows.dtype} {tuple(rows.shape)}")
     r, h = (int(v) for v in rows.shape)
+    if src_index is not None:
+        if src_index.dtype != torch.int32 or src_index.dim() != 1:
+            raise ValueError("src_index must be an int32 vector")
+        src_index = src_index.contiguous()
+        r = int(src_index.numel())
     if expert.numel() != r:
         raise ValueError(f"expert must have {r} entries, got {expert.numel()}")
     if expert.dtype != torch.int32:
@@ -61,7 +69,8 @@ def quantize_group_rows(rows: torch.Tensor, expert: torch.Tensor, num_groups: in
         rows=rows.data_ptr(), expert=expert.data_ptr(), a_out=a.data_ptr(),
         a_scale_out=a_scale.data_ptr(), m_indices_out=m_indices.data_ptr(), dest_out=dest.data_ptr(),
         m_total_out=m_total.data_ptr(), scratch=scratch.data_ptr(),
-        scratch_bytes=scratch.numel() * scratch.element_size())
+        scratch_bytes=scratch.numel() * scratch.element_size(),
+        src_index=src_index.data_ptr() if src_index is not None else None)
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         _cabi.check(_cabi.lib.dg_quant_group_rows(C.byref(args), C.c_void_p(stream)), "dg_quant_group_rows")

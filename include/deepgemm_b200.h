@@ -239,6 +239,9 @@ typedef struct dg_quant_group_args {
   int32_t*       m_total_out;   /* NULL, or one int: rows in use (multiple of align, <= m_cap) */
   void*          scratch;       /* device scratch of dg_quant_group_scratch_bytes() bytes */
   size_t         scratch_bytes;
+  const int32_t* src_index;     /* NULL, or [R]: input row r is rows[src_index[r]] (entries must be
+                                   valid rows of `rows`), so that the top-k copies of a token can
+                                   all read the token's one row */
 } dg_quant_group_args;
 
 #define DG_MAX_QUANT_HIDDEN 16384
@@ -251,6 +254,50 @@ DG_API size_t dg_quant_group_scratch_bytes(int32_t num_rows, int32_t num_groups)
  * (op_test/contiguous_w8a8_int8_common.py:38-62 builds the layout, op_test/quant_utils.py:4-19
  * quantises); the arithmetic of the latter is reproduced bit for bit. */
 DG_API int dg_quant_group_rows(const dg_quant_group_args* args, void* stream);
+
+/* Arguments of the step between the gate/up GEMM and the down GEMM of an MoE layer:
+ *   act[r][c]   = bf16( bf16(silu(x[r][c])) * x[r][H + c] )      (gate | up halves of a row)
+ *   scale_out[r] = absmax(act[r]) / qmax,   q_out[r][c] = quantise(act[r][c] * qmax / absmax)
+ * with the same per-row quantiser as dg_quant_group_rows.  Rows marked unused are skipped and
+ * their outputs left untouched: m_indices[r] < 0 (contiguous layout), or row (r % max_m) >=
+ * masked_m[r / max_m] (masked layout, num_rows = groups * max_m). */
+typedef struct dg_act_quant_args {
+  int32_t kind;              /* element type of q_out: DG_KIND_E4M3 or DG_KIND_I8 */
+  int32_t num_rows;
+  int32_t hidden;            /* H (columns of q_out), multiple of 8, <= DG_MAX_QUANT_HIDDEN */
+  int32_t max_m;             /* rows per group when masked_m is given, else ignored */
+  const void*    x;          /* [num_rows][2H] bf16 */
+  const int32_t* m_indices;  /* NULL, or [num_rows] */
+  const int32_t* masked_m;   /* NULL, or [num_rows / max_m] */
+  void*          q_out;      /* [num_rows][H] */
+  float*         scale_out;  /* [num_rows] */
+} dg_act_quant_args;
+
+/* SiLU(gate) * up fused with the per-row requantisation that feeds the down GEMM (one launch).
+ * No kernel of the reference does this step: its second-stage op
+ * (deepgemm/moe_marlin_prefill.py:15-56) takes activations that the serving framework has
+ * already activated and quantised; the quantiser formula is op_test/quant_utils.py:4-19. */
+DG_API int dg_silu_mul_quant_rows(const dg_act_quant_args* args, void* stream);
+
+/* Arguments of the top-k reduction after the down GEMM:
+ *   out[t][:] = bf16( sum_j weights[t][j] * y[src_row[t][j]][:] ),  j = 0..top_k-1 in order,
+ * fp32 accumulation; entries of src_row outside [0, num_rows) contribute nothing. */
+typedef struct dg_combine_args {
+  int32_t num_tokens;
+  int32_t top_k;
+  int32_t n;                 /* columns, multiple of 8 */
+  int32_t num_rows;          /* rows of y */
+  const void*    y;          /* [num_rows][n] bf16 */
+  const int32_t* src_row;    /* [num_tokens][top_k] */
+  const float*   weights;    /* NULL (all ones), or [num_tokens][top_k] */
+  void*          out;        /* [num_tokens][n] bf16 */
+} dg_combine_args;
+
+/* Weighted sum of each token's top-k expert outputs (one launch).  The reference folds the
+ * routing weight into its second-stage GEMM's row scale
+ * (csrc/include/moe_marlin/moe_marlin_prefill_down_fp8_device.inc.h:114-119) and leaves the
+ * sum over the top-k rows to the caller; here both happen in this reduction. */
+DG_API int dg_combine_rows(const dg_combine_args* args, void* stream);
 
 /* Same operation as dg_quant_group_rows, for callers that may not allocate device memory at
  * all: code that runs inside a serving engine after its memory pool has been frozen, plugins

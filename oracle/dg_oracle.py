@@ -199,3 +199,51 @@ def topk_routing_counts(num_tokens: int, num_experts: int, top_k: int,
         torch.randn(num_tokens, num_experts, generator=gen) + bias
     picks = scores.topk(top_k, dim=1).indices.flatten()
     return torch.bincount(picks, minlength=num_experts)
+
+
+# ----------------------------------------------------------------------------- MoE layer chain
+def ref_silu_mul(x: torch.Tensor) -> torch.Tensor:
+    """bf16 [.., 2H] (gate | up) -> bf16 [.., H], the unfused bf16 computation
+    ``silu(gate) * up``: silu evaluated in fp32 and rounded to bf16, then the product rounded to
+    bf16.  The reference has no such function (its second-stage op takes activated rows,
+    deepgemm/moe_marlin_prefill.py:15-56); this defines what the fused kernel must produce."""
+    h = x.shape[-1] // 2
+    g, u = x[..., :h].float(), x[..., h:].float()
+    s = (g / (1.0 + torch.exp(-g))).bfloat16().float()
+    return (s * u).bfloat16()
+
+
+def ref_combine(y: torch.Tensor, src_row: torch.Tensor, weights: Optional[torch.Tensor]) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * y[src_row[t, j]] in float64 (rounded to bf16 by the caller's
+    comparison); negative / out-of-range rows contribute nothing.  The routing-weight multiply is
+    the one at csrc/include/moe_marlin/moe_marlin_prefill_down_fp8_device.inc.h:114-119."""
+    t, k = src_row.shape
+    out = torch.zeros(t, y.shape[1], dtype=torch.float64)
+    for j in range(k):
+        ok = (src_row[:, j] >= 0) & (src_row[:, j] < y.shape[0])
+        rows = y[src_row[:, j].clamp(0, max(y.shape[0] - 1, 0)).long()].double()
+        w = weights[:, j].double() if weights is not None else torch.ones(t, dtype=torch.float64)
+        out += torch.where(ok[:, None], rows * w[:, None], torch.zeros_like(rows))
+    return out
+
+
+def ref_moe_layer(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                  w13: torch.Tensor, w13_scale: torch.Tensor, w2: torch.Tensor, w2_scale: torch.Tensor,
+                  kind: str = "fp8") -> torch.Tensor:
+    """One MoE layer with quantised experts, step by step with the reference formulas: per-token
+    quantise (op_test/quant_utils.py:4-19) -> dequant-matmul (masked_w8a8_int8_common.py:55-69)
+    -> silu*mul -> per-token quantise -> dequant-matmul -> weighted top-k sum.  float64 result."""
+    quant = per_token_quant_fp8 if kind == "fp8" else per_token_quant_int8
+    qa, sa = quant(hidden)
+    t, k = topk_ids.shape
+    y = torch.zeros(t * k, w2.shape[1], dtype=torch.bfloat16)
+    for e in range(w13.shape[0]):
+        pairs = torch.nonzero(topk_ids.reshape(-1) == e).flatten()
+        if pairs.numel() == 0:
+            continue
+        tok = pairs // k
+        h13 = ((qa[tok].float() @ w13[e].float().t()) * sa[tok].reshape(-1, 1) * w13_scale[e].reshape(1, -1)).bfloat16()
+        q, s = quant(ref_silu_mul(h13))
+        y[pairs] = ((q.float() @ w2[e].float().t()) * s.reshape(-1, 1) * w2_scale[e].reshape(1, -1)).bfloat16()
+    src = torch.arange(t * k, dtype=torch.int32).view(t, k)
+    return ref_combine(y, src, topk_weights)

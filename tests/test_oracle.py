@@ -91,3 +91,27 @@ def test_contiguous_layout_builder():
     assert m == 256 + 0 + 256 + 512
     assert idx[:3].tolist() == [0, 0, 0] and int(idx[3]) == -1
     assert int((idx == 3).sum()) == 257 and int((idx == -1).sum()) == m - 3 - 256 - 257
+
+
+def test_chain_oracle_matches_the_unfused_torch_ops():
+    """ref_silu_mul is torch's own bf16 `silu(gate) * up` (two roundings); ref_combine is a plain
+    weighted gather-sum; ref_moe_layer with one expert and top-1 reduces to two dequant matmuls."""
+    gen = torch.Generator().manual_seed(5)
+    x = (torch.randn(64, 256, generator=gen) * 3).bfloat16()
+    assert torch.equal(O.ref_silu_mul(x), torch.nn.functional.silu(x[:, :128]) * x[:, 128:])
+    y = torch.randn(10, 16, generator=gen).bfloat16()
+    src = torch.tensor([[0, 9], [3, -1], [12, 2]], dtype=torch.int32)
+    w = torch.tensor([[0.5, 2.0], [1.0, 7.0], [3.0, 0.25]])
+    want = torch.stack([0.5 * y[0].double() + 2.0 * y[9].double(), y[3].double(), 0.25 * y[2].double()])
+    assert torch.allclose(O.ref_combine(y, src, w), want, rtol=0, atol=1e-12)
+    hidden = torch.randn(7, 64, generator=gen).bfloat16()
+    w13, s13 = O.per_token_quant_int8(torch.randn(1, 32, 64, generator=gen))
+    w2, s2 = O.per_token_quant_int8(torch.randn(1, 64, 16, generator=gen))
+    ids = torch.zeros(7, 1, dtype=torch.int64)
+    out = O.ref_moe_layer(hidden, ids, torch.full((7, 1), 2.0), w13, s13.reshape(1, -1), w2,
+                          s2.reshape(1, -1), kind="int8")
+    qa, sa = O.per_token_quant_int8(hidden)
+    h = O.ref_masked_scaled(qa[None], w13, sa.reshape(1, -1, 1), s13.reshape(1, -1, 1))[0]
+    q, s = O.per_token_quant_int8(O.ref_silu_mul(h))
+    y2 = O.ref_masked_scaled(q[None], w2, s.reshape(1, -1, 1), s2.reshape(1, -1, 1))[0]
+    assert torch.equal(out.float().bfloat16(), (2.0 * y2.double()).float().bfloat16())
