@@ -27,6 +27,7 @@ class DispatchPlan:
     send_expert: torch.Tensor     # [S] global expert id of each sent row (non-decreasing)
     send_splits: list             # rows sent to each rank
     counts_per_expert: torch.Tensor  # [E] rows this rank sends to each global expert
+    send_pair: Optional[torch.Tensor] = None  # [S] index t * top_k + j of the pair each sent row is
 
 
 def route_topk(logits: torch.Tensor, top_k: int) -> torch.Tensor:
@@ -43,17 +44,19 @@ def build_dispatch_plan(topk_ids: torch.Tensor, num_experts: int, world: int) ->
     send_token = torch.div(order, k, rounding_mode="floor")
     counts = torch.bincount(flat, minlength=num_experts)
     per_rank = counts.view(world, num_experts // world).sum(dim=1)
-    return DispatchPlan(send_token, send_expert, [int(x) for x in per_rank.tolist()], counts)
+    return DispatchPlan(send_token, send_expert, [int(x) for x in per_rank.tolist()], counts, order)
 
 
 def dispatch_tokens(hidden: torch.Tensor, plan: DispatchPlan, num_experts: int, rank: int,
-                    world: int, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+                    world: int, group=None, return_splits: bool = False):
     """All-to-all of the routed rows.  Returns (rows [R, H] received by this rank, in source-rank
-    order, local expert id [R] of each)."""
+    order, local expert id [R] of each) and, with ``return_splits``, the rows received from each
+    rank (what ``return_rows`` needs to send results back)."""
     e_local = num_experts // world
     send_rows = hidden.index_select(0, plan.send_token)
     if world == 1:
-        return send_rows, plan.send_expert.clone()
+        res = (send_rows, plan.send_expert.clone())
+        return res + (list(plan.send_splits),) if return_splits else res
     import torch.distributed as dist
     # 1) counts: rank r receives, from every source, its rows-per-local-expert vector
     send_counts = plan.counts_per_expert.to(torch.int64).contiguous()          # [world * e_local]
@@ -69,7 +72,22 @@ def dispatch_tokens(hidden: torch.Tensor, plan: DispatchPlan, num_experts: int, 
     # local expert of every received row: per source rank, experts ascend with the given counts
     ids = torch.arange(e_local, device=hidden.device).repeat(world)
     recv_expert = torch.repeat_interleave(ids, recv_counts.reshape(-1).to(hidden.device))
+    if return_splits:
+        return recv_rows, recv_expert, recv_splits
     return recv_rows, recv_expert
+
+
+def return_rows(rows_out: torch.Tensor, recv_splits: list, send_splits: list, world: int,
+                group=None) -> torch.Tensor:
+    """The reverse all-to-all: ``rows_out`` [R, N] holds one result row per received row, in the
+    order they were received; returns [S, N], one per row this rank sent, in the order sent."""
+    if world == 1:
+        return rows_out
+    import torch.distributed as dist
+    back = torch.empty((sum(send_splits), rows_out.shape[1]), dtype=rows_out.dtype, device=rows_out.device)
+    dist.all_to_all_single(back, rows_out.contiguous(), output_split_sizes=list(send_splits),
+                           input_split_sizes=list(recv_splits), group=group)
+    return back
 
 
 def group_and_pad(rows: torch.Tensor, expert_local: torch.Tensor, e_local: int, align: int = 256
@@ -108,6 +126,35 @@ def ep_gate_up_forward(hidden: torch.Tensor, topk_ids: torch.Tensor, b_packed: t
     out = torch.zeros((a.shape[0], b_scale.shape[1]), dtype=torch.bfloat16, device=hidden.device)
     m_grouped_fp8_gemm_nt_contiguous((a, a_scale), (b_packed, b_scale), out, m_indices)
     return out, m_indices, recv_expert, dest
+
+
+def ep_moe_forward(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                   w13, w2, num_experts: int, rank: int, world: int, group=None, *,
+                   kind: str = "fp8", expert_mlp=None, combine=None) -> torch.Tensor:
+    """A whole expert-parallel MoE layer for this rank's tokens: dispatch all-to-all -> fused
+    quantise/group -> gate/up GEMM -> SiLU*up + requantise -> down GEMM -> reverse all-to-all ->
+    weighted top-k sum.  ``w13`` / ``w2`` are (packed weight, scale) of this rank's experts.
+    ``expert_mlp(rows, local_expert) -> [R, N]`` and ``combine(y, src_row, weights) -> [T, N]``
+    replace the CUDA steps (the CPU tests of the communication pattern pass torch functions)."""
+    t, k = topk_ids.shape
+    e_local = num_experts // world
+    plan = build_dispatch_plan(topk_ids, num_experts, world)
+    rows, recv_expert, recv_splits = dispatch_tokens(hidden, plan, num_experts, rank, world, group,
+                                                     return_splits=True)
+    if expert_mlp is None:
+        from .moe_chain import expert_mlp_contiguous
+        from .quant_group import quantize_group_rows
+        a, a_scale, m_indices, dest, _ = quantize_group_rows(rows, recv_expert.to(torch.int32), e_local,
+                                                             kind=kind)
+        y = expert_mlp_contiguous(a, a_scale, m_indices, w13, w2, kind=kind).index_select(0, dest.long())
+    else:
+        y = expert_mlp(rows, recv_expert)
+    back = return_rows(y, recv_splits, plan.send_splits, world, group)      # row i = pair send_pair[i]
+    src_row = torch.empty(t * k, dtype=torch.int32, device=hidden.device)
+    src_row[plan.send_pair] = torch.arange(t * k, dtype=torch.int32, device=hidden.device)
+    if combine is None:
+        from .moe_chain import combine_rows as combine
+    return combine(back, src_row.view(t, k), topk_weights.to(torch.float32))
 
 
 def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup: int = 3,

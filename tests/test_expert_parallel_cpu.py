@@ -104,3 +104,56 @@ def test_two_rank_dispatch_matches_single_process_routing():
         rows, expert_local = got[r]
         assert torch.equal(rows, torch.cat(want_rows))
         assert torch.equal(expert_local, torch.cat(want_exp))
+
+
+def _toy_mlp(rows, local_expert, first_expert):
+    """Stand-in for the experts' two GEMMs: depends on the row and on the global expert id."""
+    return rows.float() * (1.0 + (local_expert + first_expert).float()[:, None])
+
+
+def _toy_combine(y, src_row, weights):
+    return (y[src_row.long()] * weights[:, :, None]).sum(dim=1)
+
+
+def _layer_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        hidden, topk = _inputs(rank)
+        w = torch.softmax(torch.randn(T, TOPK, generator=torch.Generator().manual_seed(70 + rank)), dim=1)
+        first = rank * (E // world)
+        out = ep.ep_moe_forward(hidden, topk, w, None, None, E, rank, world,
+                                expert_mlp=lambda r, e: _toy_mlp(r, e, first), combine=_toy_combine)
+        q.put((rank, out))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_two_rank_layer_returns_every_pair_to_its_token():
+    """dispatch -> per-expert function -> reverse all-to-all -> weighted sum over two gloo ranks
+    equals the direct per-token computation (the GEMMs are replaced by an expert-dependent toy
+    function, so a row sent to the wrong expert or returned to the wrong token shows)."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_layer_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=90) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    for r in range(world):
+        hidden, topk = _inputs(r)
+        w = torch.softmax(torch.randn(T, TOPK, generator=torch.Generator().manual_seed(70 + r)), dim=1)
+        want = (hidden.float()[:, None, :] * (1.0 + topk.float())[:, :, None] * w[:, :, None]).sum(dim=1)
+        assert torch.allclose(got[r], want, rtol=1e-6, atol=1e-6), f"rank {r}"
+    # world size 1 takes the same code path without communication
+    hidden, topk = _inputs(0)
+    w = torch.ones(T, TOPK)
+    out = ep.ep_moe_forward(hidden, topk, w, None, None, E, 0, 1,
+                            expert_mlp=lambda r, e: _toy_mlp(r, e, 0), combine=_toy_combine)
+    assert torch.allclose(out, (hidden.float()[:, None, :] * (1.0 + topk.float())[:, :, None]).sum(dim=1))

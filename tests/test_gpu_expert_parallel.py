@@ -113,3 +113,85 @@ def test_two_ranks_match_single_rank_rows():
             want_rows.append(out[dest.long()].cpu())
         want = torch.cat(want_rows)
         assert torch.equal(got[r][0].view(torch.int16), want.view(torch.int16)), f"rank {r} rows differ"
+
+
+# ---------------------------------------------------------------- whole layer (gate/up -> down)
+INTER = 128
+
+
+def _layer_weights():
+    g = torch.Generator().manual_seed(6)
+    w13, s13 = O.per_token_quant_fp8(torch.randn(E, 2 * INTER, H, generator=g) * 0.05)
+    w2, s2 = O.per_token_quant_fp8(torch.randn(E, H, INTER, generator=g) * 0.05)
+    return w13, s13.reshape(E, -1), w2, s2.reshape(E, -1)
+
+
+def _layer_tokens(rank):
+    hidden, topk = _tokens(rank)
+    w = torch.softmax(torch.randn(T, TOPK, generator=torch.Generator().manual_seed(80 + rank)), dim=1)
+    return hidden, topk, w
+
+
+def _run_layer(rank, world, dev):
+    w13, s13, w2, s2 = _layer_weights()
+    e_local = E // world
+    sl = slice(rank * e_local, (rank + 1) * e_local)
+    pk = deepgemm.marlin_fp8_contiguous_weight
+    hidden, topk, w = _layer_tokens(rank)
+    out = ep.ep_moe_forward(hidden.to(dev), topk.to(dev), w.to(dev),
+                            (pk(w13[sl].clone().to(dev)), s13[sl].to(dev)),
+                            (pk(w2[sl].clone().to(dev)), s2[sl].to(dev)), E, rank, world)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def test_single_rank_layer_matches_oracle():
+    out = _run_layer(0, 1, torch.device("cuda", 0))
+    hidden, topk, w = _layer_tokens(0)
+    ref = O.ref_moe_layer(hidden, topk, w, *_layer_weights())
+    assert_calc_diff(out, ref.float(), 1e-3, "expert-parallel layer, one rank")    # calc_diff < 1e-3
+
+
+def _layer_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        q.put((rank, _run_layer(rank, world, dev)))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_rank_layer_matches_one_gpu_layer():
+    """Every token's output from the two-rank layer equals, bit for bit, what one GPU holding all
+    experts computes for the same token (each pair's row depends only on its token and expert,
+    and the top-k sum runs in the same order)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_layer_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=240) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    w13, s13, w2, s2 = _layer_weights()
+    pk = deepgemm.marlin_fp8_contiguous_weight
+    dev = torch.device("cuda", 0)
+    for r in range(world):
+        hidden, topk, w = _layer_tokens(r)
+        want = deepgemm.moe_forward(hidden.to(dev), topk.to(dev), w.to(dev),
+                                    (pk(w13.clone().to(dev)), s13.to(dev)),
+                                    (pk(w2.clone().to(dev)), s2.to(dev))).cpu()
+        assert torch.equal(got[r].view(torch.int16), want.view(torch.int16)), f"rank {r} tokens differ"
