@@ -59,15 +59,33 @@ __device__ __forceinline__ uint2 quantise8(const float (&x)[8]) {
 }
 
 // silu(g) * u with the roundings of the unfused bf16 computation: silu is rounded to bf16,
-// then the product is.
+// then the product is.  exp and the division use the fast hardware approximations (relative
+// error about 2^-21): the result is rounded to bf16 (2^-9) right after, so this moves an
+// output only when the exact value lies within that error of a rounding boundary.
 __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
-  const float s = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
+  const float s = __bfloat162float(__float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g))));
   return __bfloat162float(__float2bfloat16_rn(s * u));
 }
 
-template <int KIND>
-__global__ void __launch_bounds__(kQgThreads) act_quant_kernel(const ActQuantParams p) {
-  __shared__ float red[kQgThreads / 32];
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if (THREADS == 32) return v;
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float m = red[0];
+#pragma unroll
+  for (int w = 1; w < THREADS / 32; ++w) m = fmaxf(m, red[w]);
+  return m;
+}
+
+// One block of THREADS threads per row, at most MAXVEC 16-byte vectors of the output row per
+// thread.  Short rows use small blocks so that each thread keeps several loads in flight and
+// many rows are resident per SM.
+template <int KIND, int THREADS, int MAXVEC>
+__global__ void __launch_bounds__(THREADS) act_quant_kernel(const ActQuantParams p) {
+  __shared__ float red[THREADS / 32];
   const int r = blockIdx.x;
   if (p.m_indices != nullptr && p.m_indices[r] < 0) return;
   if (p.masked_m != nullptr && (r % p.max_m) >= p.masked_m[r / p.max_m]) return;
@@ -75,16 +93,23 @@ __global__ void __launch_bounds__(kQgThreads) act_quant_kernel(const ActQuantPar
   const int nvec = p.H / 8;
   const uint4* gate = reinterpret_cast<const uint4*>(p.x + (size_t)r * 2 * p.H);
   const uint4* up = gate + nvec;
-  float act[kQgMaxVec][8];
+  uint4 gv[MAXVEC], uv[MAXVEC];
+#pragma unroll
+  for (int i = 0; i < MAXVEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+    if (idx < nvec) {
+      gv[i] = __ldg(gate + idx);
+      uv[i] = __ldg(up + idx);
+    }
+  }
+  float act[MAXVEC][8];
   float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kQgMaxVec; ++i) {
-    const int idx = threadIdx.x + i * kQgThreads;
+  for (int i = 0; i < MAXVEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
     if (idx < nvec) {
-      const uint4 gv = __ldg(gate + idx);
-      const uint4 uv = __ldg(up + idx);
-      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
-      const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv[i]);
+      const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv[i]);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const float2 g = __bfloat1622float2(gh[k]);
@@ -95,14 +120,14 @@ __global__ void __launch_bounds__(kQgThreads) act_quant_kernel(const ActQuantPar
       }
     }
   }
-  amax = fmaxf(qg_block_max(amax, red), 1e-10f);
+  amax = fmaxf(block_max<THREADS>(amax, red), 1e-10f);
   constexpr float kQmax = (KIND == DG_KIND_E4M3) ? 448.0f : 127.0f;
   const float inv = __fmul_rn(__frcp_rn(amax), kQmax);  // as in qg_quantise_kernel
   if (threadIdx.x == 0) p.scale_out[r] = __fdiv_rn(amax, kQmax);
   uint2* dst = reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.q_out) + (size_t)r * p.H);
 #pragma unroll
-  for (int i = 0; i < kQgMaxVec; ++i) {
-    const int idx = threadIdx.x + i * kQgThreads;
+  for (int i = 0; i < MAXVEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
     if (idx < nvec) {
       float x[8];
 #pragma unroll
@@ -112,12 +137,24 @@ __global__ void __launch_bounds__(kQgThreads) act_quant_kernel(const ActQuantPar
   }
 }
 
+template <int KIND>
+inline void launch_act_quant_kind(const ActQuantParams& p, cudaStream_t stream) {
+  if (p.H <= 1024)
+    act_quant_kernel<KIND, 32, 4><<<p.rows, 32, 0, stream>>>(p);
+  else if (p.H <= 2048)
+    act_quant_kernel<KIND, 64, 4><<<p.rows, 64, 0, stream>>>(p);
+  else if (p.H <= 4096)
+    act_quant_kernel<KIND, 128, 4><<<p.rows, 128, 0, stream>>>(p);
+  else
+    act_quant_kernel<KIND, 256, DG_MAX_QUANT_HIDDEN / 8 / 256><<<p.rows, 256, 0, stream>>>(p);
+}
+
 inline cudaError_t launch_act_quant(const ActQuantParams& p, cudaStream_t stream) {
   if (p.rows == 0) return cudaSuccess;
   if (p.kind == DG_KIND_E4M3)
-    act_quant_kernel<DG_KIND_E4M3><<<p.rows, kQgThreads, 0, stream>>>(p);
+    launch_act_quant_kind<DG_KIND_E4M3>(p, stream);
   else
-    act_quant_kernel<DG_KIND_I8><<<p.rows, kQgThreads, 0, stream>>>(p);
+    launch_act_quant_kind<DG_KIND_I8>(p, stream);
   return cudaGetLastError();
 }
 

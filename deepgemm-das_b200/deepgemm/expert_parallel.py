@@ -198,7 +198,8 @@ def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup:
     e0, e1 = ev(), ev()
     e0.record()
     for _ in range(steps):
-        rows, recv_expert = dispatch_tokens(hidden, plan, num_experts, rank, world)
+        rows, recv_expert, recv_splits = dispatch_tokens(hidden, plan, num_experts, rank, world,
+                                                         return_splits=True)
     e1.record()
     sync()
     a2a_ms = e0.elapsed_time(e1) / steps
@@ -212,7 +213,7 @@ def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup:
     e0, e1 = ev(), ev()
     e0.record()
     for _ in range(steps):
-        a, a_scale, m_indices, _, _ = quantize_group_rows(rows, recv_expert, e_local)
+        a, a_scale, m_indices, dest, _ = quantize_group_rows(rows, recv_expert, e_local)
     e1.record()
     torch.cuda.synchronize()
     prep_ms = e0.elapsed_time(e1) / steps
@@ -231,7 +232,51 @@ def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup:
     sync()
     gemm_ms = e0.elapsed_time(e1) / steps
 
+    # ---- the rest of the layer: SiLU*up + requantise, down GEMM, reverse all-to-all, combine
+    from .moe_chain import combine_rows, silu_mul_quant
+
+    def timed(fn, collective=False):
+        for _ in range(warmup):
+            fn()
+        sync() if collective else torch.cuda.synchronize()
+        t0, t1 = ev(), ev()
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        sync() if collective else torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / steps
+
+    inter = n // 2
+    w2 = torch.empty(e_local, hidden_k, inter, dtype=torch.float8_e4m3fn, device=device)
+    w2_scale = torch.empty(e_local, hidden_k, dtype=torch.float32, device=device)
+    for g in range(e_local):
+        q, s = per_token_quant_fp8(torch.randn(hidden_k, inter, device=device, generator=gen))
+        w2[g], w2_scale[g] = q, s.reshape(hidden_k)
+    w2_packed = marlin_fp8_contiguous_weight(w2)
+    act_out = (torch.zeros((a.shape[0], inter), dtype=torch.float8_e4m3fn, device=device),
+               torch.zeros((a.shape[0],), dtype=torch.float32, device=device))
+    act_ms = timed(lambda: silu_mul_quant(out, kind="fp8", m_indices=m_indices, out=act_out))
+    y = torch.zeros((a.shape[0], hidden_k), dtype=torch.bfloat16, device=device)
+    down_ms = timed(lambda: m_grouped_fp8_gemm_nt_contiguous(act_out, (w2_packed, w2_scale), y, m_indices),
+                    collective=True)
+    y_recv = y.index_select(0, dest.long())
+    back_holder = {}
+
+    def send_back():
+        back_holder["rows"] = return_rows(y_recv, recv_splits, plan.send_splits, world)
+    back_ms = timed(send_back, collective=True)
+    src_row = torch.empty(tokens * top_k, dtype=torch.int32, device=device)
+    src_row[plan.send_pair] = torch.arange(tokens * top_k, dtype=torch.int32, device=device)
+    weights = torch.softmax(torch.randn(tokens, top_k, device=device, generator=gen), dim=1)
+    final = torch.empty((tokens, hidden_k), dtype=torch.bfloat16, device=device)
+    combine_ms = timed(lambda: combine_rows(back_holder["rows"], src_row.view(tokens, top_k), weights, out=final))
+
     valid = int((m_indices >= 0).sum())
+    chain = torch.tensor([act_ms, down_ms, back_ms, combine_ms], device=device, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(chain, op=dist.ReduceOp.MAX)
+    act_ms, down_ms, back_ms, combine_ms = (float(x) for x in chain.tolist())
     stats = torch.tensor([a2a_ms, gemm_ms, prep_ms], device=device, dtype=torch.float64)
     flops = torch.tensor([2.0 * valid * n * hidden_k], device=device, dtype=torch.float64)
     sent_remote = sum(s for r, s in enumerate(plan.send_splits) if r != rank) * hidden_k * 2
@@ -249,6 +294,15 @@ def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup:
         "all_to_all_ms_max_over_ranks": a2a_ms, "quantise_group_ms_max_over_ranks": prep_ms,
         "all_to_all_remote_bytes_max_per_rank": float(sent),
         "valid_rows_this_rank": valid, "m_total_this_rank": int(a.shape[0])}
+    down_flops = torch.tensor([2.0 * valid * hidden_k * inter], device=device, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(down_flops, op=dist.ReduceOp.SUM)
+    res["down_chain"] = {
+        "silu_mul_quant_ms": act_ms,
+        "silu_mul_quant_gbs_this_rank": valid * (n * 2 + inter + 4) / (act_ms * 1e-3) / 1e9,
+        "down_gemm_ms": down_ms, "down_gemm_tflops_aggregate": float(down_flops) / (down_ms * 1e-3) / 1e12,
+        "combine_all_to_all_ms": back_ms, "combine_sum_ms": combine_ms,
+        "combine_sum_gbs_this_rank": tokens * (top_k + 1) * hidden_k * 2 / (combine_ms * 1e-3) / 1e9}
     if float(sent) > 0:
         res["all_to_all_gbs_per_rank"] = float(sent) / (a2a_ms * 1e-3) / 1e9
     if peaks:
