@@ -132,6 +132,8 @@ struct Problem {
   const int32_t* offsets;
   int G, M, N, K, block_n, expected_m;
   int narrow;  // filled by validate_and_launch: KernelParams::narrow for the BN = 128 tile
+  int dense;     // 1: dg_dense_gemm (row-major weights, no masked_m, any N, out_kind honoured)
+  int out_kind;  // DG_OUT_BF16 / DG_OUT_F16 / DG_OUT_F32
   void* debug_acc;
   int32_t* status;
 };
@@ -162,6 +164,8 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.d = static_cast<__nv_bfloat16*>(pr.d);
   p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
   p.status = pr.status;
+  p.b_rowmajor = pr.dense;
+  p.out_kind = pr.out_kind;
 
   const long long max_blocks = pr.mode == MODE_MASKED    ? (long long)pr.G * p.m_blocks
                                : pr.mode == MODE_COMPACT ? (long long)p.m_blocks + pr.G
@@ -200,27 +204,24 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   }
   if (rc != DG_OK) return rc;
   // B (packed): a flat list of G*kblocks*N rows of 128 bytes, so a BN-row box is one
-  // contiguous span.
+  // contiguous span.  Dense GEMM: plain [G*N][K] rows, the box walks along K.
+  const uint64_t b_dims[2] = {pr.dense ? (uint64_t)pr.K : (uint64_t)elems_per_row,
+                              pr.dense ? (uint64_t)pr.G * pr.N : (uint64_t)pr.G * p.kblocks * pr.N};
+  const uint64_t b_strides[1] = {pr.dense ? (uint64_t)pr.K * esize : (uint64_t)kRowBytes};
   {
-    const uint64_t rows = (uint64_t)pr.G * p.kblocks * pr.N;
-    const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
-    const uint64_t strides[1] = {(uint64_t)kRowBytes};
     const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)BN};
-    rc = encode_map(&tm_b, dt_a, 2, pr.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = encode_map(&tm_b, dt_a, 2, pr.b, b_dims, b_strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc != DG_OK) return rc;
   // Narrow weight boxes (64 and 32 rows) for sparse routing; only the BN = 128 tile uses them.
   CUtensorMap tm_b64 = tm_b, tm_b32 = tm_b;
   p.narrow = (BN == 128 && pr.mode != MODE_CONTIG) ? pr.narrow : 0;
   if (p.narrow) {
-    const uint64_t rows = (uint64_t)pr.G * p.kblocks * pr.N;
-    const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
-    const uint64_t strides[1] = {(uint64_t)kRowBytes};
     const uint32_t box64[2] = {(uint32_t)elems_per_row, 64u};
     const uint32_t box32[2] = {(uint32_t)elems_per_row, 32u};
-    rc = encode_map(&tm_b64, dt_a, 2, pr.b, dims, strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = encode_map(&tm_b64, dt_a, 2, pr.b, b_dims, b_strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
-      rc = encode_map(&tm_b32, dt_a, 2, pr.b, dims, strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
+      rc = encode_map(&tm_b32, dt_a, 2, pr.b, b_dims, b_strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != DG_OK) return rc;
   }
 
@@ -269,6 +270,7 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.d = static_cast<__nv_bfloat16*>(pr.d);
   p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
   p.status = pr.status;
+  p.b_rowmajor = pr.dense;
 
   const long long max_items =
       (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : 2LL * p.m_blocks) * p.n_tiles;
@@ -294,9 +296,9 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   }
   if (rc != DG_OK) return rc;
   {
-    const uint64_t rows = (uint64_t)pr.G * p.kblocks * pr.N;
-    const uint64_t dims[2] = {(uint64_t)elems_per_row, rows};
-    const uint64_t strides[1] = {(uint64_t)kRowBytes};
+    const uint64_t dims[2] = {pr.dense ? (uint64_t)pr.K : (uint64_t)elems_per_row,
+                              pr.dense ? (uint64_t)pr.G * pr.N : (uint64_t)pr.G * p.kblocks * pr.N};
+    const uint64_t strides[1] = {pr.dense ? (uint64_t)pr.K * esize : (uint64_t)kRowBytes};
     const uint32_t box[2] = {(uint32_t)elems_per_row, 128u};  // each block loads half the tile
     rc = encode_map(&tm_b, dt_a, 2, pr.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   }
@@ -422,21 +424,26 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
   if (pr.kind < DG_KIND_I8 || pr.kind > DG_KIND_BF16) return DG_ERR_BAD_KIND;
   if (pr.scale_mode < DG_SCALE_PER_CHANNEL || pr.scale_mode > DG_SCALE_NONE)
     return DG_ERR_BAD_SCALE_MODE;
-  if ((pr.kind == DG_KIND_BF16) != (pr.scale_mode == DG_SCALE_NONE)) return DG_ERR_BAD_SCALE_MODE;
-  if (pr.G < 1 || pr.M < 0 || pr.N < 16 || pr.K < 1) return DG_ERR_BAD_SHAPE;
+  if (!pr.dense && (pr.kind == DG_KIND_BF16) != (pr.scale_mode == DG_SCALE_NONE))
+    return DG_ERR_BAD_SCALE_MODE;
+  if (pr.G < 1 || pr.M < 0 || pr.N < (pr.dense ? 1 : 16) || pr.K < 1) return DG_ERR_BAD_SHAPE;
+  if (pr.out_kind < DG_OUT_BF16 || pr.out_kind > DG_OUT_F32) return DG_ERR_BAD_ARGUMENT;
+  if (pr.dense && pr.kind == DG_KIND_W4A8) return DG_ERR_BAD_KIND;
   if (pr.G > DG_MAX_GROUPS) return DG_ERR_TOO_LARGE;
   if (pr.mode != MODE_MASKED && pr.M > DG_MAX_CONTIG_ROWS) return DG_ERR_TOO_LARGE;
   if (pr.mode == MODE_COMPACT && pr.kind == DG_KIND_W4A8) return DG_ERR_BAD_KIND;
-  if (pr.N % 16 != 0) return DG_ERR_BAD_SHAPE;
+  if (!pr.dense && pr.N % 16 != 0) return DG_ERR_BAD_SHAPE;
   const int kq = (pr.kind == DG_KIND_BF16) ? 64 : (pr.kind == DG_KIND_W4A8 ? 256 : 128);
   if (pr.K % kq != 0) return DG_ERR_BAD_SHAPE;
   if ((long long)pr.G * (pr.K / kq) * pr.N > 0x7fffffffLL) return DG_ERR_TOO_LARGE;
   if (pr.M == 0) return DG_OK;
-  if (!pr.a || !pr.b || !pr.d || !pr.sched) return DG_ERR_NULL_POINTER;
+  if (!pr.a || !pr.b || !pr.d || (!pr.sched && !pr.dense)) return DG_ERR_NULL_POINTER;
   if (pr.mode == MODE_COMPACT && !pr.offsets) return DG_ERR_NULL_POINTER;
   if (pr.scale_mode != DG_SCALE_NONE && (!pr.a_scale || !pr.b_scale)) return DG_ERR_NULL_POINTER;
   if (!aligned16(pr.a) || !aligned16(pr.b) || !aligned16(pr.d)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.scale_mode == DG_SCALE_PER_CHANNEL && !aligned16(pr.b_scale)) return DG_ERR_BAD_ALIGNMENT;
+  // fp16 / fp32 output and rows of D that start unaligned exist only in the one-CTA kernel
+  const bool scalar_out = pr.out_kind != DG_OUT_BF16 || (pr.N % 8) != 0;
   if (pr.debug_acc && !aligned16(pr.debug_acc)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.block_n != 0 && pr.block_n != 32 && pr.block_n != 64 && pr.block_n != 128 &&
       pr.block_n != 256 && pr.block_n != 512)
@@ -475,6 +482,7 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
       bn = (pr.expected_m > 256 && pr.N >= 256) ? 256 : 128;
   }
   if (bn == 512 && (pr.N < 256 || pr.mode == MODE_COMPACT)) bn = 128;
+  if (bn == 512 && scalar_out) bn = 256;
   if (pr.kind == DG_KIND_W4A8) return launch_w4(pr, *dev, stream);
 
   if (bn == 512) {  // two-CTA 256x256 tiles
@@ -547,6 +555,33 @@ int dg_compact_gemm(const dg_compact_args* a, void* stream) {
   pr.K = a->k;
   pr.block_n = a->block_n;
   pr.expected_m = a->expected_m;
+  pr.debug_acc = a->debug_acc;
+  pr.status = a->status;
+  return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
+}
+
+int dg_dense_gemm(const dg_dense_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if ((a->a_scale == nullptr) != (a->b_scale == nullptr)) return DG_ERR_BAD_ARGUMENT;
+  Problem pr{};
+  pr.kind = a->kind;
+  pr.scale_mode = a->a_scale ? DG_SCALE_PER_CHANNEL : DG_SCALE_NONE;
+  if (a->kind == DG_KIND_BF16 && a->a_scale) return DG_ERR_BAD_SCALE_MODE;
+  pr.mode = MODE_MASKED;  // batch = groups, every row valid
+  pr.dense = 1;
+  pr.out_kind = a->out_kind;
+  pr.a = a->a;
+  pr.b = a->b;
+  pr.d = a->d;
+  pr.a_scale = a->a_scale;
+  pr.b_scale = a->b_scale;
+  pr.sched = nullptr;
+  pr.G = a->batch;
+  pr.M = a->m;
+  pr.N = a->n;
+  pr.K = a->k;
+  pr.block_n = a->block_n;
+  pr.expected_m = a->m;
   pr.debug_acc = a->debug_acc;
   pr.status = a->status;
   return validate_and_launch(pr, static_cast<cudaStream_t>(stream));

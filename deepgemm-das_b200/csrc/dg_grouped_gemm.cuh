@@ -31,6 +31,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "deepgemm_b200.h"
 #include "dg_ptx.cuh"
@@ -72,6 +73,8 @@ struct KernelParams {
   __nv_bfloat16* d;
   uint32_t* debug_acc;
   int32_t* status;
+  int b_rowmajor;  // 1: weights are plain [G][N][K] rows (dense GEMM), 0: the packed layout
+  int out_kind;    // 0 = bf16 output; 1 = fp16, 2 = fp32 (dense GEMM only, scalar stores)
   int narrow;  // BN = 128, masked / compact: 0 = tiles stay 128 columns wide, 1 = the kernel may
                // narrow them to 64 / 32 columns when few groups have rows, 64 / 32 = forced width
 };
@@ -173,6 +176,45 @@ __device__ __forceinline__ void epilogue_store32(const uint32_t (&r)[32], const 
         *reinterpret_cast<uint4*>(e.dbg_row + col + j + 4) =
             make_uint4(r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
       }
+    }
+  }
+}
+
+// TMA coordinates of the weight tile of K block kb: packed layout = flat list of 128-byte rows
+// ordered [g][kb][n]; row-major = rows [g][n] of K elements.
+__device__ __forceinline__ void weight_coords(const KernelParams& p, int g, int n0, int kb,
+                                              int elems_per_row, int& x, int& y) {
+  if (p.b_rowmajor) {
+    x = kb * elems_per_row;
+    y = g * p.N + n0;
+  } else {
+    x = 0;
+    y = (g * p.kblocks + kb) * p.N + n0;
+  }
+}
+
+// Slow twin of epilogue_store32 for what the grouped entry points never produce: fp16 / fp32
+// output or an N that is not a multiple of 8 (rows of D then start at unaligned addresses).
+// Same arithmetic, one scalar store per element.
+template <bool kIntAcc>
+__device__ __forceinline__ void epilogue_store32_scalar(const uint32_t (&r)[32], const EpiRow& e,
+                                                        int scale_mode, int col, int cols_left,
+                                                        int out_kind) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (j < cols_left) {
+      float v = kIntAcc ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);
+      if (scale_mode == DG_SCALE_PER_CHANNEL)
+        v = (v * e.as) * __ldg(e.bs_row + col + j);
+      else if (scale_mode == DG_SCALE_TENSOR_WISE)
+        v = (v * e.as) * e.bs_g;
+      if (out_kind == 0)
+        e.d_row[col + j] = __float2bfloat16_rn(v);
+      else if (out_kind == 1)
+        reinterpret_cast<__half*>(e.d_row)[col + j] = __float2half_rn(v);
+      else
+        reinterpret_cast<float*>(e.d_row)[col + j] = v;
+      if (e.dbg_row != nullptr) e.dbg_row[col + j] = r[j];
     }
   }
 }
@@ -288,7 +330,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     int32_t* cnt = tbl;
     int32_t* pref = tbl + p.G;
     for (int g = tid; g < p.G; g += blockDim.x) {
-      cnt[g] = max(0, min(p.sched[g], p.M));
+      cnt[g] = p.sched ? max(0, min(p.sched[g], p.M)) : p.M;  // no masked_m: every row (dense GEMM)
       if (p.mode == MODE_COMPACT) tbl[2 * p.G + 1 + g] = max(0, min(p.offsets[g], p.M));
     }
     __syncthreads();
@@ -379,7 +421,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           const StageShape sh = stage_shape(t.rows_valid, kNarrow ? bn_eff : BN, BN);
           const CUtensorMap* tm_act = (sh.a_rows == kBM) ? &tm_a : &tm_a32;
           const int kps = kNarrow ? sh.kps : 1;
-          const int b_row0 = t.g * p.kblocks * p.N + t.n0;
           for (int kb0 = 0; kb0 < p.kblocks; kb0 += kps, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
@@ -393,8 +434,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                 tma_load_3d(a_dst, tm_act, bar_full(s), kb * kElemsPerRow, t.row0, t.g, pol_a);
               else
                 tma_load_2d(a_dst, tm_act, bar_full(s), kb * kElemsPerRow, t.row0, pol_a);
-              tma_load_2d(base + L::off_b + s * L::kBStage + j * sh.b_stride, tm_w, bar_full(s), 0,
-                          b_row0 + kb * p.N, pol_b);
+              int bx, by;
+              weight_coords(p, t.g, t.n0, kb, kElemsPerRow, bx, by);
+              tma_load_2d(base + L::off_b + s * L::kBStage + j * sh.b_stride, tm_w, bar_full(s), bx,
+                          by, pol_b);
             }
           }
         }
@@ -487,8 +530,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         row.as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
         row.bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
         row.bs_row = p.b_scale + (size_t)t.g * p.N + t.n0;  // PER_CHANNEL only
-        row.d_row = p.d + grow * p.N + t.n0;
+        const size_t d_off = grow * p.N + t.n0;  // in output elements
+        row.d_row = p.out_kind == 2 ? reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<float*>(p.d) + d_off)
+                                    : p.d + d_off;
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
+        const bool scalar_out = p.out_kind != 0 || (p.N & 7) != 0;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
         for (int c = 0; c < bn_eff / 32; ++c) {
@@ -497,7 +543,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
-          if (rv) epilogue_store32<kIntAcc>(r, row, p.scale_mode, c * 32, cols_left);
+          if (rv) {
+            if (!scalar_out)
+              epilogue_store32<kIntAcc>(r, row, p.scale_mode, c * 32, cols_left);
+            else
+              epilogue_store32_scalar<kIntAcc>(r, row, p.scale_mode, c * 32, cols_left, p.out_kind);
+          }
         }
       }
       // hand the accumulator back to the UMMA issuer

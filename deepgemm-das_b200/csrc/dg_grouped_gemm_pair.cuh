@@ -139,7 +139,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (p.mode == MODE_MASKED) {
     int32_t* cnt = tbl;
     int32_t* pref = tbl + p.G;
-    for (int g = tid; g < p.G; g += blockDim.x) cnt[g] = max(0, min(p.sched[g], p.M));
+    for (int g = tid; g < p.G; g += blockDim.x) cnt[g] = p.sched ? max(0, min(p.sched[g], p.M)) : p.M;
     __syncthreads();
     if (warp == 0) {
       int running = 0;
@@ -219,7 +219,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       for (int item = pair; ok && item < n_items; item += num_pairs) {
         const PairTile t = dec.get(item);
         const int a_row = t.row0 + static_cast<int>(rank) * 128;
-        const int b_row0 = t.g * p.kblocks * p.N + t.n0 + static_cast<int>(rank) * 128;
+        const int b_n0 = t.n0 + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -235,7 +235,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
             tma_load_3d_pair(a_dst, &tm_a, full_leader, kb * kElemsPerRow, a_row, t.g, pol_a);
           else
             tma_load_2d_pair(a_dst, &tm_a, full_leader, kb * kElemsPerRow, a_row, pol_a);
-          tma_load_2d_pair(b_dst, &tm_b, full_leader, 0, b_row0 + kb * p.N, pol_b);
+          int bx, by;
+          weight_coords(p, t.g, b_n0, kb, kElemsPerRow, bx, by);
+          tma_load_2d_pair(b_dst, &tm_b, full_leader, bx, by, pol_b);
         }
       }
       if (rank == 0) {

@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "dg_masked_gemm",
     "dg_contig_gemm",
     "dg_compact_gemm",
+    "dg_dense_gemm",
     "dg_quant_group_rows",
     "dg_quant_group_scratch_bytes",
     "dg_quant_group_rows_noalloc",
@@ -122,6 +123,26 @@ class QuantGroupArgs(C.Structure):
     ]
 
 
+class DenseArgs(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("out_kind", C.c_int32),
+        ("a", C.c_void_p),
+        ("b", C.c_void_p),
+        ("d", C.c_void_p),
+        ("a_scale", C.c_void_p),
+        ("b_scale", C.c_void_p),
+        ("batch", C.c_int32),
+        ("m", C.c_int32),
+        ("n", C.c_int32),
+        ("k", C.c_int32),
+        ("block_n", C.c_int32),
+        ("reserved", C.c_int32),
+        ("debug_acc", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 class ActQuantArgs(C.Structure):
     _fields_ = [
         ("kind", C.c_int32),
@@ -173,6 +194,8 @@ def _load() -> C.CDLL:
     lib.dg_quant_group_rows_noalloc.restype = C.c_int
     lib.dg_quant_group_scratch_bytes.argtypes = [C.c_int32, C.c_int32]
     lib.dg_quant_group_scratch_bytes.restype = C.c_size_t
+    lib.dg_dense_gemm.argtypes = [C.POINTER(DenseArgs), C.c_void_p]
+    lib.dg_dense_gemm.restype = C.c_int
     lib.dg_silu_mul_quant_rows.argtypes = [C.POINTER(ActQuantArgs), C.c_void_p]
     lib.dg_silu_mul_quant_rows.restype = C.c_int
     lib.dg_combine_rows.argtypes = [C.POINTER(CombineArgs), C.c_void_p]

@@ -195,6 +195,38 @@ DG_API int dg_contig_gemm(const dg_contig_args* args, void* stream);
  *     (rows per group given as token_per_expert; the caller passes their running sum as offsets) */
 DG_API int dg_compact_gemm(const dg_compact_args* args, void* stream);
 
+/* Output element types of dg_dense_gemm. */
+#define DG_OUT_BF16 0
+#define DG_OUT_F16  1
+#define DG_OUT_F32  2
+
+/* Arguments of the plain (batched) GEMM  d[b] = (a[b] * a_scale[b][:,None]) @ (w[b] *
+ * b_scale[b][:,None])^T  with weights in their natural row-major [n][k] order (no packing),
+ * computed as  out((float(acc) * a_scale[row]) * b_scale[col]). */
+typedef struct dg_dense_args {
+  int32_t kind;               /* DG_KIND_I8, DG_KIND_E4M3 or DG_KIND_BF16 */
+  int32_t out_kind;           /* DG_OUT_BF16 / DG_OUT_F16 / DG_OUT_F32 */
+  const void*  a;             /* [batch][m][k] */
+  const void*  b;             /* [batch][n][k] */
+  void*        d;             /* [batch][m][n] */
+  const float* a_scale;       /* [batch][m], or NULL together with b_scale: no scaling */
+  const float* b_scale;       /* [batch][n] */
+  int32_t batch;              /* 1..DG_MAX_GROUPS */
+  int32_t m;
+  int32_t n;                  /* any n >= 1; n % 8 != 0 and non-bf16 outputs use scalar stores */
+  int32_t k;                  /* multiple of 128 (64 for bf16) */
+  int32_t block_n;            /* 0 = choose; 128 / 256 / 512 as in dg_masked_args */
+  int32_t reserved;           /* must be 0 */
+  void*        debug_acc;     /* NULL, or [batch][m][n] raw 32-bit accumulators */
+  int32_t*     status;        /* NULL, or int32[DG_STATUS_WORDS] */
+} dg_dense_args;
+
+/* Dense GEMM on the grouped kernels (a batch entry is a group whose rows are all valid).
+ * Stands in for deepgemm::fp8_gemm / fp8_gemm_hipc behind deepgemm/gemm.py:8-42 and :44-83
+ * (hipBLASLt and csrc/arch/gfx938/fp8_gemm_hipc.cu there): same operands, alpha = 1, beta = 0,
+ * no bias. */
+DG_API int dg_dense_gemm(const dg_dense_args* args, void* stream);
+
 /* Nibble order of a row-major int4 source [G][N][K/2]:
  *   DG_NIBBLE_HIGH_FIRST: byte j holds w[2j] in its high nibble (the reference's
  *     framework layout, deepgemm/group_gemm_weight_pack.py:594-602)

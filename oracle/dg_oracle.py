@@ -247,3 +247,18 @@ def ref_moe_layer(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: to
         y[pairs] = ((q.float() @ w2[e].float().t()) * s.reshape(-1, 1) * w2_scale[e].reshape(1, -1)).bfloat16()
     src = torch.arange(t * k, dtype=torch.int32).view(t, k)
     return ref_combine(y, src, topk_weights)
+
+
+# ----------------------------------------------------------------------------- dense GEMM
+def ref_dense_scaled(a: torch.Tensor, b: torch.Tensor, scale_a: Optional[torch.Tensor],
+                     scale_b: Optional[torch.Tensor], out_dtype=torch.bfloat16) -> torch.Tensor:
+    """a [M,K], b [N,K], scale_a [M], scale_b [N] -> [M,N]; op_test/test_fp8_gemm.py:31-39
+    (operands are scaled first, then one fp32 matmul); identity scales as in
+    op_test/test_fp8_gemm_hipc.py:96-101 when a scale is None."""
+    a_fp = a.to(torch.float32)
+    b_fp = b.to(torch.float32).t()
+    if scale_a is not None:
+        a_fp = a_fp * scale_a.view(-1, 1)
+    if scale_b is not None:
+        b_fp = b_fp * scale_b.view(1, -1)
+    return torch.matmul(a_fp, b_fp).to(out_dtype)

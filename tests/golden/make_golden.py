@@ -57,7 +57,7 @@ def _import_reference_helpers():
     for name in ("quant_utils", "masked_w8a8_int8_common", "contiguous_w8a8_int8_common",
                  "test_deepgemm_masked_w8a8_fp8", "test_deepgemm_masked_w8a8_fp8_tensor_wise",
                  "test_deepgemm_masked_w4a8", "test_deepgemm_contiguous_w8a8_fp8",
-                 "test_deepgemm_contiguous_w8a8_fp8_tensor_wise"):
+                 "test_deepgemm_contiguous_w8a8_fp8_tensor_wise", "test_fp8_gemm"):
         mods[name] = importlib.import_module(name)
     # The reference's int4 framework packer lives in its package; load that one file with
     # its sibling import stubbed.
@@ -166,6 +166,17 @@ def main():
     ref = m["test_deepgemm_contiguous_w8a8_fp8_tensor_wise"].torch_gemm(
         at, bt, torch.zeros(len(idx_t), 16, dtype=torch.bfloat16), sat, sbt, 1.0, 0.0, mi_t)
     _save("contig_fp8_tensor_wise", a=at, a_scale=sat, b=bt, b_scale=sbt, m_indices=mi_t, out=ref)
+
+    # 9. dense FP8 GEMM with per-row scales on both operands (N not a multiple of 8, as the
+    #    reference's own first accuracy case)
+    md, nd, kd = 24, 22, 256
+    ad = to_fp8(torch.randn(md, kd, generator=g) * 0.5)
+    bd = to_fp8(torch.randn(nd, kd, generator=g) * 0.5)
+    sad = torch.randn(md, generator=g).abs() * 0.01 + 0.01
+    sbd = torch.randn(nd, generator=g).abs() * 0.01 + 0.01
+    ref = m["test_fp8_gemm"].torch_fp8_gemm(ad, bd.t(), sad, sbd, out_dtype=torch.bfloat16)
+    ref16 = m["test_fp8_gemm"].torch_fp8_gemm(ad, bd.t(), sad, sbd, out_dtype=torch.float16)
+    _save("dense_fp8", a=ad, a_scale=sad, b=bd, b_scale=sbd, out=ref, out_f16=ref16)
 
 
 if __name__ == "__main__":

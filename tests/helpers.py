@@ -12,7 +12,8 @@ import dg_oracle as O
 
 GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 FP8 = torch.float8_e4m3fn
-_FP8_CASES = {"masked_fp8", "masked_fp8_tensor_wise", "contig_fp8", "contig_fp8_tensor_wise"}
+_FP8_CASES = {"masked_fp8", "masked_fp8_tensor_wise", "contig_fp8", "contig_fp8_tensor_wise",
+              "dense_fp8"}
 
 
 def load_golden(name: str) -> dict:

@@ -115,3 +115,11 @@ def test_chain_oracle_matches_the_unfused_torch_ops():
     q, s = O.per_token_quant_int8(O.ref_silu_mul(h))
     y2 = O.ref_masked_scaled(q[None], w2, s.reshape(1, -1, 1), s2.reshape(1, -1, 1))[0]
     assert torch.equal(out.float().bfloat16(), (2.0 * y2.double()).float().bfloat16())
+
+
+def test_dense_fp8_matches_reference():
+    g = load_golden("dense_fp8")
+    out = O.ref_dense_scaled(g["a"], g["b"], g["a_scale"], g["b_scale"], torch.bfloat16)
+    assert torch.equal(out.view(torch.int16), g["out"].view(torch.int16))
+    out16 = O.ref_dense_scaled(g["a"], g["b"], g["a_scale"], g["b_scale"], torch.float16)
+    assert torch.equal(out16.view(torch.int16), g["out_f16"].view(torch.int16))
