@@ -691,6 +691,49 @@ int dg_quant_group_rows(const dg_quant_group_args* a, void* stream) {
   return quant_group_common(a, static_cast<int32_t*>(a->scratch), stream);
 }
 
+int dg_group_sorted_rows(const dg_group_sorted_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->num_sorted < 0 || a->block_m < 1 || a->size_m < 0 || a->hidden < 16 || a->hidden % 16 != 0 ||
+      a->num_groups < 1 || a->align < 1 || a->m_cap < 0 || a->real_topk < 1 || a->real_topk > 255)
+    return DG_ERR_BAD_SHAPE;
+  if (a->num_groups > DG_MAX_GROUPS) return DG_ERR_TOO_LARGE;
+  if (!a->a_out || !a->a_scale_out || !a->m_indices_out || !a->scratch) return DG_ERR_NULL_POINTER;
+  if (a->num_sorted > 0 && (!a->rows || !a->row_scale || !a->sorted_token_ids || !a->expert_ids ||
+                            !a->num_tokens_post_pad))
+    return DG_ERR_NULL_POINTER;
+  if (!aligned16(a->rows) || !aligned16(a->a_out) || !aligned16(a->scratch)) return DG_ERR_BAD_ALIGNMENT;
+  if (a->scratch_bytes < dg_quant_group_scratch_bytes(a->num_sorted, a->num_groups))
+    return DG_ERR_BAD_ARGUMENT;
+  dg::QuantGroupParams p{};
+  p.rows = static_cast<const __nv_bfloat16*>(a->rows);
+  p.sorted_ids = a->sorted_token_ids;
+  p.expert_ids = a->expert_ids;
+  p.num_post_pad = a->num_tokens_post_pad;
+  p.row_scale = a->row_scale;
+  p.row_weight = a->row_weight;
+  p.block_m = a->block_m;
+  p.real_topk = a->real_topk;
+  p.size_m = a->size_m;
+  p.a_out = a->a_out;
+  p.a_scale_out = a->a_scale_out;
+  p.m_indices_out = a->m_indices_out;
+  p.dest_out = a->dest_out;
+  p.m_total_out = a->m_total_out;
+  p.R = a->num_sorted;
+  p.H = a->hidden;
+  p.G = a->num_groups;
+  p.align = a->align;
+  p.m_cap = a->m_cap;
+  p.chunks = (a->num_sorted + dg::kQgChunk - 1) / dg::kQgChunk;
+  p.kind = DG_KIND_I8;
+  p.hist = static_cast<int32_t*>(a->scratch);
+  p.starts = p.hist + static_cast<size_t>(p.chunks) * p.G;
+  cudaError_t e = dg::launch_quant_group(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(a->num_sorted > 0 ? 4 : 1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
 int dg_silu_mul_quant_rows(const dg_act_quant_args* a, void* stream) {
   if (a == nullptr) return DG_ERR_NULL_POINTER;
   if (a->kind != DG_KIND_E4M3 && a->kind != DG_KIND_I8) return DG_ERR_BAD_KIND;

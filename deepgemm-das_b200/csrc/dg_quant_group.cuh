@@ -43,6 +43,18 @@ struct QuantGroupParams {
   const __nv_bfloat16* rows;
   const int32_t* expert;
   const int32_t* src_index;  // nullable: input row r is rows[src_index[r]] instead of rows[r]
+  // "sorted ids" input (all null / 0 otherwise): row r is entry r of a routing list in which
+  // every entry packs (top-k slot << 24 | token), entries come in blocks of block_m that share
+  // one expert (expert_ids[r / block_m], -1 = not on this rank), and entries at or beyond
+  // *num_post_pad, with a slot >= real_topk or a row index >= size_m are padding.  The row
+  // read is token * real_topk + slot; it is already quantised (1 byte per element, scale
+  // row_scale[row], optionally times row_weight[row]) and is copied, not quantised.
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  const float* row_scale;
+  const float* row_weight;
+  int block_m, real_topk, size_m;
   void* a_out;
   float* a_scale_out;
   int32_t* m_indices_out;
@@ -53,6 +65,22 @@ struct QuantGroupParams {
   int R, H, G, align, m_cap, chunks, kind;
 };
 
+// Expert of input row r (-1 = drop) and the row of `rows` it reads.
+__device__ __forceinline__ int qg_expert_of(const QuantGroupParams& p, int r, int* src) {
+  if (p.sorted_ids == nullptr) {
+    *src = p.src_index ? p.src_index[r] : r;
+    return p.expert[r];
+  }
+  *src = 0;
+  if (r >= *p.num_post_pad) return -1;
+  const uint32_t id = static_cast<uint32_t>(p.sorted_ids[r]);
+  const int slot = static_cast<int>(id >> 24);
+  const long long row = static_cast<long long>(id & 0x00FFFFFFu) * p.real_topk + slot;
+  if (slot >= p.real_topk || row >= p.size_m) return -1;
+  *src = static_cast<int>(row);
+  return p.expert_ids[r / p.block_m];
+}
+
 __global__ void qg_histogram_kernel(const QuantGroupParams p) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
@@ -62,7 +90,8 @@ __global__ void qg_histogram_kernel(const QuantGroupParams p) {
     for (int e = lane; e < p.G; e += 32) p.hist[(size_t)e * p.chunks + c] = 0;
     __syncwarp();
     const int r = c * kQgChunk + lane;
-    int e = (r < p.R) ? p.expert[r] : -1;
+    int src;
+    int e = (r < p.R) ? qg_expert_of(p, r, &src) : -1;
     if (e >= p.G) e = -1;
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     if (e >= 0 && (peers & ((1u << lane) - 1u)) == 0)  // first lane of each distinct expert
@@ -70,6 +99,8 @@ __global__ void qg_histogram_kernel(const QuantGroupParams p) {
   }
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
   for (int i = tid; i < p.m_cap; i += gridDim.x * blockDim.x) p.m_indices_out[i] = -1;
+  if (p.sorted_ids != nullptr && p.dest_out != nullptr)  // dest is indexed by source row there
+    for (int i = tid; i < p.size_m; i += gridDim.x * blockDim.x) p.dest_out[i] = -1;
 }
 
 // Block e: exclusive scan of hist[e][0..chunks) in place, total to starts[e].
@@ -126,32 +157,34 @@ __device__ __forceinline__ float qg_block_max(float v, float* red) {
   return m;
 }
 
+// Output row of input row r (-1 = dropped), its expert and the row it reads.  One thread.
+__device__ __forceinline__ int qg_dest_of(const QuantGroupParams& p, int r, int* expert, int* src) {
+  const int e = qg_expert_of(p, r, src);
+  *expert = e;
+  if (e < 0 || e >= p.G) return -1;
+  // stable rank inside the chunk: earlier rows of the same chunk with the same expert
+  const int c = r / kQgChunk;
+  int rank = 0, other;
+  for (int j = c * kQgChunk; j < r; ++j) rank += (qg_expert_of(p, j, &other) == e);
+  const int dest = p.starts[e] + p.hist[(size_t)e * p.chunks + c] + rank;
+  return dest < p.m_cap ? dest : -1;
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGroupParams p) {
   __shared__ float red[kQgThreads / 32];
-  __shared__ int s_dest;
+  __shared__ int s_dest, s_src, s_expert;
   const int r = blockIdx.x;
   if (threadIdx.x == 0) {
-    int e = p.expert[r];
-    int dest = -1;
-    if (e >= 0 && e < p.G) {
-      // stable rank inside the chunk: earlier rows of the same chunk with the same expert
-      const int c = r / kQgChunk;
-      int rank = 0;
-      for (int j = c * kQgChunk; j < r; ++j) rank += (p.expert[j] == e);
-      dest = p.starts[e] + p.hist[(size_t)e * p.chunks + c] + rank;
-      if (dest >= p.m_cap) dest = -1;
-    }
-    s_dest = dest;
-    if (p.dest_out != nullptr) p.dest_out[r] = dest;
+    s_dest = qg_dest_of(p, r, &s_expert, &s_src);
+    if (p.dest_out != nullptr) p.dest_out[r] = s_dest;
   }
   __syncthreads();
   const int dest = s_dest;
   if (dest < 0) return;
 
   const int nvec = p.H / 8;  // 16-byte vectors of 8 bf16
-  const size_t src_row = p.src_index ? static_cast<size_t>(p.src_index[r]) : static_cast<size_t>(r);
-  const uint4* src = reinterpret_cast<const uint4*>(p.rows + src_row * p.H);
+  const uint4* src = reinterpret_cast<const uint4*>(p.rows + static_cast<size_t>(s_src) * p.H);
   uint4 v[kQgMaxVec];
   float amax = 0.0f;
 #pragma unroll
@@ -174,7 +207,7 @@ __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGrou
   const float inv = __fmul_rn(__frcp_rn(amax), kQmax);
   if (threadIdx.x == 0) {
     p.a_scale_out[dest] = __fdiv_rn(amax, kQmax);
-    p.m_indices_out[dest] = p.expert[r];
+    p.m_indices_out[dest] = s_expert;
   }
   uint2* dst = reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.a_out) + (size_t)dest * p.H);
 #pragma unroll
@@ -211,6 +244,28 @@ __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGrou
   }
 }
 
+// Sorted-ids input: the rows are quantised already; copy H bytes and the (weighted) scale.
+constexpr int kQgCopyThreads = 64;
+__global__ void __launch_bounds__(kQgCopyThreads) qg_copy_kernel(const QuantGroupParams p) {
+  __shared__ int s_dest, s_src, s_expert;
+  const int r = blockIdx.x;
+  if (threadIdx.x == 0) {
+    s_dest = qg_dest_of(p, r, &s_expert, &s_src);
+    if (s_dest >= 0) {
+      if (p.dest_out != nullptr) p.dest_out[s_src] = s_dest;
+      const float w = p.row_weight ? p.row_weight[s_src] : 1.0f;
+      p.a_scale_out[s_dest] = p.row_weight ? __fmul_rn(w, p.row_scale[s_src]) : p.row_scale[s_src];
+      p.m_indices_out[s_dest] = s_expert;
+    }
+  }
+  __syncthreads();
+  if (s_dest < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.rows) +
+                                                    static_cast<size_t>(s_src) * p.H);
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.a_out) + static_cast<size_t>(s_dest) * p.H);
+  for (int i = threadIdx.x; i < p.H / 16; i += kQgCopyThreads) dst[i] = __ldg(src + i);
+}
+
 inline cudaError_t launch_quant_group(const QuantGroupParams& p, cudaStream_t stream) {
   if (p.R == 0) {
     // still mark every row unused
@@ -226,7 +281,9 @@ inline cudaError_t launch_quant_group(const QuantGroupParams& p, cudaStream_t st
   qg_histogram_kernel<<<hblocks, 256, 0, stream>>>(p);
   qg_scan_kernel<<<p.G, 256, 0, stream>>>(p);
   qg_starts_kernel<<<1, 32, 0, stream>>>(p);
-  if (p.kind == DG_KIND_E4M3)
+  if (p.sorted_ids != nullptr)
+    qg_copy_kernel<<<p.R, kQgCopyThreads, 0, stream>>>(p);
+  else if (p.kind == DG_KIND_E4M3)
     qg_quantise_kernel<DG_KIND_E4M3><<<p.R, kQgThreads, 0, stream>>>(p);
   else
     qg_quantise_kernel<DG_KIND_I8><<<p.R, kQgThreads, 0, stream>>>(p);

@@ -62,6 +62,7 @@ from .m_group_gemm_nt_masked import (
 
 from .legacy_compat import *  # noqa: F401,F403  (old names, as the reference re-exports them)
 from .quant_group import quant_group_capacity, quantize_group_rows
+from .moe_marlin_prefill import assert_moe_prefill_down_fp8_shapes, moe_w8a8_marlin_prefill_down_fp8
 from .moe_chain import combine_rows, expert_mlp_contiguous, moe_forward, silu_mul_quant
 from .print_size import install_op_size_printer
 

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "dg_quant_group_rows",
     "dg_quant_group_scratch_bytes",
     "dg_quant_group_rows_noalloc",
+    "dg_group_sorted_rows",
     "dg_silu_mul_quant_rows",
     "dg_combine_rows",
     "dg_pack_weight",
@@ -143,6 +144,32 @@ class DenseArgs(C.Structure):
     ]
 
 
+class GroupSortedArgs(C.Structure):
+    _fields_ = [
+        ("num_sorted", C.c_int32),
+        ("block_m", C.c_int32),
+        ("size_m", C.c_int32),
+        ("hidden", C.c_int32),
+        ("num_groups", C.c_int32),
+        ("align", C.c_int32),
+        ("m_cap", C.c_int32),
+        ("real_topk", C.c_int32),
+        ("rows", C.c_void_p),
+        ("row_scale", C.c_void_p),
+        ("row_weight", C.c_void_p),
+        ("sorted_token_ids", C.c_void_p),
+        ("expert_ids", C.c_void_p),
+        ("num_tokens_post_pad", C.c_void_p),
+        ("a_out", C.c_void_p),
+        ("a_scale_out", C.c_void_p),
+        ("m_indices_out", C.c_void_p),
+        ("dest_out", C.c_void_p),
+        ("m_total_out", C.c_void_p),
+        ("scratch", C.c_void_p),
+        ("scratch_bytes", C.c_size_t),
+    ]
+
+
 class ActQuantArgs(C.Structure):
     _fields_ = [
         ("kind", C.c_int32),
@@ -196,6 +223,8 @@ def _load() -> C.CDLL:
     lib.dg_quant_group_scratch_bytes.restype = C.c_size_t
     lib.dg_dense_gemm.argtypes = [C.POINTER(DenseArgs), C.c_void_p]
     lib.dg_dense_gemm.restype = C.c_int
+    lib.dg_group_sorted_rows.argtypes = [C.POINTER(GroupSortedArgs), C.c_void_p]
+    lib.dg_group_sorted_rows.restype = C.c_int
     lib.dg_silu_mul_quant_rows.argtypes = [C.POINTER(ActQuantArgs), C.c_void_p]
     lib.dg_silu_mul_quant_rows.restype = C.c_int
     lib.dg_combine_rows.argtypes = [C.POINTER(CombineArgs), C.c_void_p]

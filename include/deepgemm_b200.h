@@ -287,6 +287,49 @@ DG_API size_t dg_quant_group_scratch_bytes(int32_t num_rows, int32_t num_groups)
  * quantises); the arithmetic of the latter is reproduced bit for bit. */
 DG_API int dg_quant_group_rows(const dg_quant_group_args* args, void* stream);
 
+/* Arguments of the grouping step for callers that hold a vLLM-style routing list instead of an
+ * expert id per row (the operands of the reference's second-stage op, see below):
+ *   sorted_token_ids[i] = (top-k slot << 24) | token, in blocks of block_m entries that share
+ *   the expert expert_ids[i / block_m] (-1 = expert not on this rank); entries at or beyond
+ *   num_tokens_post_pad[0], with slot >= real_topk, or whose row token * real_topk + slot is
+ *   >= size_m, are padding.
+ * Row token * real_topk + slot of `rows` (already quantised, one byte per element) is copied to
+ * a_out[dest], a_scale_out[dest] = row_scale[row] * row_weight[row], m_indices_out[dest] = its
+ * expert, each expert's block padded to `align` rows as in dg_quant_group_rows;
+ * dest_out[row] = dest for every row copied and -1 for every other row of `rows`. */
+typedef struct dg_group_sorted_args {
+  int32_t num_sorted;        /* entries of sorted_token_ids */
+  int32_t block_m;           /* entries per expert_ids entry (32 in the reference) */
+  int32_t size_m;            /* rows of `rows` */
+  int32_t hidden;            /* bytes per row, multiple of 16 */
+  int32_t num_groups;        /* 1..DG_MAX_GROUPS */
+  int32_t align;
+  int32_t m_cap;
+  int32_t real_topk;
+  const void*    rows;                /* [size_m][hidden] int8 / e4m3 */
+  const float*   row_scale;           /* [size_m] */
+  const float*   row_weight;          /* NULL, or [size_m] routing weights */
+  const int32_t* sorted_token_ids;    /* [num_sorted] */
+  const int32_t* expert_ids;          /* [ceil(num_sorted / block_m)] */
+  const int32_t* num_tokens_post_pad; /* [1] */
+  void*          a_out;               /* [m_cap][hidden] */
+  float*         a_scale_out;         /* [m_cap] */
+  int32_t*       m_indices_out;       /* [m_cap] */
+  int32_t*       dest_out;            /* NULL, or [size_m] */
+  int32_t*       m_total_out;         /* NULL, or one int */
+  void*          scratch;             /* dg_quant_group_scratch_bytes(num_sorted, num_groups) bytes */
+  size_t         scratch_bytes;
+} dg_group_sorted_args;
+
+/* Regroups the rows named by a sorted routing list into the contiguous layout of
+ * dg_contig_gemm (four small launches).  With dg_contig_gemm and dg_combine_rows (top_k = 1,
+ * src_row = dest_out) this is the reference's second-stage MoE GEMM
+ * moe_marlin_w8a8_gemm2_prefill_down_fp8 (csrc/arch/gfx938/moe_w8a8_marlin_prefill_down_fp8.cu:27-110;
+ * gather and routing-weight multiply at csrc/include/moe_marlin/
+ * moe_marlin_prefill_down_fp8_device.inc.h:58-64,114-119, scatter at :262-272), whose kernel
+ * gathers 32-row blocks itself; tcgen05 tiles want 128 rows of one expert, hence the regroup. */
+DG_API int dg_group_sorted_rows(const dg_group_sorted_args* args, void* stream);
+
 /* Arguments of the step between the gate/up GEMM and the down GEMM of an MoE layer:
  *   act[r][c]   = bf16( bf16(silu(x[r][c])) * x[r][H + c] )      (gate | up halves of a row)
  *   scale_out[r] = absmax(act[r]) / qmax,   q_out[r][c] = quantise(act[r][c] * qmax / absmax)

@@ -262,3 +262,59 @@ def ref_dense_scaled(a: torch.Tensor, b: torch.Tensor, scale_a: Optional[torch.T
     if scale_b is not None:
         b_fp = b_fp * scale_b.view(1, -1)
     return torch.matmul(a_fp, b_fp).to(out_dtype)
+
+
+# ----------------------------------------------------------------------------- second-stage MoE GEMM
+def build_sorted_routing(topk_ids: torch.Tensor, num_experts: int, block_m: int,
+                         local_experts=None, extra_blocks: int = 0):
+    """The routing list the reference's second-stage op consumes (what aiter / vLLM's
+    moe_align_block_size produces): entries ``slot << 24 | token`` sorted by expert, each
+    expert's run padded to a multiple of block_m with ``top_k << 24 | T`` (an invalid slot),
+    one expert id per block (-1 for experts outside ``local_experts``), the number of entries
+    in use, plus ``extra_blocks`` unused blocks of padding at the end."""
+    t, k = topk_ids.shape
+    ids, experts = [], []
+    pad = (k << 24) | t
+    for e in range(num_experts):
+        pairs = torch.nonzero(topk_ids == e)
+        if pairs.numel() == 0:
+            continue
+        run = [(int(s) << 24) | int(tok) for tok, s in pairs.tolist()]
+        run += [pad] * (-len(run) % block_m)
+        ids += run
+        local = local_experts is None or e in local_experts
+        experts += [e if local else -1] * (len(run) // block_m)
+    used = len(ids)
+    ids += [pad] * (extra_blocks * block_m)
+    experts += [0] * extra_blocks
+    return (torch.tensor(ids, dtype=torch.int32), torch.tensor(experts, dtype=torch.int32),
+            torch.tensor([used], dtype=torch.int32))
+
+
+def ref_prefill_down(inp: torch.Tensor, w: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor,
+                     topk_weights: torch.Tensor, sorted_token_ids: torch.Tensor, expert_ids: torch.Tensor,
+                     num_tokens_post_pad: torch.Tensor, real_topk: int, out: torch.Tensor) -> torch.Tensor:
+    """Block by block as the reference kernel walks the list
+    (csrc/include/moe_marlin/moe_marlin_prefill_down_fp8_device.inc.h): a block is skipped when
+    it starts at or beyond num_tokens_post_pad or its first entry has slot >= real_topk (:58-59);
+    expert -1 writes zeros (:137-156); otherwise row = token * real_topk + slot gets
+    bf16(acc * (topk_weight[row] * a_scale[row]) * b_scale[e][n]) (:114-119, :262-272).
+    inp [size_m, K] int8 / e4m3, w [E, N, K], out bf16 [size_m, N] updated in place."""
+    block_m = sorted_token_ids.numel() // expert_ids.numel()
+    size_m = inp.shape[0]
+    for blk in range(expert_ids.numel()):
+        ids = sorted_token_ids[blk * block_m:(blk + 1) * block_m].to(torch.int64) & 0xFFFFFFFF
+        if blk * block_m >= int(num_tokens_post_pad[0]) or int(ids[0] >> 24) >= real_topk:
+            continue
+        slot, tok = ids >> 24, ids & 0xFFFFFF
+        row = tok * real_topk + slot
+        keep = (slot < real_topk) & (row < size_m)
+        row = row[keep]
+        e = int(expert_ids[blk])
+        if e < 0:
+            out[row] = 0
+            continue
+        acc = inp[row].float().double() @ w[e].float().double().t()
+        scale = (topk_weights.reshape(-1)[row] * a_scale.reshape(-1)[row]).float()
+        out[row] = ((acc.float() * scale[:, None]) * b_scale[e].reshape(1, -1).float()).bfloat16()
+    return out

@@ -1,0 +1,86 @@
+"""moe_w8a8_marlin_prefill_down_fp8 (second-stage MoE GEMM on a sorted routing list) against a
+block-by-block CPU restatement of the reference kernel.  INT8: within 1 bf16 ulp (the int32
+accumulators are exact, only the fp32 scale products can round differently from the float64
+oracle); FP8 with small-integer values: the same bar."""
+import pytest
+import torch
+
+import deepgemm
+
+import dg_oracle as O
+from helpers import assert_bf16_within_ulp
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+FP8 = torch.float8_e4m3fn
+
+
+def _case(kind, t, k, e, hid, n, block_m, seed, local=None, extra_blocks=0):
+    g = torch.Generator().manual_seed(seed)
+    topk_ids = torch.rand(t, e, generator=g).topk(k, dim=1).indices
+    if kind == "int8":
+        inp = torch.randint(-128, 128, (t * k, hid), generator=g).to(torch.int8)
+        w = torch.randint(-128, 128, (e, n, hid), generator=g).to(torch.int8)
+    else:
+        inp = torch.randint(-6, 7, (t * k, hid), generator=g).float().to(FP8)
+        w = torch.randint(-6, 7, (e, n, hid), generator=g).float().to(FP8)
+    a_scale = torch.rand(t * k, generator=g) * 0.02 + 0.01
+    b_scale = torch.rand(e, n, generator=g) * 0.02 + 0.01
+    topk_w = torch.softmax(torch.randn(t, k, generator=g), dim=1)
+    ids, experts, used = O.build_sorted_routing(topk_ids, e, block_m, local, extra_blocks)
+    return dict(inp=inp, w=w, a_scale=a_scale, b_scale=b_scale, topk_w=topk_w, ids=ids, experts=experts,
+                used=used, k=k)
+
+
+def _run(c, kind, sentinel=3.0):
+    pack = deepgemm.marlin_fp8_contiguous_weight if kind == "fp8" else deepgemm.marlin_i8_contiguous_weight
+    size_m, n = c["inp"].shape[0], c["w"].shape[1]
+    out = torch.full((size_m, n), sentinel, dtype=torch.bfloat16, device=DEV)
+    r = deepgemm.moe_w8a8_marlin_prefill_down_fp8(
+        c["inp"].to(DEV), pack(c["w"].clone().to(DEV)), out, c["a_scale"].to(DEV), c["b_scale"].to(DEV),
+        c["topk_w"].to(DEV), c["ids"].to(DEV), c["experts"].to(DEV), c["used"].to(DEV), c["k"], c["k"])
+    assert r is out
+    want = O.ref_prefill_down(c["inp"], c["w"], c["a_scale"], c["b_scale"], c["topk_w"], c["ids"],
+                              c["experts"], c["used"], c["k"], torch.zeros(size_m, n, dtype=torch.bfloat16))
+    return out.cpu(), want
+
+
+@pytest.mark.parametrize("kind", ["int8", "fp8"])
+@pytest.mark.parametrize("t,k,e,hid,n,block_m", [(200, 4, 6, 256, 512, 32), (64, 2, 3, 128, 1024, 16),
+                                                 (1500, 8, 32, 512, 512, 32)])
+def test_matches_the_block_by_block_oracle(kind, t, k, e, hid, n, block_m):
+    c = _case(kind, t, k, e, hid, n, block_m, seed=t + e, extra_blocks=2)
+    out, want = _run(c, kind)
+    assert_bf16_within_ulp(out, want, 1, f"prefill-down {kind} T={t} top{k} E={e}")
+
+
+def test_experts_of_other_ranks_give_zero_rows():
+    c = _case("int8", 120, 4, 8, 256, 512, 32, seed=5, local={0, 1, 2, 3})
+    out, want = _run(c, "int8")
+    assert_bf16_within_ulp(out, want, 1, "prefill-down, half of the experts remote")
+    assert float(want.abs().sum()) > 0 and torch.any(torch.all(out == 0, dim=1))
+
+
+def test_argument_errors():
+    c = _case("int8", 16, 2, 2, 128, 512, 32, seed=1)
+    pk = deepgemm.marlin_i8_contiguous_weight(c["w"].clone().to(DEV))
+    out = torch.zeros(32, 512, dtype=torch.bfloat16, device=DEV)
+    args = [c["inp"].to(DEV), pk, out, c["a_scale"].to(DEV), c["b_scale"].to(DEV), c["topk_w"].to(DEV),
+            c["ids"].to(DEV), c["experts"].to(DEV), c["used"].to(DEV), 2, 2]
+    bad = list(args)
+    bad[6] = bad[6].to(torch.int64)
+    with pytest.raises(RuntimeError):
+        deepgemm.moe_w8a8_marlin_prefill_down_fp8(*bad)
+    bad = list(args)
+    bad[1] = c["w"].to(DEV)                                   # not packed
+    with pytest.raises(RuntimeError):
+        deepgemm.moe_w8a8_marlin_prefill_down_fp8(*bad)
+    bad = list(args)
+    bad[2] = out.float()
+    with pytest.raises(RuntimeError):
+        deepgemm.moe_w8a8_marlin_prefill_down_fp8(*bad)
+    with pytest.raises(ValueError):
+        deepgemm.assert_moe_prefill_down_fp8_shapes(k=100, n=512)
+    with pytest.raises(ValueError):
+        deepgemm.assert_moe_prefill_down_fp8_shapes(k=128, n=640)
+    deepgemm.assert_moe_prefill_down_fp8_shapes(k=128, n=1024)

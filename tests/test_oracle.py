@@ -123,3 +123,24 @@ def test_dense_fp8_matches_reference():
     assert torch.equal(out.view(torch.int16), g["out"].view(torch.int16))
     out16 = O.ref_dense_scaled(g["a"], g["b"], g["a_scale"], g["b_scale"], torch.float16)
     assert torch.equal(out16.view(torch.int16), g["out_f16"].view(torch.int16))
+
+
+def test_sorted_routing_oracle_equals_the_per_pair_formula():
+    """build_sorted_routing + ref_prefill_down (block walk of the reference kernel) give every
+    (token, slot) row the plain formula; rows of experts marked remote are zero."""
+    g = torch.Generator().manual_seed(0)
+    t, k, e, hid, n = 50, 3, 5, 64, 32
+    topk = torch.rand(t, e, generator=g).topk(k, dim=1).indices
+    ids, ex, used = O.build_sorted_routing(topk, e, 16, local_experts={0, 1, 2, 4}, extra_blocks=1)
+    assert ids.numel() % 16 == 0 and ex.numel() == ids.numel() // 16 and int(used) == ids.numel() - 16
+    inp = torch.randint(-128, 128, (t * k, hid), generator=g).to(torch.int8)
+    w = torch.randint(-128, 128, (e, n, hid), generator=g).to(torch.int8)
+    a_s, b_s, tw = torch.rand(t * k, generator=g), torch.rand(e, n, generator=g), torch.rand(t, k, generator=g)
+    out = O.ref_prefill_down(inp, w, a_s, b_s, tw, ids, ex, used, k,
+                             torch.full((t * k, n), 9.0, dtype=torch.bfloat16))
+    for tok in range(t):
+        for s in range(k):
+            r, ee = tok * k + s, int(topk[tok, s])
+            want = ((inp[r].double() @ w[ee].double().t()).float() * (tw[tok, s] * a_s[r])) * b_s[ee]
+            want = torch.zeros(n) if ee == 3 else want
+            assert torch.equal(out[r], want.bfloat16()), (tok, s)
