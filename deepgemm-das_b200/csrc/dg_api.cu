@@ -373,20 +373,25 @@ int launch_w4(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   const int smem_bytes = L::total(table_bytes);
   if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
 
-  CUtensorMap tm_tok, tm_w;
-  int rc;
-  if (pr.mode == MODE_MASKED) {
-    const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
-    const uint64_t strides[2] = {(uint64_t)pr.K, (uint64_t)pr.M * pr.K};
-    const uint32_t box[3] = {128u, 128u, 1u};
-    rc = encode_map(&tm_tok, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, pr.a, dims, strides, box,
-                    CU_TENSOR_MAP_SWIZZLE_128B);
-  } else {
-    const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
-    const uint64_t strides[1] = {(uint64_t)pr.K};
-    const uint32_t box[2] = {128u, 128u};
-    rc = encode_map(&tm_tok, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.a, dims, strides, box,
-                    CU_TENSOR_MAP_SWIZZLE_128B);
+  // Token tiles: three boxes (128, 64, 32 rows) so an item fetches no more rows than the next
+  // power of two above its valid rows.
+  CUtensorMap tm_tok[3], tm_w;
+  int rc = DG_OK;
+  for (int i = 0; i < 3 && rc == DG_OK; ++i) {
+    const uint32_t rows = 128u >> i;
+    if (pr.mode == MODE_MASKED) {
+      const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
+      const uint64_t strides[2] = {(uint64_t)pr.K, (uint64_t)pr.M * pr.K};
+      const uint32_t box[3] = {128u, rows, 1u};
+      rc = encode_map(&tm_tok[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, pr.a, dims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
+      const uint64_t strides[1] = {(uint64_t)pr.K};
+      const uint32_t box[2] = {128u, rows};
+      rc = encode_map(&tm_tok[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.a, dims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    }
   }
   if (rc != DG_OK) return rc;
   {
@@ -411,7 +416,7 @@ int launch_w4(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
     configured.fetch_or(bit, std::memory_order_release);
   }
   const int grid = static_cast<int>(max_items < dev.sm_count ? max_items : dev.sm_count);
-  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_tok, tm_w, p);
+  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_tok[0], tm_tok[1], tm_tok[2], tm_w, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);

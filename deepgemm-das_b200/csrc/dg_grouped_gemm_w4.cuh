@@ -10,7 +10,8 @@
 //            warps (one thread per channel) read their 128-byte row into registers and
 //            release the stage at once.
 //   round slots (kW4Rounds)  each = a 32 KB token stage (two [128 tokens][128 B] tiles, UMMA B
-//            operand, TMA from L2) + 64 TMEM columns holding the unpacked weights of the same
+//            operand, TMA from L2; only the first 32 / 64 rows are fetched when the item has
+//            no more valid rows than that) + 64 TMEM columns holding the unpacked weights of the same
 //            256 K values, stored by the unpack warps with tcgen05.st: each packed word `x`
 //            becomes `x & 0xF0F0F0F0` and `(x << 4) & 0xF0F0F0F0`, i.e. every nibble becomes
 //            the int8 value 16*w -- the reference's rule
@@ -64,6 +65,8 @@ struct W4Smem {
 
 __global__ void __launch_bounds__(W4Smem::kThreads, 1)
 grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
+                       const __grid_constant__ CUtensorMap tm_tok64,
+                       const __grid_constant__ CUtensorMap tm_tok32,
                        const __grid_constant__ CUtensorMap tm_w, const KernelParams p) {
   using L = W4Smem;
   constexpr int WS = kW4WStages, RS = kW4Rounds;
@@ -109,6 +112,8 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
     mbar_init(bar_drain, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tm_tok);
+    tma_prefetch_desc(&tm_tok64);
+    tma_prefetch_desc(&tm_tok32);
     tma_prefetch_desc(&tm_w);
   }
 
@@ -210,6 +215,10 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
       bool ok = true;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
         const TileCoord t = dec.get(item);
+        // fetch 32, 64 or 128 token rows: what the UMMA reads is rows_valid rounded up to 16
+        const int box_rows = t.rows_valid <= 32 ? 32 : (t.rows_valid <= 64 ? 64 : 128);
+        const CUtensorMap* tm = box_rows == 128 ? &tm_tok : (box_rows == 64 ? &tm_tok64 : &tm_tok32);
+        const uint32_t round_bytes = 2u * static_cast<uint32_t>(box_rows) * kRowBytes;
         for (int wb = 0; wb < wblocks; ++wb, ++it) {
           const int s = it % RS;
           const uint32_t ph = (it / RS) & 1u;
@@ -217,14 +226,14 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_rfull(s), L::kTokBytes);
+          mbar_arrive_expect_tx(bar_rfull(s), round_bytes);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t dst = base + L::off_tok + s * L::kTokBytes + h * (L::kTokBytes / 2);
             if (p.mode == MODE_MASKED)
-              tma_load_3d(dst, &tm_tok, bar_rfull(s), (2 * wb + h) * 128, t.row0, t.g, pol_tok);
+              tma_load_3d(dst, tm, bar_rfull(s), (2 * wb + h) * 128, t.row0, t.g, pol_tok);
             else
-              tma_load_2d(dst, &tm_tok, bar_rfull(s), (2 * wb + h) * 128, t.row0, pol_tok);
+              tma_load_2d(dst, tm, bar_rfull(s), (2 * wb + h) * 128, t.row0, pol_tok);
           }
         }
       }

@@ -170,28 +170,39 @@ __device__ __forceinline__ int qg_dest_of(const QuantGroupParams& p, int r, int*
   return dest < p.m_cap ? dest : -1;
 }
 
-template <int KIND>
+// MAXVEC = 16-byte vectors of the row per thread (rows up to 256 * 8 * MAXVEC elements); the
+// smaller instantiation needs fewer registers, so more rows are resident per SM.
+template <int KIND, int MAXVEC>
 __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGroupParams p) {
   __shared__ float red[kQgThreads / 32];
   __shared__ int s_dest, s_src, s_expert;
   const int r = blockIdx.x;
+  // Every thread can tell a dropped row and find the source row by itself; the row's loads
+  // are issued before thread 0 works out the destination (a chain of dependent global loads)
+  // so that the two latencies overlap.
+  int src_row;
+  const int e_all = qg_expert_of(p, r, &src_row);
+  if (e_all < 0 || e_all >= p.G) {
+    if (threadIdx.x == 0 && p.dest_out != nullptr) p.dest_out[r] = -1;
+    return;
+  }
+  const int nvec = p.H / 8;  // 16-byte vectors of 8 bf16
+  const uint4* src = reinterpret_cast<const uint4*>(p.rows + static_cast<size_t>(src_row) * p.H);
+  uint4 v[MAXVEC];
+#pragma unroll
+  for (int i = 0; i < MAXVEC; ++i) {
+    const int idx = threadIdx.x + i * kQgThreads;
+    if (idx < nvec) v[i] = __ldg(src + idx);
+  }
   if (threadIdx.x == 0) {
     s_dest = qg_dest_of(p, r, &s_expert, &s_src);
     if (p.dest_out != nullptr) p.dest_out[r] = s_dest;
   }
-  __syncthreads();
-  const int dest = s_dest;
-  if (dest < 0) return;
-
-  const int nvec = p.H / 8;  // 16-byte vectors of 8 bf16
-  const uint4* src = reinterpret_cast<const uint4*>(p.rows + static_cast<size_t>(s_src) * p.H);
-  uint4 v[kQgMaxVec];
   float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kQgMaxVec; ++i) {
+  for (int i = 0; i < MAXVEC; ++i) {
     const int idx = threadIdx.x + i * kQgThreads;
     if (idx < nvec) {
-      v[i] = __ldg(src + idx);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -200,7 +211,9 @@ __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGrou
       }
     }
   }
-  amax = fmaxf(qg_block_max(amax, red), 1e-10f);
+  amax = fmaxf(qg_block_max(amax, red), 1e-10f);  // its barrier also publishes s_dest
+  const int dest = s_dest;
+  if (dest < 0) return;
   constexpr float kQmax = (KIND == DG_KIND_E4M3) ? 448.0f : 127.0f;
   // torch evaluates `qmax / absmax` (scalar / tensor) as reciprocal(absmax) * qmax: two
   // roundings, reproduced here so that ties fall the same way
@@ -211,7 +224,7 @@ __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGrou
   }
   uint2* dst = reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.a_out) + (size_t)dest * p.H);
 #pragma unroll
-  for (int i = 0; i < kQgMaxVec; ++i) {
+  for (int i = 0; i < MAXVEC; ++i) {
     const int idx = threadIdx.x + i * kQgThreads;
     if (idx < nvec) {
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
@@ -283,10 +296,17 @@ inline cudaError_t launch_quant_group(const QuantGroupParams& p, cudaStream_t st
   qg_starts_kernel<<<1, 32, 0, stream>>>(p);
   if (p.sorted_ids != nullptr)
     qg_copy_kernel<<<p.R, kQgCopyThreads, 0, stream>>>(p);
-  else if (p.kind == DG_KIND_E4M3)
-    qg_quantise_kernel<DG_KIND_E4M3><<<p.R, kQgThreads, 0, stream>>>(p);
-  else
-    qg_quantise_kernel<DG_KIND_I8><<<p.R, kQgThreads, 0, stream>>>(p);
+  else if (p.H <= kQgThreads * 8 * 4) {
+    if (p.kind == DG_KIND_E4M3)
+      qg_quantise_kernel<DG_KIND_E4M3, 4><<<p.R, kQgThreads, 0, stream>>>(p);
+    else
+      qg_quantise_kernel<DG_KIND_I8, 4><<<p.R, kQgThreads, 0, stream>>>(p);
+  } else {
+    if (p.kind == DG_KIND_E4M3)
+      qg_quantise_kernel<DG_KIND_E4M3, kQgMaxVec><<<p.R, kQgThreads, 0, stream>>>(p);
+    else
+      qg_quantise_kernel<DG_KIND_I8, kQgMaxVec><<<p.R, kQgThreads, 0, stream>>>(p);
+  }
   return cudaGetLastError();
 }
 
