@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz from the REFERENCE's own helper functions.
 
-Run in a container that has the reference checkout (default /root/reference, or pass its
-path):   python tests/golden/make_golden.py [reference_dir]
+Run where a checkout of the reference is available, passing its path (or setting
+DEEPGEMM_REFERENCE_DIR):   python tests/golden/make_golden.py <reference_dir>
 
 It imports the pure-torch oracles that the reference's op_test/ scripts compare their GPU
 kernels with, feeds them small seeded inputs and stores inputs and outputs.  The reference
@@ -21,7 +21,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DEEPGEMM_REFERENCE_DIR", "")
+if not os.path.isdir(os.path.join(REF, "op_test")):
+    sys.exit("usage: make_golden.py <directory of the HYGON-AI/deepgemm-das checkout>")
 
 
 class _Stub(types.ModuleType):
