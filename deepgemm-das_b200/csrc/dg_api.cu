@@ -182,23 +182,29 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // group; contiguous: (K, M_total).  Rows past the extent read as zero.
   const CUtensorMapDataType dt_a =
       (KIND == DG_KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  // tm_a32 fetches one 32-row slice of it, for tiles with fewer than 97 valid rows.
-  CUtensorMap tm_a, tm_a32, tm_b;
+  // tm_a64 / tm_a32 fetch the first 64 / 32 rows of it, for tiles with no more valid rows.
+  CUtensorMap tm_a, tm_a64, tm_a32, tm_b;
   int rc;
   if (pr.mode == MODE_MASKED) {
     const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
     const uint64_t strides[2] = {(uint64_t)pr.K * esize, (uint64_t)pr.M * pr.K * esize};
     const uint32_t box[3] = {(uint32_t)elems_per_row, (uint32_t)kBM, 1u};
+    const uint32_t box64[3] = {(uint32_t)elems_per_row, 64u, 1u};
     const uint32_t box32[3] = {(uint32_t)elems_per_row, 32u, 1u};
     rc = encode_map(&tm_a, dt_a, 3, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_a64, dt_a, 3, pr.a, dims, strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
       rc = encode_map(&tm_a32, dt_a, 3, pr.a, dims, strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
     const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
     const uint64_t strides[1] = {(uint64_t)pr.K * esize};
     const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)kBM};
+    const uint32_t box64[2] = {(uint32_t)elems_per_row, 64u};
     const uint32_t box32[2] = {(uint32_t)elems_per_row, 32u};
     rc = encode_map(&tm_a, dt_a, 2, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_a64, dt_a, 2, pr.a, dims, strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
       rc = encode_map(&tm_a32, dt_a, 2, pr.a, dims, strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
   }
@@ -240,7 +246,7 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // With narrowing allowed the item count can reach max_blocks * ceil(N / 32).
   const long long grid_items = p.narrow ? max_blocks * ((pr.N + 31) / 32) : max_items;
   const int grid = static_cast<int>(grid_items < dev.sm_count ? grid_items : dev.sm_count);
-  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_a32, tm_b, tm_b64, tm_b32, p);
+  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_a64, tm_a32, tm_b, tm_b64, tm_b32, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);

@@ -80,14 +80,15 @@ struct KernelParams {
 };
 
 // Shape of one pipeline stage for a tile with `rows_valid` rows and `bn_eff` columns.  A tile
-// with at most 32 valid rows fetches only a 32-row slice of A (the UMMA still reads 128 rows;
-// what it reads beyond the slice is stale shared memory that only reaches accumulator rows
-// nobody stores).  Splitting A into several slices was measured 18 % slower on the decode
-// workload than one 128-row copy, so 33..128 rows fetch the whole tile.  When both operands
+// with at most 32 / 64 valid rows fetches only a 32 / 64-row slice of A with one TMA box of
+// that height (the UMMA still reads 128 rows; what it reads beyond the slice is stale shared
+// memory that only reaches accumulator rows nobody stores).  Several 32-row copies per tile
+// were measured 18 % slower on the decode workload than one copy, so there is one box per
+// height.  When both operands
 // are narrow, several K blocks share one stage slot so the bytes in flight per stage stay
 // near 32 KB.
 struct StageShape {
-  int a_rows;         // rows of A fetched per K block: 32 or 128
+  int a_rows;         // rows of A fetched per K block: 32, 64 or 128 (one TMA box each)
   int kps;            // K blocks per stage
   uint32_t a_stride;  // bytes between the A sub-tiles of consecutive K blocks in a slot
   uint32_t b_stride;  // same for the weight sub-tiles
@@ -95,7 +96,7 @@ struct StageShape {
 };
 __device__ __forceinline__ StageShape stage_shape(int rows_valid, int bn_eff, int bn) {
   StageShape sh;
-  sh.a_rows = rows_valid <= 32 ? 32 : kBM;
+  sh.a_rows = rows_valid <= 32 ? 32 : (rows_valid <= 64 ? 64 : kBM);
   sh.kps = min(bn / bn_eff, kBM / sh.a_rows);
   sh.a_stride = static_cast<uint32_t>(sh.a_rows) * kRowBytes;
   sh.b_stride = static_cast<uint32_t>(bn_eff) * kRowBytes;
@@ -273,6 +274,7 @@ struct ItemDecoder {
 template <int KIND, int BN, int STAGES>
 __global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
+                    const __grid_constant__ CUtensorMap tm_a64,
                     const __grid_constant__ CUtensorMap tm_a32,
                     const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_b64,
@@ -419,7 +421,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
           const TileCoord t = dec.get(item);
           const StageShape sh = stage_shape(t.rows_valid, kNarrow ? bn_eff : BN, BN);
-          const CUtensorMap* tm_act = (sh.a_rows == kBM) ? &tm_a : &tm_a32;
+          const CUtensorMap* tm_act = (sh.a_rows == kBM) ? &tm_a : (sh.a_rows == 64 ? &tm_a64 : &tm_a32);
           const int kps = kNarrow ? sh.kps : 1;
           for (int kb0 = 0; kb0 < p.kblocks; kb0 += kps, ++it) {
             const int s = it % STAGES;
