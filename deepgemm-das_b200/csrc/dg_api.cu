@@ -663,6 +663,7 @@ static int quant_group_common(const dg_quant_group_args* a, int32_t* scratch, vo
   if (a->num_rows < 0 || a->hidden < 8 || a->hidden % 8 != 0 || a->num_groups < 1 ||
       a->align < 1 || a->m_cap < 0)
     return DG_ERR_BAD_SHAPE;
+  if (a->row_scale != nullptr && a->hidden % 16 != 0) return DG_ERR_BAD_SHAPE;  // 16-byte copies
   if (a->num_groups > DG_MAX_GROUPS || a->hidden > DG_MAX_QUANT_HIDDEN) return DG_ERR_TOO_LARGE;
   if (!a->a_out || !a->a_scale_out || !a->m_indices_out || !scratch) return DG_ERR_NULL_POINTER;
   if (a->num_rows > 0 && (!a->rows || !a->expert)) return DG_ERR_NULL_POINTER;
@@ -674,6 +675,7 @@ static int quant_group_common(const dg_quant_group_args* a, int32_t* scratch, vo
   p.rows = static_cast<const __nv_bfloat16*>(a->rows);
   p.expert = a->expert;
   p.src_index = a->src_index;
+  p.row_scale = a->row_scale;
   p.a_out = a->a_out;
   p.a_scale_out = a->a_scale_out;
   p.m_indices_out = a->m_indices_out;

@@ -257,15 +257,18 @@ __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGrou
   }
 }
 
-// Sorted-ids input: the rows are quantised already; copy H bytes and the (weighted) scale.
+// Rows that are quantised already (row_scale given; always so for sorted-ids input): copy H
+// bytes and the (weighted) scale.
 constexpr int kQgCopyThreads = 64;
 __global__ void __launch_bounds__(kQgCopyThreads) qg_copy_kernel(const QuantGroupParams p) {
   __shared__ int s_dest, s_src, s_expert;
   const int r = blockIdx.x;
   if (threadIdx.x == 0) {
     s_dest = qg_dest_of(p, r, &s_expert, &s_src);
+    if (p.dest_out != nullptr && p.sorted_ids == nullptr) p.dest_out[r] = s_dest;
     if (s_dest >= 0) {
-      if (p.dest_out != nullptr) p.dest_out[s_src] = s_dest;
+      // sorted-ids input: dest is indexed by the source row (one entry per row of `rows`)
+      if (p.dest_out != nullptr && p.sorted_ids != nullptr) p.dest_out[s_src] = s_dest;
       const float w = p.row_weight ? p.row_weight[s_src] : 1.0f;
       p.a_scale_out[s_dest] = p.row_weight ? __fmul_rn(w, p.row_scale[s_src]) : p.row_scale[s_src];
       p.m_indices_out[s_dest] = s_expert;
@@ -294,7 +297,7 @@ inline cudaError_t launch_quant_group(const QuantGroupParams& p, cudaStream_t st
   qg_histogram_kernel<<<hblocks, 256, 0, stream>>>(p);
   qg_scan_kernel<<<p.G, 256, 0, stream>>>(p);
   qg_starts_kernel<<<1, 32, 0, stream>>>(p);
-  if (p.sorted_ids != nullptr)
+  if (p.row_scale != nullptr)  // rows are quantised already
     qg_copy_kernel<<<p.R, kQgCopyThreads, 0, stream>>>(p);
   else if (p.H <= kQgThreads * 8 * 4) {
     if (p.kind == DG_KIND_E4M3)

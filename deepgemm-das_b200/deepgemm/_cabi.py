@@ -121,6 +121,7 @@ class QuantGroupArgs(C.Structure):
         ("scratch", C.c_void_p),
         ("scratch_bytes", C.c_size_t),
         ("src_index", C.c_void_p),
+        ("row_scale", C.c_void_p),
     ]
 
 

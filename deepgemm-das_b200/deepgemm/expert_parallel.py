@@ -48,15 +48,22 @@ def build_dispatch_plan(topk_ids: torch.Tensor, num_experts: int, world: int) ->
 
 
 def dispatch_tokens(hidden: torch.Tensor, plan: DispatchPlan, num_experts: int, rank: int,
-                    world: int, group=None, return_splits: bool = False):
+                    world: int, group=None, return_splits: bool = False,
+                    row_scale: Optional[torch.Tensor] = None):
     """All-to-all of the routed rows.  Returns (rows [R, H] received by this rank, in source-rank
     order, local expert id [R] of each) and, with ``return_splits``, the rows received from each
-    rank (what ``return_rows`` needs to send results back)."""
+    rank (what ``return_rows`` needs to send results back).  ``hidden`` may be any dtype; when
+    it holds rows quantised at the source, pass their scales as ``row_scale`` [T] and the scales
+    of the received rows are appended to the result (half the bytes on the wire for e4m3, and
+    each token is quantised once instead of once per expert)."""
     e_local = num_experts // world
     send_rows = hidden.index_select(0, plan.send_token)
+    send_scale = row_scale.index_select(0, plan.send_token) if row_scale is not None else None
     if world == 1:
         res = (send_rows, plan.send_expert.clone())
-        return res + (list(plan.send_splits),) if return_splits else res
+        if return_splits:
+            res = res + (list(plan.send_splits),)
+        return res + (send_scale,) if row_scale is not None else res
     import torch.distributed as dist
     # 1) counts: rank r receives, from every source, its rows-per-local-expert vector
     send_counts = plan.counts_per_expert.to(torch.int64).contiguous()          # [world * e_local]
@@ -67,14 +74,21 @@ def dispatch_tokens(hidden: torch.Tensor, plan: DispatchPlan, num_experts: int, 
     # 2) payload
     recv_rows = torch.empty((sum(recv_splits), hidden.shape[1]), dtype=hidden.dtype,
                             device=hidden.device)
-    dist.all_to_all_single(recv_rows, send_rows, output_split_sizes=recv_splits,
+    wire = torch.uint8 if hidden.element_size() == 1 else hidden.dtype   # NCCL has no fp8 type here
+    dist.all_to_all_single(recv_rows.view(wire), send_rows.view(wire), output_split_sizes=recv_splits,
                            input_split_sizes=plan.send_splits, group=group)
+    recv_scale = None
+    if send_scale is not None:
+        recv_scale = torch.empty((sum(recv_splits),), dtype=send_scale.dtype, device=hidden.device)
+        dist.all_to_all_single(recv_scale, send_scale.contiguous(), output_split_sizes=recv_splits,
+                               input_split_sizes=plan.send_splits, group=group)
     # local expert of every received row: per source rank, experts ascend with the given counts
     ids = torch.arange(e_local, device=hidden.device).repeat(world)
     recv_expert = torch.repeat_interleave(ids, recv_counts.reshape(-1).to(hidden.device))
+    res = (recv_rows, recv_expert)
     if return_splits:
-        return recv_rows, recv_expert, recv_splits
-    return recv_rows, recv_expert
+        res = res + (recv_splits,)
+    return res + (recv_scale,) if row_scale is not None else res
 
 
 def return_rows(rows_out: torch.Tensor, recv_splits: list, send_splits: list, world: int,
@@ -130,24 +144,37 @@ def ep_gate_up_forward(hidden: torch.Tensor, topk_ids: torch.Tensor, b_packed: t
 
 def ep_moe_forward(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
                    w13, w2, num_experts: int, rank: int, world: int, group=None, *,
-                   kind: str = "fp8", expert_mlp=None, combine=None) -> torch.Tensor:
-    """A whole expert-parallel MoE layer for this rank's tokens: dispatch all-to-all -> fused
-    quantise/group -> gate/up GEMM -> SiLU*up + requantise -> down GEMM -> reverse all-to-all ->
-    weighted top-k sum.  ``w13`` / ``w2`` are (packed weight, scale) of this rank's experts.
-    ``expert_mlp(rows, local_expert) -> [R, N]`` and ``combine(y, src_row, weights) -> [T, N]``
-    replace the CUDA steps (the CPU tests of the communication pattern pass torch functions)."""
+                   kind: str = "fp8", quantise_before_dispatch: bool = True,
+                   expert_mlp=None, combine=None) -> torch.Tensor:
+    """A whole expert-parallel MoE layer for this rank's tokens: per-token quantise -> dispatch
+    all-to-all of the quantised rows and their scales -> group by expert -> gate/up GEMM ->
+    SiLU*up + requantise -> down GEMM -> reverse all-to-all -> weighted top-k sum.  ``w13`` /
+    ``w2`` are (packed weight, scale) of this rank's experts.  With
+    ``quantise_before_dispatch=False`` the bf16 rows travel and are quantised by the receiver
+    (same results: a row's quantisation depends on the row only).  ``expert_mlp(rows,
+    local_expert) -> [R, N]`` and ``combine(y, src_row, weights) -> [T, N]`` replace the CUDA
+    steps (the CPU tests of the communication pattern pass torch functions)."""
     t, k = topk_ids.shape
     e_local = num_experts // world
     plan = build_dispatch_plan(topk_ids, num_experts, world)
-    rows, recv_expert, recv_splits = dispatch_tokens(hidden, plan, num_experts, rank, world, group,
-                                                     return_splits=True)
     if expert_mlp is None:
         from .moe_chain import expert_mlp_contiguous
-        from .quant_group import quantize_group_rows
-        a, a_scale, m_indices, dest, _ = quantize_group_rows(rows, recv_expert.to(torch.int32), e_local,
-                                                             kind=kind)
+        from .quant_group import quantize_group_rows, quantize_rows
+        if quantise_before_dispatch:
+            q, q_scale = quantize_rows(hidden, kind=kind)
+            rows, recv_expert, recv_splits, recv_scale = dispatch_tokens(
+                q, plan, num_experts, rank, world, group, return_splits=True, row_scale=q_scale)
+            a, a_scale, m_indices, dest, _ = quantize_group_rows(
+                rows, recv_expert.to(torch.int32), e_local, kind=kind, row_scale=recv_scale)
+        else:
+            rows, recv_expert, recv_splits = dispatch_tokens(hidden, plan, num_experts, rank, world,
+                                                             group, return_splits=True)
+            a, a_scale, m_indices, dest, _ = quantize_group_rows(rows, recv_expert.to(torch.int32),
+                                                                 e_local, kind=kind)
         y = expert_mlp_contiguous(a, a_scale, m_indices, w13, w2, kind=kind).index_select(0, dest.long())
     else:
+        rows, recv_expert, recv_splits = dispatch_tokens(hidden, plan, num_experts, rank, world, group,
+                                                         return_splits=True)
         y = expert_mlp(rows, recv_expert)
     back = return_rows(y, recv_splits, plan.send_splits, world, group)      # row i = pair send_pair[i]
     src_row = torch.empty(t * k, dtype=torch.int32, device=hidden.device)
@@ -204,8 +231,41 @@ def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup:
     sync()
     a2a_ms = e0.elapsed_time(e1) / steps
 
+    # the same dispatch with rows quantised at the source: e4m3 payload + fp32 scales
+    from .quant_group import quantize_group_rows, quantize_rows
+    for _ in range(warmup):
+        q8, q8_scale = quantize_rows(hidden)
+    torch.cuda.synchronize()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        q8, q8_scale = quantize_rows(hidden)
+    e1.record()
+    torch.cuda.synchronize()
+    quant_src_ms = e0.elapsed_time(e1) / steps
+    for _ in range(warmup):
+        rows8, _, scale8 = dispatch_tokens(q8, plan, num_experts, rank, world, row_scale=q8_scale)
+    sync()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        rows8, _, scale8 = dispatch_tokens(q8, plan, num_experts, rank, world, row_scale=q8_scale)
+    e1.record()
+    sync()
+    a2a8_ms = e0.elapsed_time(e1) / steps
+    for _ in range(warmup):
+        quantize_group_rows(rows8, recv_expert.to(torch.int32), e_local, row_scale=scale8)
+    torch.cuda.synchronize()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        quantize_group_rows(rows8, recv_expert.to(torch.int32), e_local, row_scale=scale8)
+    e1.record()
+    torch.cuda.synchronize()
+    group8_ms = e0.elapsed_time(e1) / steps
+    del rows8, scale8, q8, q8_scale
+
     # quantise + group + pad (fused producer kernels; reported beside the two headline figures)
-    from .quant_group import quantize_group_rows
     recv_expert = recv_expert.to(torch.int32)
     for _ in range(warmup):
         a, a_scale, m_indices, _, _ = quantize_group_rows(rows, recv_expert, e_local)
@@ -273,10 +333,11 @@ def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup:
     combine_ms = timed(lambda: combine_rows(back_holder["rows"], src_row.view(tokens, top_k), weights, out=final))
 
     valid = int((m_indices >= 0).sum())
-    chain = torch.tensor([act_ms, down_ms, back_ms, combine_ms], device=device, dtype=torch.float64)
+    chain = torch.tensor([act_ms, down_ms, back_ms, combine_ms, quant_src_ms, a2a8_ms, group8_ms],
+                         device=device, dtype=torch.float64)
     if dist:
         dist.all_reduce(chain, op=dist.ReduceOp.MAX)
-    act_ms, down_ms, back_ms, combine_ms = (float(x) for x in chain.tolist())
+    act_ms, down_ms, back_ms, combine_ms, quant_src_ms, a2a8_ms, group8_ms = (float(x) for x in chain.tolist())
     stats = torch.tensor([a2a_ms, gemm_ms, prep_ms], device=device, dtype=torch.float64)
     flops = torch.tensor([2.0 * valid * n * hidden_k], device=device, dtype=torch.float64)
     sent_remote = sum(s for r, s in enumerate(plan.send_splits) if r != rank) * hidden_k * 2
@@ -297,6 +358,10 @@ def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup:
     down_flops = torch.tensor([2.0 * valid * hidden_k * inter], device=device, dtype=torch.float64)
     if dist:
         dist.all_reduce(down_flops, op=dist.ReduceOp.SUM)
+    res["fp8_dispatch"] = {   # rows quantised once per token at the source, half the bytes on the wire
+        "quantise_tokens_ms": quant_src_ms, "all_to_all_ms_max_over_ranks": a2a8_ms,
+        "group_ms_max_over_ranks": group8_ms,
+        "all_to_all_remote_bytes_max_per_rank": float(sent) / 2 + float(sent) / (hidden_k * 2) * 4}
     res["down_chain"] = {
         "silu_mul_quant_ms": act_ms,
         "silu_mul_quant_gbs_this_rank": valid * (n * 2 + inter + 4) / (act_ms * 1e-3) / 1e9,

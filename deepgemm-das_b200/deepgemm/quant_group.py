@@ -26,16 +26,28 @@ def quant_group_capacity(num_rows: int, num_groups: int, align: int = 256) -> in
 def quantize_group_rows(rows: torch.Tensor, expert: torch.Tensor, num_groups: int, *,
                         kind: str = "fp8", align: int = 256, m_cap: Optional[int] = None,
                         scratch: Optional[torch.Tensor] = None,
-                        src_index: Optional[torch.Tensor] = None
+                        src_index: Optional[torch.Tensor] = None,
+                        row_scale: Optional[torch.Tensor] = None
                         ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """rows bf16 [R, H] (CUDA), expert int32 [R] -> (a [m_cap, H] e4m3 / int8, a_scale fp32
     [m_cap], m_indices int32 [m_cap], dest int32 [R], m_total int32 [1]); all on the device,
     no synchronisation.  Pass the results to the contiguous grouped GEMM as they are.  With
     ``src_index`` (int32 [R], entries in [0, rows.shape[0])) row r is read from
-    ``rows[src_index[r]]``, so the top-k copies of a token need not be materialised."""
+    ``rows[src_index[r]]``, so the top-k copies of a token need not be materialised.  With
+    ``row_scale`` (fp32, one per row of ``rows``) the rows are e4m3 / int8 already and are only
+    grouped: bytes copied, scales carried along."""
     if not rows.is_cuda:
         raise RuntimeError("quantize_group_rows: rows must be a CUDA tensor (there is no CPU implementation)")
-    if rows.dim() != 2 or rows.dtype != torch.bfloat16 or not rows.is_contiguous():
+    if kind not in ("fp8", "int8"):
+        raise ValueError(f"kind must be 'fp8' or 'int8', got {kind!r}")
+    if row_scale is not None:
+        want = torch.float8_e4m3fn if kind == "fp8" else torch.int8
+        if rows.dim() != 2 or rows.dtype != want or not rows.is_contiguous():
+            raise ValueError(f"with row_scale, rows must be a contiguous {want} [R, H] tensor")
+        if row_scale.dtype != torch.float32 or row_scale.numel() != rows.shape[0]:
+            raise ValueError("row_scale must be fp32 with one entry per row")
+        row_scale = row_scale.contiguous()
+    elif rows.dim() != 2 or rows.dtype != torch.bfloat16 or not rows.is_contiguous():
         raise ValueError(f"rows must be a contiguous bf16 [R, H] tensor, got {rows.dtype} {tuple(rows.shape)}")
     r, h = (int(v) for v in rows.shape)
     if src_index is not None:
@@ -48,8 +60,6 @@ def quantize_group_rows(rows: torch.Tensor, expert: torch.Tensor, num_groups: in
     if expert.dtype != torch.int32:
         expert = expert.to(torch.int32)
     expert = expert.contiguous()
-    if kind not in ("fp8", "int8"):
-        raise ValueError(f"kind must be 'fp8' or 'int8', got {kind!r}")
     k = KIND_E4M3 if kind == "fp8" else KIND_I8
     if m_cap is None:
         m_cap = quant_group_capacity(r, num_groups, align)
@@ -70,8 +80,18 @@ def quantize_group_rows(rows: torch.Tensor, expert: torch.Tensor, num_groups: in
         a_scale_out=a_scale.data_ptr(), m_indices_out=m_indices.data_ptr(), dest_out=dest.data_ptr(),
         m_total_out=m_total.data_ptr(), scratch=scratch.data_ptr(),
         scratch_bytes=scratch.numel() * scratch.element_size(),
-        src_index=src_index.data_ptr() if src_index is not None else None)
+        src_index=src_index.data_ptr() if src_index is not None else None,
+        row_scale=row_scale.data_ptr() if row_scale is not None else None)
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         _cabi.check(_cabi.lib.dg_quant_group_rows(C.byref(args), C.c_void_p(stream)), "dg_quant_group_rows")
     return a, a_scale, m_indices, dest, m_total
+
+
+def quantize_rows(rows: torch.Tensor, *, kind: str = "fp8") -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row quantisation only: bf16 [R, H] -> (q [R, H] e4m3 / int8, scale fp32 [R]), rows in
+    place (the producer with a single group and no padding)."""
+    r = rows.shape[0]
+    expert = torch.zeros((r,), dtype=torch.int32, device=rows.device)
+    a, a_scale, _, _, _ = quantize_group_rows(rows, expert, 1, kind=kind, align=1, m_cap=max(r, 1))
+    return a[:r], a_scale[:r]

@@ -274,6 +274,11 @@ typedef struct dg_quant_group_args {
   const int32_t* src_index;     /* NULL, or [R]: input row r is rows[src_index[r]] (entries must be
                                    valid rows of `rows`), so that the top-k copies of a token can
                                    all read the token's one row */
+  const float*   row_scale;     /* NULL, or [rows of `rows`]: the rows are quantised already (`rows`
+                                   holds `hidden` one-byte elements of type `kind` per row, hidden a
+                                   multiple of 16); they are copied and a_scale_out gets row_scale of
+                                   the row read -- grouping only, e.g. after a dispatch that moved
+                                   quantised rows */
 } dg_quant_group_args;
 
 #define DG_MAX_QUANT_HIDDEN 16384

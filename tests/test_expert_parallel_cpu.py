@@ -61,7 +61,11 @@ def _worker(rank, world, port, q):
         hidden, topk = _inputs(rank)
         plan = ep.build_dispatch_plan(topk, E, world)
         rows, expert_local = ep.dispatch_tokens(hidden, plan, E, rank, world)
-        q.put((rank, rows.float(), expert_local))
+        # quantised rows travel as bytes with their scales: here the "scale" names (rank, token)
+        tag = torch.arange(T, dtype=torch.float32) + 1000.0 * rank
+        rows8, _, scale = ep.dispatch_tokens(hidden.view(torch.uint8), plan, E, rank, world, row_scale=tag)
+        assert torch.equal(rows8.view(torch.bfloat16), rows)
+        q.put((rank, rows.float(), expert_local, scale))
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -86,22 +90,24 @@ def test_two_rank_dispatch_matches_single_process_routing():
         p.start()
     got = {}
     for _ in range(world):
-        r, rows, expert_local = q.get(timeout=90)
-        got[r] = (rows, expert_local)
+        r, rows, expert_local, scale = q.get(timeout=90)
+        got[r] = (rows, expert_local, scale)
     for p in procs:
         p.join(timeout=30)
         assert p.exitcode == 0
     e_local = E // world
     for r in range(world):
         # expectation: for each source rank in order, its rows for r's experts, ordered by expert
-        want_rows, want_exp = [], []
+        want_rows, want_exp, want_tag = [], [], []
         for src in range(world):
             hidden, topk = _inputs(src)
             plan = ep.build_dispatch_plan(topk, E, world)
             sel = (plan.send_expert >= r * e_local) & (plan.send_expert < (r + 1) * e_local)
             want_rows.append(hidden.index_select(0, plan.send_token[sel]).float())
             want_exp.append(plan.send_expert[sel] - r * e_local)
-        rows, expert_local = got[r]
+            want_tag.append(plan.send_token[sel].float() + 1000.0 * src)
+        rows, expert_local, scale = got[r]
+        assert torch.equal(scale, torch.cat(want_tag))
         assert torch.equal(rows, torch.cat(want_rows))
         assert torch.equal(expert_local, torch.cat(want_exp))
 

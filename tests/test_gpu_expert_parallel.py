@@ -132,7 +132,7 @@ def _layer_tokens(rank):
     return hidden, topk, w
 
 
-def _run_layer(rank, world, dev):
+def _run_layer(rank, world, dev, quantise_before_dispatch=True):
     w13, s13, w2, s2 = _layer_weights()
     e_local = E // world
     sl = slice(rank * e_local, (rank + 1) * e_local)
@@ -140,7 +140,8 @@ def _run_layer(rank, world, dev):
     hidden, topk, w = _layer_tokens(rank)
     out = ep.ep_moe_forward(hidden.to(dev), topk.to(dev), w.to(dev),
                             (pk(w13[sl].clone().to(dev)), s13[sl].to(dev)),
-                            (pk(w2[sl].clone().to(dev)), s2[sl].to(dev)), E, rank, world)
+                            (pk(w2[sl].clone().to(dev)), s2[sl].to(dev)), E, rank, world,
+                            quantise_before_dispatch=quantise_before_dispatch)
     torch.cuda.synchronize()
     return out.cpu()
 
@@ -150,6 +151,9 @@ def test_single_rank_layer_matches_oracle():
     hidden, topk, w = _layer_tokens(0)
     ref = O.ref_moe_layer(hidden, topk, w, *_layer_weights())
     assert_calc_diff(out, ref.float(), 1e-3, "expert-parallel layer, one rank")    # calc_diff < 1e-3
+    late = _run_layer(0, 1, torch.device("cuda", 0), quantise_before_dispatch=False)
+    assert torch.equal(out.view(torch.int16), late.view(torch.int16)), \
+        "quantising before or after the dispatch must not change a single bit"
 
 
 def _layer_worker(rank, world, port, q):
@@ -159,7 +163,10 @@ def _layer_worker(rank, world, port, q):
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        q.put((rank, _run_layer(rank, world, dev)))
+        early = _run_layer(rank, world, dev, quantise_before_dispatch=True)
+        late = _run_layer(rank, world, dev, quantise_before_dispatch=False)
+        assert torch.equal(early.view(torch.int16), late.view(torch.int16))
+        q.put((rank, early))
     finally:
         dist.barrier()
         dist.destroy_process_group()

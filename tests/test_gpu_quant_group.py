@@ -74,3 +74,27 @@ def test_argument_errors():
         quantize_group_rows(torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV), e, 2)   # H % 8
     with pytest.raises(RuntimeError):
         quantize_group_rows(rows.cpu(), e.cpu(), 2)
+
+
+@pytest.mark.parametrize("kind", ["fp8", "int8"])
+def test_grouping_rows_quantised_elsewhere_gives_the_same_operands(kind):
+    """quantize_rows + grouping with row_scale (what a rank does with rows that were quantised
+    before the dispatch) must produce exactly what quantise+group in one go does."""
+    from deepgemm.quant_group import quantize_rows
+    gen = torch.Generator().manual_seed(11)
+    R, H, G = 777, 1024, 9
+    rows = (torch.randn(R, H, generator=gen) * 2).bfloat16().to(DEV)
+    expert = torch.randint(-1, G, (R,), generator=gen).to(torch.int32).to(DEV)
+    want = quantize_group_rows(rows, expert, G, kind=kind, align=128)
+    q, s = quantize_rows(rows, kind=kind)
+    quant = per_token_quant_fp8 if kind == "fp8" else per_token_quant_int8
+    q_ref, s_ref = quant(rows.cpu())
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(s.cpu(), s_ref.reshape(-1))
+    got = quantize_group_rows(q, expert, G, kind=kind, align=128, row_scale=s)
+    torch.cuda.synchronize()
+    m = int(want[4])
+    assert int(got[4]) == m
+    assert torch.equal(got[2], want[2]) and torch.equal(got[3], want[3])          # m_indices, dest
+    valid = (want[2][:m] >= 0).cpu()
+    assert torch.equal(got[0][:m].cpu().view(torch.uint8)[valid], want[0][:m].cpu().view(torch.uint8)[valid])
+    assert torch.equal(got[1][:m].cpu()[valid], want[1][:m].cpu()[valid])
