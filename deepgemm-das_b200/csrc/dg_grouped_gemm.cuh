@@ -116,7 +116,9 @@ struct SmemLayout {
   // full[S], empty[S], acc_full[2], acc_empty[2], drain
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;  // tmem slot, abort, n_items, pad
-  static constexpr int off_table = off_misc + 16;
+  static constexpr int off_bs = (off_misc + 16 + 15) & ~15;  // a tile's weight scales, one strip per epilogue warp; read as float4
+  static constexpr int off_table = off_bs + 4 * BN * 4;
+  static_assert(off_bs % 16 == 0 && off_table % 4 == 0, "scale strips are read with 16-byte loads");
   static constexpr int kThreads = 192;
   static constexpr int kTmemCols = 2 * BN;
   __host__ __device__ static constexpr int total(int table_bytes) {
@@ -128,7 +130,7 @@ struct SmemLayout {
 struct EpiRow {
   float as;              // a_scale of this row (1 when unscaled)
   float bs_g;            // per-group weight scale (TENSOR_WISE)
-  const float* bs_row;   // b_scale[g] + n0 (PER_CHANNEL)
+  const float* bs_row;   // the tile's weight scales (PER_CHANNEL), staged in shared memory
   __nv_bfloat16* d_row;  // &D[row][n0]
   uint32_t* dbg_row;     // &debug_acc[row][n0] or nullptr
 };
@@ -147,8 +149,8 @@ __device__ __forceinline__ void epilogue_store32(const uint32_t (&r)[32], const 
       for (int i = 0; i < 8; ++i)
         v[i] = kIntAcc ? __int2float_rn(static_cast<int>(r[j + i])) : __uint_as_float(r[j + i]);
       if (scale_mode == DG_SCALE_PER_CHANNEL) {
-        const float4 b0 = __ldg(reinterpret_cast<const float4*>(e.bs_row + col + j));
-        const float4 b1 = __ldg(reinterpret_cast<const float4*>(e.bs_row + col + j + 4));
+        const float4 b0 = *reinterpret_cast<const float4*>(e.bs_row + col + j);
+        const float4 b1 = *reinterpret_cast<const float4*>(e.bs_row + col + j + 4);
         v[0] = (v[0] * e.as) * b0.x;
         v[1] = (v[1] * e.as) * b0.y;
         v[2] = (v[2] * e.as) * b0.z;
@@ -206,7 +208,7 @@ __device__ __forceinline__ void epilogue_store32_scalar(const uint32_t (&r)[32],
     if (j < cols_left) {
       float v = kIntAcc ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);
       if (scale_mode == DG_SCALE_PER_CHANNEL)
-        v = (v * e.as) * __ldg(e.bs_row + col + j);
+        v = (v * e.as) * e.bs_row[col + j];
       else if (scale_mode == DG_SCALE_TENSOR_WISE)
         v = (v * e.as) * e.bs_g;
       if (out_kind == 0)
@@ -218,6 +220,21 @@ __device__ __forceinline__ void epilogue_store32_scalar(const uint32_t (&r)[32],
       if (e.dbg_row != nullptr) e.dbg_row[col + j] = r[j];
     }
   }
+}
+
+// Each epilogue warp copies the weight scales of a tile's `width` columns into its own strip of
+// shared memory before it waits for the accumulator, so that the global-load latency hides
+// behind the main loop and the per-column reads in epilogue_store32 are shared-memory
+// broadcasts (read from global memory there, eight columns at a time, they cost more than
+// the stores).  Columns at or beyond N get 0.  Strips are private to a warp, so a
+// __syncwarp() is all the ordering needed and no warp ever waits for another.
+__device__ __forceinline__ void stage_tile_scales(float* dst, const float* b_scale_group, int n0,
+                                                  int width, int n, int lane, bool per_channel) {
+  __syncwarp();  // the previous tile's reads of the strip are done
+  if (per_channel) {
+    for (int c = lane; c < width; c += 32) dst[c] = (n0 + c < n) ? __ldg(b_scale_group + n0 + c) : 0.0f;
+  }
+  __syncwarp();
 }
 
 struct FalseTag { static constexpr bool value = false; };
@@ -521,6 +538,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       const TileCoord t = dec.get(item);
       const uint32_t buf = tile & 1u;
       const uint32_t aph = (tile >> 1) & 1u;
+      float* bs_s = reinterpret_cast<float*>(smem + L::off_bs) + q * BN;
+      if (t.rows_valid > q * 32)
+        stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, bn_eff, p.N, lane,
+                          p.scale_mode == DG_SCALE_PER_CHANNEL);
       if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
       if (t.rows_valid > q * 32) {  // warp-uniform
@@ -531,7 +552,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         EpiRow row;
         row.as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
         row.bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
-        row.bs_row = p.b_scale + (size_t)t.g * p.N + t.n0;  // PER_CHANNEL only
+        row.bs_row = bs_s;  // PER_CHANNEL only
         const size_t d_off = grow * p.N + t.n0;  // in output elements
         row.d_row = p.out_kind == 2 ? reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<float*>(p.d) + d_off)
                                     : p.d + d_off;

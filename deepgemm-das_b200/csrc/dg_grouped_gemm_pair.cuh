@@ -36,7 +36,9 @@ struct PairSmem {
   // full[S], empty[S], acc_full[2], acc_empty[2], drain
   static constexpr int kNumBars = 2 * kPairStages + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;
-  static constexpr int off_table = off_misc + 16;
+  static constexpr int off_bs = (off_misc + 16 + 15) & ~15;  // a tile's weight scales, one strip per epilogue warp; read as float4
+  static constexpr int off_table = off_bs + 4 * kPairBN * 4;
+  static_assert(off_bs % 16 == 0 && off_table % 4 == 0, "scale strips are read with 16-byte loads");
   static constexpr int kThreads = 192;
   __host__ __device__ static constexpr int total(int table_bytes) {
     return off_table + table_bytes + 1024;
@@ -301,6 +303,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       const PairTile t = dec.get(item);
       const uint32_t buf = tile & 1u;
       const uint32_t aph = (tile >> 1) & 1u;
+      float* bs_s = reinterpret_cast<float*>(smem + L::off_bs) + q * kPairBN;
+      stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, kPairBN, p.N, lane,
+                        p.scale_mode == DG_SCALE_PER_CHANNEL);
       if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
       const int half_rows = t.rows_valid - static_cast<int>(rank) * 128;  // rows of my half
@@ -312,7 +317,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         EpiRow row;
         row.as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
         row.bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
-        row.bs_row = p.b_scale + (size_t)t.g * p.N + t.n0;
+        row.bs_row = bs_s;
         row.d_row = p.d + grow * p.N + t.n0;
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kPairBN;
