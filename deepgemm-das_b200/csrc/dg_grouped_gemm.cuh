@@ -237,6 +237,35 @@ __device__ __forceinline__ void stage_tile_scales(float* dst, const float* b_sca
   __syncwarp();
 }
 
+// Drains `nchunks` 32-column chunks of one accumulator row block: the TMEM load of chunk c + 1
+// is in flight while chunk c is scaled, converted and stored.  `cols_left0` = N - first column
+// of the tile.  Every lane of the warp takes part in the loads; only lanes with `rv` store.
+template <bool kIntAcc>
+__device__ __forceinline__ void epilogue_drain(uint32_t t_row, int nchunks, bool rv, const EpiRow& row,
+                                               int scale_mode, int cols_left0, bool scalar_out,
+                                               int out_kind) {
+  auto store = [&](const uint32_t (&r)[32], int c) {
+    if (!rv) return;
+    if (!scalar_out)
+      epilogue_store32<kIntAcc>(r, row, scale_mode, c * 32, cols_left0 - c * 32);
+    else
+      epilogue_store32_scalar<kIntAcc>(r, row, scale_mode, c * 32, cols_left0 - c * 32, out_kind);
+  };
+  uint32_t ra[32], rb[32];
+  if (nchunks > 0) tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+  for (int c = 0; c < nchunks; c += 2) {
+    tmem_ld_wait();
+    if (c + 1 < nchunks) tmem_ld_32x32(t_row + (c + 1) * 32, rb);
+    store(ra, c);
+    if (c + 1 < nchunks) {
+      tmem_ld_wait();
+      if (c + 2 < nchunks) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
+      store(rb, c + 1);
+    }
+  }
+}
+
 struct FalseTag { static constexpr bool value = false; };
 struct TrueTag { static constexpr bool value = true; };
 
@@ -538,20 +567,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       const TileCoord t = dec.get(item);
       const uint32_t buf = tile & 1u;
       const uint32_t aph = (tile >> 1) & 1u;
+      // Everything that depends only on the tile's coordinates is fetched before the wait for
+      // the accumulator, so that the global-load latency hides behind the main loop.
       float* bs_s = reinterpret_cast<float*>(smem + L::off_bs) + q * BN;
-      if (t.rows_valid > q * 32)
+      const bool warp_has_rows = t.rows_valid > q * 32;  // warp-uniform
+      bool rv = false;
+      size_t grow = 0;
+      EpiRow row;
+      row.as = 1.0f;
+      row.bs_g = 1.0f;
+      if (warp_has_rows) {
         stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, bn_eff, p.N, lane,
                           p.scale_mode == DG_SCALE_PER_CHANNEL);
+        rv = row_in_tile < t.rows_valid;
+        grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 + row_in_tile;
+        if (p.mode == MODE_CONTIG && rv) rv = p.sched[grow] >= 0;
+        if (rv && p.scale_mode != DG_SCALE_NONE) row.as = p.a_scale[grow];
+        if (p.scale_mode == DG_SCALE_TENSOR_WISE) row.bs_g = p.b_scale[t.g];
+      }
       if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
-      if (t.rows_valid > q * 32) {  // warp-uniform
-        bool rv = row_in_tile < t.rows_valid;
-        const size_t grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 +
-                            row_in_tile;
-        if (p.mode == MODE_CONTIG && rv) rv = p.sched[grow] >= 0;
-        EpiRow row;
-        row.as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
-        row.bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
+      if (warp_has_rows) {
         row.bs_row = bs_s;  // PER_CHANNEL only
         const size_t d_off = grow * p.N + t.n0;  // in output elements
         row.d_row = p.out_kind == 2 ? reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<float*>(p.d) + d_off)
@@ -559,20 +595,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const bool scalar_out = p.out_kind != 0 || (p.N & 7) != 0;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-        for (int c = 0; c < bn_eff / 32; ++c) {
-          const int cols_left = p.N - (t.n0 + c * 32);
-          if (cols_left <= 0) break;  // warp-uniform
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c * 32, r);
-          tmem_ld_wait();
-          if (rv) {
-            if (!scalar_out)
-              epilogue_store32<kIntAcc>(r, row, p.scale_mode, c * 32, cols_left);
-            else
-              epilogue_store32_scalar<kIntAcc>(r, row, p.scale_mode, c * 32, cols_left, p.out_kind);
-          }
-        }
+        const int cols_left0 = p.N - t.n0;
+        epilogue_drain<kIntAcc>(t_row, min(bn_eff / 32, (cols_left0 + 31) / 32), rv, row, p.scale_mode,
+                                cols_left0, scalar_out, p.out_kind);
       }
       // hand the accumulator back to the UMMA issuer
       tc_fence_before_sync();

@@ -303,33 +303,35 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       const PairTile t = dec.get(item);
       const uint32_t buf = tile & 1u;
       const uint32_t aph = (tile >> 1) & 1u;
+      // Everything that depends only on the tile's coordinates is fetched before the wait for
+      // the accumulator, so that the global-load latency hides behind the main loop.
       float* bs_s = reinterpret_cast<float*>(smem + L::off_bs) + q * kPairBN;
-      stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, kPairBN, p.N, lane,
-                        p.scale_mode == DG_SCALE_PER_CHANNEL);
+      const int half_rows = t.rows_valid - static_cast<int>(rank) * 128;           // rows of my half
+      const bool warp_has_rows = ((t.half_mask >> rank) & 1) && half_rows > q * 32;  // warp-uniform
+      bool rv = false;
+      size_t grow = 0;
+      EpiRow row;
+      row.as = 1.0f;
+      row.bs_g = 1.0f;
+      if (warp_has_rows) {
+        stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, kPairBN, p.N, lane,
+                          p.scale_mode == DG_SCALE_PER_CHANNEL);
+        rv = row_in_half < half_rows;
+        grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 + rank * 128 + row_in_half;
+        if (p.mode == MODE_CONTIG && rv) rv = p.sched[grow] >= 0;
+        if (rv && p.scale_mode != DG_SCALE_NONE) row.as = p.a_scale[grow];
+        if (p.scale_mode == DG_SCALE_TENSOR_WISE) row.bs_g = p.b_scale[t.g];
+      }
       if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
-      const int half_rows = t.rows_valid - static_cast<int>(rank) * 128;  // rows of my half
-      if (((t.half_mask >> rank) & 1) && half_rows > q * 32) {            // warp-uniform
-        bool rv = row_in_half < half_rows;
-        const size_t grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 +
-                            rank * 128 + row_in_half;
-        if (p.mode == MODE_CONTIG && rv) rv = p.sched[grow] >= 0;
-        EpiRow row;
-        row.as = (rv && p.scale_mode != DG_SCALE_NONE) ? p.a_scale[grow] : 1.0f;
-        row.bs_g = (p.scale_mode == DG_SCALE_TENSOR_WISE) ? p.b_scale[t.g] : 1.0f;
+      if (warp_has_rows) {
         row.bs_row = bs_s;
         row.d_row = p.d + grow * p.N + t.n0;
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kPairBN;
-#pragma unroll 1
-        for (int c = 0; c < kPairBN / 32; ++c) {
-          const int cols_left = p.N - (t.n0 + c * 32);
-          if (cols_left <= 0) break;
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c * 32, r);
-          tmem_ld_wait();
-          if (rv) epilogue_store32<kIntAcc>(r, row, p.scale_mode, c * 32, cols_left);
-        }
+        const int cols_left0 = p.N - t.n0;
+        epilogue_drain<kIntAcc>(t_row, min(kPairBN / 32, (cols_left0 + 31) / 32), rv, row, p.scale_mode,
+                                cols_left0, false, 0);
       }
       tc_fence_before_sync();
       __syncwarp();
