@@ -36,7 +36,7 @@ import torch  # noqa: E402
 # (246.03 MB per launch); traffic grows in proportion to the number of experts.
 NCU_DECODE_DRAM_BYTES_PER_EXPERT = 246.03e6 / 8
 PREHEAT_S = 0.1
-PREHEAT_MAX_S = 2.0
+PREHEAT_MAX_S = 0.3   # long preheats push a power-capped GPU deeper into its cap
 METRIC = "masked_fp8_decode_hbm_bandwidth"
 UNIT = "GB/s"
 C2 = dict(G=32, K=7168, N=4096, max_m=128, tokens=256, top_k=8)
@@ -71,6 +71,11 @@ class ClockSampler:
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
         except Exception:
             self.h = None
+        self.power_limit_w = None
+        try:
+            self.power_limit_w = self.nv.nvmlDeviceGetEnforcedPowerLimit(self.h) / 1000.0
+        except Exception:
+            pass
 
     def _loop(self):
         nv = self.nv
@@ -81,7 +86,11 @@ class ClockSampler:
                     rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
                 except Exception:
                     rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                self.samples.append((time.perf_counter(), mhz, int(rs)))
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                except Exception:
+                    watts = None
+                self.samples.append((time.perf_counter(), mhz, int(rs), watts))
             except Exception:
                 pass
             time.sleep(self.period)
@@ -110,9 +119,12 @@ class ClockSampler:
         bits = 0
         for s in inside:
             bits |= s[2]
+        watts = sorted(s[3] for s in inside if s[3] is not None)
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(n for b, n in self._REASONS.items() if bits & b),
-                "samples": len(inside)}
+                "samples": len(inside),
+                "power_w": watts[len(watts) // 2] if watts else None,
+                "power_limit_w": self.power_limit_w}
 
 
 # ----------------------------------------------------------------------------- workloads
