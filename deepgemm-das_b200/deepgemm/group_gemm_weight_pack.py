@@ -77,25 +77,6 @@ def _resolve_i8_layout_mode(mode: Any) -> int:
     return value
 
 
-def _resolve_i8_layout_mode_from_config(config: Optional[dict]) -> int:
-    if config:
-        for key in ("LAYOUT_MODE", "I8_LAYOUT_MODE"):
-            if key in config:
-                return _resolve_i8_layout_mode(config[key])
-    return I8_LAYOUT_MODE_DEFAULT
-
-
-def _strip_i8_layout_mode_from_config(config: Optional[dict]) -> Optional[dict]:
-    if not config:
-        return None
-    stripped = {k: v for k, v in config.items() if k not in ("LAYOUT_MODE", "I8_LAYOUT_MODE")}
-    return stripped or None
-
-
-def _is_gfx936_contiguous_arch(arch: str) -> bool:
-    return False
-
-
 # ----------------------------------------------------------------------------- core re-layout
 def _nibble_order(order) -> int:
     if order in (NIBBLE_HIGH_FIRST, "high_first", "high"):
@@ -129,10 +110,6 @@ def _torch_unpack_rows(packed_u8: torch.Tensor, w4: bool, nibble_order: int) -> 
         first, second = w[..., 0], w[..., 1]
         x = ((first << 4) | second) if nibble_order == NIBBLE_HIGH_FIRST else ((second << 4) | first)
     return x.reshape(n, kb * blk).contiguous()
-
-
-def _kind_row_bytes(kind: int, k: int) -> int:
-    return k * 2 if kind == KIND_BF16 else (k // 2 if kind == KIND_W4A8 else k)
 
 
 def _pack_inplace(weight: torch.Tensor, kind: int, nibble_order: int = NIBBLE_HIGH_FIRST
