@@ -65,6 +65,12 @@ def _worker(rank, world, port, q):
         tag = torch.arange(T, dtype=torch.float32) + 1000.0 * rank
         rows8, _, scale = ep.dispatch_tokens(hidden.view(torch.uint8), plan, E, rank, world, row_scale=tag)
         assert torch.equal(rows8.view(torch.bfloat16), rows)
+        # each token once per destination rank: the pairs must read the same rows as before
+        urows, src_index, uexpert, usplits, uscale = ep.dispatch_unique(hidden, plan, E, rank, world,
+                                                                         row_scale=tag)
+        assert torch.equal(urows.index_select(0, src_index.long()), rows)
+        assert torch.equal(uexpert.long(), expert_local) and torch.equal(uscale[src_index.long()], scale)
+        assert urows.shape[0] <= rows.shape[0] and len(torch.unique(uscale)) == urows.shape[0]
         q.put((rank, rows.float(), expert_local, scale))
     finally:
         dist.barrier()
