@@ -56,7 +56,11 @@ struct W4Smem {
   // wfull[W], wempty[W], rfull[R], cons[R], acc_full[2], acc_empty[2], drain
   static constexpr int kNumBars = 2 * kW4WStages + 2 * kW4Rounds + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;
-  static constexpr int off_table = off_misc + 16;
+  // epilogue transposition strips: [16 tokens][32 channels] bf16 per epilogue warp
+  static constexpr int kEpiStripBytes = 16 * 32 * 2;
+  static constexpr int off_epi = (off_misc + 16 + 15) & ~15;
+  static constexpr int off_table = off_epi + 4 * kW4Groups * kEpiStripBytes;
+  static_assert(off_epi % 16 == 0 && off_table % 4 == 0, "strips are read with 16-byte loads");
   static constexpr int kThreads = 32 * (kW4TokWarp + 1);
   __host__ __device__ static constexpr int total(int table_bytes) {
     return off_table + table_bytes + 1024;
@@ -325,8 +329,14 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
       if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kW4AccCols;
-      // 16 tokens per step; the step loop stays rolled to keep the code small (the fully
-      // unrolled form stalled on instruction fetch)
+      // 16 tokens per step.  A lane holds one channel of 16 tokens, but D is token-major, so the
+      // step goes through a [16 tokens][32 channels] strip of shared memory: 16 two-byte
+      // writes per lane, then every lane stores two 16-byte pieces (8 channels of one token),
+      // 2 global store instructions per lane and step instead of 16.  The step loop stays
+      // rolled to keep the code small (the fully unrolled form stalled on instruction fetch).
+      __nv_bfloat16* strip = reinterpret_cast<__nv_bfloat16*>(
+          smem + L::off_epi + (warp - kW4EpiWarp0) * L::kEpiStripBytes);
+      const int piece_chan = t.n0 + q * 32 + (lane & 3) * 8;   // first channel of this lane's pieces
 #pragma unroll 1
       for (int c = 0; c * 16 < t.rows_valid; ++c) {
         const int w = c >> 1;  // which of the four prefetched 32-token groups
@@ -337,17 +347,28 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
         uint32_t r[16];
         tmem_ld_32x16(t_lane + c * 16, r);
         tmem_ld_wait();
-        __nv_bfloat16* d_col = p.d + (row_base + c * 16) * p.N + chan;
-        uint32_t* dbg_col = p.debug_acc + (row_base + c * 16) * p.N + chan;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const float as_j = __shfl_sync(0xffffffffu, as_w, (c & 1) * 16 + j);
-          if (((m_w >> j) & 1u) && chan_ok) {
-            const float v = (__int2float_rn(static_cast<int>(r[j])) * as_j) * bs;
-            d_col[(size_t)j * p.N] = __float2bfloat16_rn(v);
-            if (p.debug_acc != nullptr) dbg_col[(size_t)j * p.N] = r[j];
+          const float v = (__int2float_rn(static_cast<int>(r[j])) * as_j) * bs;
+          strip[j * 32 + lane] = __float2bfloat16_rn(v);
+        }
+        if (p.debug_acc != nullptr && chan_ok) {  // raw accumulators (tests only): direct stores
+          uint32_t* dbg_col = p.debug_acc + (row_base + c * 16) * p.N + chan;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if ((m_w >> j) & 1u) dbg_col[(size_t)j * p.N] = r[j];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int tok = (lane >> 2) + 8 * h;  // token of the step this lane stores a piece of
+          if (((m_w >> tok) & 1u) && piece_chan < p.N) {
+            const uint4 v16 = *reinterpret_cast<const uint4*>(strip + tok * 32 + (lane & 3) * 8);
+            *reinterpret_cast<uint4*>(p.d + (row_base + c * 16 + tok) * p.N + piece_chan) = v16;
           }
         }
+        __syncwarp();  // the strip is rewritten by the next step
       }
       tc_fence_before_sync();
       __syncwarp();
