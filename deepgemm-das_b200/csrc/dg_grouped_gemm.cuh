@@ -117,8 +117,10 @@ struct SmemLayout {
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;  // tmem slot, abort, n_items, pad
   static constexpr int off_bs = (off_misc + 16 + 15) & ~15;  // a tile's weight scales, one strip per epilogue warp; read as float4
-  static constexpr int off_table = off_bs + 4 * BN * 4;
-  static_assert(off_bs % 16 == 0 && off_table % 4 == 0, "scale strips are read with 16-byte loads");
+  static constexpr int off_epi = off_bs + 4 * BN * 4;        // store strips: 32 rows x 64 B per epilogue warp
+  static constexpr int off_table = off_epi + 4 * 2048;
+  static_assert(off_bs % 16 == 0 && off_epi % 16 == 0 && off_table % 4 == 0,
+                "scale and store strips are accessed with 16-byte loads and stores");
   static constexpr int kThreads = 192;
   static constexpr int kTmemCols = 2 * BN;
   __host__ __device__ static constexpr int total(int table_bytes) {
@@ -135,45 +137,54 @@ struct EpiRow {
   uint32_t* dbg_row;     // &debug_acc[row][n0] or nullptr
 };
 
-// Scales, converts and stores 32 accumulator columns of one row: out = bf16_rne((float(acc) *
-// a_scale) * b_scale), two separate fp32 multiplications in the reference's order
-// (m_grouped_fp8_gemm_nt_maksed_low_latency.cu:584), 16-byte stores, columns >= N skipped.
+// Scales and converts 8 accumulator columns (j .. j+7 of the chunk that starts at column
+// `col` of the tile) of one row: out = bf16_rne((float(acc) * a_scale) * b_scale), two separate
+// fp32 multiplications in the reference's order (m_grouped_fp8_gemm_nt_maksed_low_latency.cu:584).
+template <bool kIntAcc>
+__device__ __forceinline__ uint4 epilogue_pack8(const uint32_t (&r)[32], int j, const EpiRow& e,
+                                                int scale_mode, int col) {
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    v[i] = kIntAcc ? __int2float_rn(static_cast<int>(r[j + i])) : __uint_as_float(r[j + i]);
+  if (scale_mode == DG_SCALE_PER_CHANNEL) {
+    const float4 b0 = *reinterpret_cast<const float4*>(e.bs_row + col + j);
+    const float4 b1 = *reinterpret_cast<const float4*>(e.bs_row + col + j + 4);
+    v[0] = (v[0] * e.as) * b0.x;
+    v[1] = (v[1] * e.as) * b0.y;
+    v[2] = (v[2] * e.as) * b0.z;
+    v[3] = (v[3] * e.as) * b0.w;
+    v[4] = (v[4] * e.as) * b1.x;
+    v[5] = (v[5] * e.as) * b1.y;
+    v[6] = (v[6] * e.as) * b1.z;
+    v[7] = (v[7] * e.as) * b1.w;
+  } else if (scale_mode == DG_SCALE_TENSOR_WISE) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (v[i] * e.as) * e.bs_g;
+  }
+  uint4 o;
+  __nv_bfloat162 h;
+  h = __floats2bfloat162_rn(v[0], v[1]);
+  o.x = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(v[2], v[3]);
+  o.y = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(v[4], v[5]);
+  o.z = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(v[6], v[7]);
+  o.w = *reinterpret_cast<uint32_t*>(&h);
+  return o;
+}
+
+// Stores 32 accumulator columns of this lane's row straight from registers: 16-byte stores,
+// columns >= N skipped.  (Every lane of a warp writes a different row, so one store
+// instruction touches 32 rows; epilogue_store32_staged is the coalesced form.)
 template <bool kIntAcc>
 __device__ __forceinline__ void epilogue_store32(const uint32_t (&r)[32], const EpiRow& e,
                                                  int scale_mode, int col, int cols_left) {
 #pragma unroll
   for (int j = 0; j < 32; j += 8) {
     if (j + 8 <= cols_left) {
-      float v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        v[i] = kIntAcc ? __int2float_rn(static_cast<int>(r[j + i])) : __uint_as_float(r[j + i]);
-      if (scale_mode == DG_SCALE_PER_CHANNEL) {
-        const float4 b0 = *reinterpret_cast<const float4*>(e.bs_row + col + j);
-        const float4 b1 = *reinterpret_cast<const float4*>(e.bs_row + col + j + 4);
-        v[0] = (v[0] * e.as) * b0.x;
-        v[1] = (v[1] * e.as) * b0.y;
-        v[2] = (v[2] * e.as) * b0.z;
-        v[3] = (v[3] * e.as) * b0.w;
-        v[4] = (v[4] * e.as) * b1.x;
-        v[5] = (v[5] * e.as) * b1.y;
-        v[6] = (v[6] * e.as) * b1.z;
-        v[7] = (v[7] * e.as) * b1.w;
-      } else if (scale_mode == DG_SCALE_TENSOR_WISE) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = (v[i] * e.as) * e.bs_g;
-      }
-      uint4 o;
-      __nv_bfloat162 h;
-      h = __floats2bfloat162_rn(v[0], v[1]);
-      o.x = *reinterpret_cast<uint32_t*>(&h);
-      h = __floats2bfloat162_rn(v[2], v[3]);
-      o.y = *reinterpret_cast<uint32_t*>(&h);
-      h = __floats2bfloat162_rn(v[4], v[5]);
-      o.z = *reinterpret_cast<uint32_t*>(&h);
-      h = __floats2bfloat162_rn(v[6], v[7]);
-      o.w = *reinterpret_cast<uint32_t*>(&h);
-      *reinterpret_cast<uint4*>(e.d_row + col + j) = o;
+      *reinterpret_cast<uint4*>(e.d_row + col + j) = epilogue_pack8<kIntAcc>(r, j, e, scale_mode, col);
       if (e.dbg_row != nullptr) {
         *reinterpret_cast<uint4*>(e.dbg_row + col + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
         *reinterpret_cast<uint4*>(e.dbg_row + col + j + 4) =
@@ -181,6 +192,42 @@ __device__ __forceinline__ void epilogue_store32(const uint32_t (&r)[32], const 
       }
     }
   }
+}
+
+// What a warp needs to store its 32 consecutive rows through shared memory.
+struct EpiWarp {
+  uint8_t* strip;         // 32 rows x 64 bytes of shared memory private to the warp
+  __nv_bfloat16* d_warp;  // &D[first row of the warp][n0]
+  size_t ld;              // elements between consecutive rows of D (= N)
+  unsigned rv_mask;       // bit r: row r of the warp may be stored
+  int lane;
+};
+
+// Coalesced form of epilogue_store32: every lane converts its row's 32 columns into the warp's
+// strip (four 16-byte pieces per row, piece index XOR-swizzled with the row so that neither the
+// writes nor the reads conflict), then lane l stores piece l % 4 of rows l / 4, l / 4 + 8, ...:
+// a store instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+template <bool kIntAcc>
+__device__ __forceinline__ void epilogue_store32_staged(const uint32_t (&r)[32], const EpiRow& e,
+                                                        const EpiWarp& w, int scale_mode, int col,
+                                                        int cols_left) {
+  const int swz = (w.lane >> 1) & 3;
+#pragma unroll
+  for (int p = 0; p < 4; ++p)
+    *reinterpret_cast<uint4*>(w.strip + w.lane * 64 + ((p ^ swz) << 4)) =
+        epilogue_pack8<kIntAcc>(r, 8 * p, e, scale_mode, col);
+  __syncwarp();
+  const int p = w.lane & 3;
+  if (8 * p + 8 <= cols_left) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const int row = (w.lane >> 2) + 8 * h;
+      if ((w.rv_mask >> row) & 1u)
+        *reinterpret_cast<uint4*>(w.d_warp + row * w.ld + col + 8 * p) =
+            *reinterpret_cast<const uint4*>(w.strip + row * 64 + ((p ^ ((row >> 1) & 3)) << 4));
+    }
+  }
+  __syncwarp();  // the strip is rewritten by the next chunk
 }
 
 // TMA coordinates of the weight tile of K block kb: packed layout = flat list of 128-byte rows
@@ -239,12 +286,18 @@ __device__ __forceinline__ void stage_tile_scales(float* dst, const float* b_sca
 
 // Drains `nchunks` 32-column chunks of one accumulator row block: the TMEM load of chunk c + 1
 // is in flight while chunk c is scaled, converted and stored.  `cols_left0` = N - first column
-// of the tile.  Every lane of the warp takes part in the loads; only lanes with `rv` store.
+// of the tile.  Every lane of the warp takes part in the loads (and in the staged stores); in
+// the direct forms only lanes with `rv` store.
 template <bool kIntAcc>
 __device__ __forceinline__ void epilogue_drain(uint32_t t_row, int nchunks, bool rv, const EpiRow& row,
-                                               int scale_mode, int cols_left0, bool scalar_out,
-                                               int out_kind) {
+                                               const EpiWarp& ew, int scale_mode, int cols_left0,
+                                               bool scalar_out, int out_kind) {
+  const bool staged = !scalar_out && row.dbg_row == nullptr && ew.strip != nullptr;  // warp-uniform
   auto store = [&](const uint32_t (&r)[32], int c) {
+    if (staged) {
+      epilogue_store32_staged<kIntAcc>(r, row, ew, scale_mode, c * 32, cols_left0 - c * 32);
+      return;
+    }
     if (!rv) return;
     if (!scalar_out)
       epilogue_store32<kIntAcc>(r, row, scale_mode, c * 32, cols_left0 - c * 32);
@@ -596,7 +649,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         const bool scalar_out = p.out_kind != 0 || (p.N & 7) != 0;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
         const int cols_left0 = p.N - t.n0;
-        epilogue_drain<kIntAcc>(t_row, min(bn_eff / 32, (cols_left0 + 31) / 32), rv, row, p.scale_mode,
+        EpiWarp ew;
+        ew.strip = smem + L::off_epi + q * 2048;
+        ew.d_warp = p.d + (grow - lane) * p.N + t.n0;  // rows of a warp are consecutive in D
+        ew.ld = static_cast<size_t>(p.N);
+        ew.rv_mask = __ballot_sync(0xffffffffu, rv);
+        ew.lane = lane;
+        epilogue_drain<kIntAcc>(t_row, min(bn_eff / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
                                 cols_left0, scalar_out, p.out_kind);
       }
       // hand the accumulator back to the UMMA issuer

@@ -37,8 +37,10 @@ struct PairSmem {
   static constexpr int kNumBars = 2 * kPairStages + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;
   static constexpr int off_bs = (off_misc + 16 + 15) & ~15;  // a tile's weight scales, one strip per epilogue warp; read as float4
-  static constexpr int off_table = off_bs + 4 * kPairBN * 4;
-  static_assert(off_bs % 16 == 0 && off_table % 4 == 0, "scale strips are read with 16-byte loads");
+  static constexpr int off_epi = off_bs + 4 * kPairBN * 4;  // store strips: 32 rows x 64 B per epilogue warp
+  static constexpr int off_table = off_epi + 4 * 2048;
+  static_assert(off_bs % 16 == 0 && off_epi % 16 == 0 && off_table % 4 == 0,
+                "scale and store strips are accessed with 16-byte loads and stores");
   static constexpr int kThreads = 192;
   __host__ __device__ static constexpr int total(int table_bytes) {
     return off_table + table_bytes + 1024;
@@ -330,7 +332,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kPairBN;
         const int cols_left0 = p.N - t.n0;
-        epilogue_drain<kIntAcc>(t_row, min(kPairBN / 32, (cols_left0 + 31) / 32), rv, row, p.scale_mode,
+        EpiWarp ew;
+        ew.strip = smem + L::off_epi + q * 2048;
+        ew.d_warp = p.d + (grow - lane) * p.N + t.n0;  // rows of a warp are consecutive in D
+        ew.ld = static_cast<size_t>(p.N);
+        ew.rv_mask = __ballot_sync(0xffffffffu, rv);
+        ew.lane = lane;
+        epilogue_drain<kIntAcc>(t_row, min(kPairBN / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
                                 cols_left0, false, 0);
       }
       tc_fence_before_sync();
