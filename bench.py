@@ -34,7 +34,7 @@ import torch  # noqa: E402
 # DRAM bytes (read + write) one decode launch moves per expert, from the ncu capture of the
 # 8-expert case summarised in profiles/grouped_gemm_e4m3_bn128_masked_fp8_decode.md
 # (246.03 MB per launch); traffic grows in proportion to the number of experts.
-NCU_DECODE_DRAM_BYTES_PER_EXPERT = 246.03e6 / 8
+NCU_DECODE_DRAM_BYTES_PER_EXPERT = 247.85e6 / 8   # ncu dram read+write of the 8-expert capture (profiles/)
 PREHEAT_S = 0.1
 PREHEAT_MAX_S = 0.3   # long preheats push a power-capped GPU deeper into its cap
 METRIC = "masked_fp8_decode_hbm_bandwidth"
