@@ -105,6 +105,15 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* b
   CUresult r = enc(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr,
                    bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // A host thread that has made no runtime call of its own yet (a worker thread of the
+    // caller) has no context bound for the driver entry point above: bind the device's
+    // primary context (cudaFree(nullptr) does nothing else) and try once more.
+    cudaFree(nullptr);
+    r = enc(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr, bdim, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) {
     tl_last_cuda_error = 10000 + static_cast<int>(r);
     return DG_ERR_CUDA;
