@@ -109,3 +109,22 @@ def test_launch_goes_to_the_current_stream():
         _launch(dev, d, em)
     side.synchronize()
     _check(c, d, ref, "side stream")
+
+
+def test_tensors_on_a_device_other_than_the_current_one():
+    """Like the reference (device guard on the input's device), the op runs where its tensors
+    live, whatever the caller's current device is; per-device set-up must not leak across."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    c, dev0, ref, em = _problem(7)
+    dev1 = {k: v.to("cuda:1") for k, v in dev0.items()}
+    d1 = torch.zeros_like(ref, device="cuda:1")
+    d0 = torch.zeros_like(ref, device="cuda:0")
+    assert torch.cuda.current_device() == 0
+    _launch(dev1, d1, em)                       # first use of device 1 in this process
+    _launch(dev0, d0, em)
+    _launch(dev1, d1, em)
+    torch.cuda.synchronize(0)
+    torch.cuda.synchronize(1)
+    _check(c, d1, ref, "device 1 while device 0 is current")
+    _check(c, d0, ref, "device 0")
