@@ -7,6 +7,7 @@ GEMM entry point.
 """
 from . import _cabi  # noqa: F401  (loads the shared library; fails loudly when it is missing)
 from . import op  # noqa: F401  (registers torch.ops.deep_gemm.*)
+from .einsum import einsum, fp8_einsum
 from .gemm import fp8_gemm, fp8_gemm_hipc
 from .group_gemm_weight_pack import (
     marlin_bf16_masked_weight,

@@ -30,6 +30,9 @@ def _dense(a, b, d, where: str, allowed) -> torch.Tensor:
         raise ValueError(f"{where}: A is {mat_a.dtype} but B is {mat_b.dtype}")
     if not mat_a.is_cuda:
         raise RuntimeError(f"{where}: tensors must be on a CUDA device (there is no CPU implementation)")
+    if mat_a.dtype == torch.bfloat16 and ((scale_a is not None and scale_a.numel()) or
+                                          (scale_b is not None and scale_b.numel())):
+        raise ValueError(f"{where}: bf16 operands take no scales")
     if mat_a.dim() not in (2, 3) or mat_b.dim() != mat_a.dim():
         raise ValueError(f"{where}: A and B must both be 2-D or both 3-D")
     batch = mat_b.shape[0] if mat_b.dim() == 3 else 1
