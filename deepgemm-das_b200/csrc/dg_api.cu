@@ -231,6 +231,12 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // Narrow weight boxes (64 and 32 rows) for sparse routing; only the BN = 128 tile uses them.
   CUtensorMap tm_b64 = tm_b, tm_b32 = tm_b;
   p.narrow = (BN == 128 && pr.mode != MODE_CONTIG) ? pr.narrow : 0;
+  p.split_tail = (BN == 256 && pr.mode != MODE_CONTIG) ? 1 : 0;
+  if (p.split_tail) {  // 128-row weight box for the half items of the last round
+    const uint32_t box128[2] = {(uint32_t)elems_per_row, 128u};
+    rc = encode_map(&tm_b64, dt_a, 2, pr.b, b_dims, b_strides, box128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != DG_OK) return rc;
+  }
   if (p.narrow) {
     const uint32_t box64[2] = {(uint32_t)elems_per_row, 64u};
     const uint32_t box32[2] = {(uint32_t)elems_per_row, 32u};
@@ -253,7 +259,7 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   }
 
   // With narrowing allowed the item count can reach max_blocks * ceil(N / 32).
-  const long long grid_items = p.narrow ? max_blocks * ((pr.N + 31) / 32) : max_items;
+  const long long grid_items = p.narrow ? max_blocks * ((pr.N + 31) / 32) : max_items;  // split tails need no more
   const int grid = static_cast<int>(grid_items < dev.sm_count ? grid_items : dev.sm_count);
   kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_a64, tm_a32, tm_b, tm_b64, tm_b32, p);
   cudaError_t e = cudaGetLastError();

@@ -75,6 +75,9 @@ struct KernelParams {
   int32_t* status;
   int b_rowmajor;  // 1: weights are plain [G][N][K] rows (dense GEMM), 0: the packed layout
   int out_kind;    // 0 = bf16 output; 1 = fp16, 2 = fp32 (dense GEMM only, scalar stores)
+  int split_tail;  // BN = 256, masked / compact: 1 = the items of the last, partly filled round are
+                   // split into two 128-column halves (the weight map of that height travels in
+                   // the tm_b64 argument)
   int narrow;  // BN = 128, masked / compact: 0 = tiles stay 128 columns wide, 1 = the kernel may
                // narrow them to 64 / 32 columns when few groups have rows, 64 / 32 = forced width
 };
@@ -116,7 +119,7 @@ struct SmemLayout {
   // full[S], empty[S], acc_full[2], acc_empty[2], drain
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int off_misc = off_bar + kNumBars * 8;  // tmem slot, abort, n_items, pad
-  static constexpr int off_bs = (off_misc + 16 + 15) & ~15;  // a tile's weight scales, one strip per epilogue warp; read as float4
+  static constexpr int off_bs = (off_misc + 32 + 15) & ~15;  // a tile's weight scales, one strip per epilogue warp; read as float4
   static constexpr int off_epi = off_bs + 4 * BN * 4;        // store strips: 32 rows x 64 B per epilogue warp
   static constexpr int off_table = off_epi + 4 * 2048;
   static_assert(off_bs % 16 == 0 && off_epi % 16 == 0 && off_table % 4 == 0,
@@ -326,6 +329,7 @@ struct TileCoord {
   int g;           // group
   int row0;        // first row: within the group (masked) or global (contiguous)
   int n0;          // first output column
+  int width;       // columns of this item
   int rows_valid;  // rows of this tile that may be stored (before the m_indices check)
 };
 
@@ -340,10 +344,20 @@ struct ItemDecoder {
   int bn;
   int n_tiles;
   int cursor;
-  __device__ ItemDecoder(const KernelParams& p_, const int32_t* tbl_, int bn_, int n_tiles_)
-      : p(p_), tbl(tbl_), bn(bn_), n_tiles(n_tiles_), cursor(0) {}
+  int split_from;  // items from this one on are halves of tiles: item = split_from + 2 * k + half
+  __device__ ItemDecoder(const KernelParams& p_, const int32_t* tbl_, int bn_, int n_tiles_,
+                         int split_from_ = 0x7fffffff)
+      : p(p_), tbl(tbl_), bn(bn_), n_tiles(n_tiles_), cursor(0), split_from(split_from_) {}
   __device__ __forceinline__ TileCoord get(int item) {
     TileCoord t;
+    t.width = bn;
+    int sub = 0;
+    if (item >= split_from) {
+      const int j = item - split_from;
+      item = split_from + (j >> 1);
+      t.width = bn >> 1;
+      sub = (j & 1) * t.width;
+    }
     if (p.mode != MODE_CONTIG) {
       const int32_t* cnt = tbl;
       const int32_t* pref = tbl + p.G;
@@ -352,7 +366,7 @@ struct ItemDecoder {
       const int mt = blk - pref[cursor];
       t.g = cursor;
       t.row0 = mt * kBM;
-      t.n0 = (item - blk * n_tiles) * bn;
+      t.n0 = (item - blk * n_tiles) * bn + sub;
       t.rows_valid = min(kBM, cnt[cursor] - t.row0);
       if (p.mode == MODE_COMPACT) {  // rows of group g start at offsets[g] in the flat tensor
         t.row0 += tbl[2 * p.G + 1 + cursor];
@@ -363,7 +377,7 @@ struct ItemDecoder {
       const int e = tbl[bi];
       t.g = e >> 16;
       t.row0 = (e & 0xFFFF) * kBM;
-      t.n0 = (item - bi * n_tiles) * bn;
+      t.n0 = (item - bi * n_tiles) * bn + sub;
       t.rows_valid = min(kBM, p.M - t.row0);
     }
     return t;
@@ -405,6 +419,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
   volatile int* n_items_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 8);
   volatile int* bn_eff_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 12);
+  volatile int* split_from_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 16);
   int32_t* tbl = reinterpret_cast<int32_t*>(smem + L::off_table);
 
   // ------------------------------------------------------------------ one-time set-up
@@ -463,7 +478,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (running * ((p.N + bn - 1) / bn) <= static_cast<int>(gridDim.x)) bn_eff = bn;
         }
         *bn_eff_s = bn_eff;
-        *n_items_s = running * ((p.N + bn_eff - 1) / bn_eff);
+        int items = running * ((p.N + bn_eff - 1) / bn_eff);
+        int split_from = 0x7fffffff;
+        if (BN == 256 && p.split_tail) {
+          // Items go round-robin to the blocks, so a last round with few items leaves most SMs
+          // idle for a whole item.  If that round is at most half full, its tiles are split in
+          // two: one more round of half the length, on twice as many blocks.
+          const int tail = items % static_cast<int>(gridDim.x);
+          if (items > static_cast<int>(gridDim.x) && tail > 0 && 2 * tail <= static_cast<int>(gridDim.x)) {
+            split_from = items - tail;
+            items += tail;
+          }
+        }
+        *split_from_s = split_from;
+        *n_items_s = items;
       }
     }
   } else {
@@ -485,6 +513,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       if (lane == 0) {
         *bn_eff_s = BN;
+        *split_from_s = 0x7fffffff;
         *n_items_s = count * p.n_tiles;
       }
       if (__any_sync(0xffffffffu, bad) && lane == 0 && blockIdx.x == 0 && p.status != nullptr)
@@ -502,6 +531,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   const uint32_t tmem_base = *tmem_slot;
   const int n_items = *n_items_s;
+  const int split_from = *split_from_s;
   const int bn_eff = *bn_eff_s;                      // tile width in use: BN, or 64 / 32 when narrowed
   const int nt_eff = (p.N + bn_eff - 1) / bn_eff;    // column tiles at that width
 
@@ -515,11 +545,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t it = 0;
       auto produce = [&](auto narrow_tag) {
         constexpr bool kNarrow = decltype(narrow_tag)::value;
-        ItemDecoder dec(p, tbl, bn_eff, nt_eff);
-        const CUtensorMap* tm_w = !kNarrow ? &tm_b : (bn_eff == 64 ? &tm_b64 : &tm_b32);
+        ItemDecoder dec(p, tbl, bn_eff, nt_eff, split_from);
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
           const TileCoord t = dec.get(item);
-          const StageShape sh = stage_shape(t.rows_valid, kNarrow ? bn_eff : BN, BN);
+          // weight box of the item's width (a 256-column kernel's half items: 128 rows, in tm_b64)
+          const CUtensorMap* tm_w = t.width == BN ? &tm_b : ((BN == 256 || t.width == 64) ? &tm_b64 : &tm_b32);
+          const StageShape sh = stage_shape(t.rows_valid, t.width, BN);
           const CUtensorMap* tm_act = (sh.a_rows == kBM) ? &tm_a : (sh.a_rows == 64 ? &tm_a64 : &tm_a32);
           const int kps = kNarrow ? sh.kps : 1;
           for (int kb0 = 0; kb0 < p.kblocks; kb0 += kps, ++it) {
@@ -562,14 +593,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       // ---- UMMA issuer (same two variants as the producer)
       auto issue = [&](auto narrow_tag) {
         constexpr bool kNarrow = decltype(narrow_tag)::value;
-        const uint32_t idesc =
-            !kNarrow ? kIdesc
-                     : (kIdesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>(bn_eff >> 3) << 17);
-        ItemDecoder dec(p, tbl, bn_eff, nt_eff);
+        ItemDecoder dec(p, tbl, bn_eff, nt_eff, split_from);
         uint32_t it = 0, tile = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
-          StageShape sh;
-          if (kNarrow) sh = stage_shape(dec.get(item).rows_valid, bn_eff, BN);
+          const TileCoord t = dec.get(item);
+          const StageShape sh = stage_shape(t.rows_valid, t.width, BN);
+          const uint32_t idesc = (kIdesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>(t.width >> 3) << 17);
           const int kps = kNarrow ? sh.kps : 1;
           const uint32_t buf = tile & 1u;
           const uint32_t aph = (tile >> 1) & 1u;
@@ -614,7 +643,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     // ---- epilogue: this warp may touch TMEM lanes [32q, 32q+32)
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
-    ItemDecoder dec(p, tbl, bn_eff, nt_eff);
+    ItemDecoder dec(p, tbl, bn_eff, nt_eff, split_from);
     uint32_t tile = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
       const TileCoord t = dec.get(item);
@@ -630,7 +659,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       row.as = 1.0f;
       row.bs_g = 1.0f;
       if (warp_has_rows) {
-        stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, bn_eff, p.N, lane,
+        stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, t.width, p.N, lane,
                           p.scale_mode == DG_SCALE_PER_CHANNEL);
         rv = row_in_tile < t.rows_valid;
         grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 + row_in_tile;
@@ -655,7 +684,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         ew.ld = static_cast<size_t>(p.N);
         ew.rv_mask = __ballot_sync(0xffffffffu, rv);
         ew.lane = lane;
-        epilogue_drain<kIntAcc>(t_row, min(bn_eff / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
+        epilogue_drain<kIntAcc>(t_row, min(t.width / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
                                 cols_left0, scalar_out, p.out_kind);
       }
       // hand the accumulator back to the UMMA issuer

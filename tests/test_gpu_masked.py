@@ -278,3 +278,16 @@ def test_sparse_routing_fp8_narrow_tiles():
     for bn in (64, 32, 0):
         assert torch.equal(outs[bn].view(torch.int16), outs[128].view(torch.int16)), f"block_n={bn}"
     assert torch.all(outs[32][0].float() == SENTINEL) and torch.all(outs[32][1, 7:].float() == SENTINEL)
+
+
+def test_tail_round_split_into_half_tiles_bit_exact():
+    """256-column tiles, 40 groups x 4 column tiles = 160 items on (at most) 148 SMs: the 12
+    items of the second round are computed as 24 half tiles.  Same parity bar; the split must
+    not show in the result.  (On a GPU with more SMs than items nothing is split and the test
+    still checks the 256-column path.)"""
+    G, max_m, n, k = 40, 32, 1024, 384
+    gen = torch.Generator().manual_seed(77)
+    mm = torch.randint(1, max_m + 1, (G,), generator=gen)
+    c = gen_masked_int8(G, max_m, n, k, mm, seed=78)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=256, what="tail split, 256-column tiles")
