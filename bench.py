@@ -34,7 +34,7 @@ import torch  # noqa: E402
 # DRAM bytes (read + write) one decode launch moves per expert, from the ncu capture of the
 # 8-expert case summarised in profiles/grouped_gemm_e4m3_bn128_masked_fp8_decode.md
 # (246.03 MB per launch); traffic grows in proportion to the number of experts.
-NCU_DECODE_DRAM_BYTES_PER_EXPERT = 247.85e6 / 8   # ncu dram read+write of the 8-expert capture (profiles/)
+NCU_DECODE_DRAM_BYTES_PER_EXPERT = 966.73e6 / 32   # ncu dram read+write of a full launch (profiles/)
 PREHEAT_S = 0.1
 PREHEAT_MAX_S = 0.3   # long preheats push a power-capped GPU deeper into its cap
 METRIC = "masked_fp8_decode_hbm_bandwidth"
@@ -513,8 +513,8 @@ def main():
             "roofline": {"bound": "hbm", "achieved": own_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": own_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "traffic": NCU_DECODE_DRAM_BYTES_PER_EXPERT * cfg["G"],
-                         "traffic_note": "ncu dram bytes of an 8-expert launch scaled by experts",
-                         "kernel": "grouped_gemm_kernel<E4M3,BN=128> (rank 0)",
+                         "traffic_note": "ncu dram__bytes_read + write of one full-size launch (32 experts), per expert x local experts",
+                         "kernel": "grouped_gemm_kernel<E4M3,BN=256,4 stages> (rank 0)",
                          "algorithmic_bytes_per_launch": bytes_per_step},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
