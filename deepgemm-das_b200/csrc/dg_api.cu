@@ -231,10 +231,10 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // Narrow weight boxes (64 and 32 rows) for sparse routing; only the BN = 128 tile uses them.
   CUtensorMap tm_b64 = tm_b, tm_b32 = tm_b;
   p.narrow = (BN == 128 && pr.mode != MODE_CONTIG) ? pr.narrow : 0;
-  p.split_tail = (BN == 256 && pr.mode != MODE_CONTIG) ? 1 : 0;
-  if (p.split_tail) {  // 128-row weight box for the half items of the last round
-    const uint32_t box128[2] = {(uint32_t)elems_per_row, 128u};
-    rc = encode_map(&tm_b64, dt_a, 2, pr.b, b_dims, b_strides, box128, CU_TENSOR_MAP_SWIZZLE_128B);
+  p.split_tail = (pr.mode != MODE_CONTIG) ? 1 : 0;
+  if (p.split_tail) {  // weight box of BN / 2 rows for the half items of the last round
+    const uint32_t box_half[2] = {(uint32_t)elems_per_row, (uint32_t)(BN / 2)};
+    rc = encode_map(&tm_b64, dt_a, 2, pr.b, b_dims, b_strides, box_half, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != DG_OK) return rc;
   }
   if (p.narrow) {

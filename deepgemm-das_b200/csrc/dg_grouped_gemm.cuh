@@ -75,9 +75,9 @@ struct KernelParams {
   int32_t* status;
   int b_rowmajor;  // 1: weights are plain [G][N][K] rows (dense GEMM), 0: the packed layout
   int out_kind;    // 0 = bf16 output; 1 = fp16, 2 = fp32 (dense GEMM only, scalar stores)
-  int split_tail;  // BN = 256, masked / compact: 1 = the items of the last, partly filled round are
-                   // split into two 128-column halves (the weight map of that height travels in
-                   // the tm_b64 argument)
+  int split_tail;  // masked / compact: 1 = the items of a last round that is at most half full are
+                   // split into two halves of BN / 2 columns (the weight map of that height
+                   // travels in the tm_b64 argument)
   int narrow;  // BN = 128, masked / compact: 0 = tiles stay 128 columns wide, 1 = the kernel may
                // narrow them to 64 / 32 columns when few groups have rows, 64 / 32 = forced width
 };
@@ -480,7 +480,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         *bn_eff_s = bn_eff;
         int items = running * ((p.N + bn_eff - 1) / bn_eff);
         int split_from = 0x7fffffff;
-        if (BN == 256 && p.split_tail) {
+        if (bn_eff == BN && p.split_tail) {
           // Items go round-robin to the blocks, so a last round with few items leaves most SMs
           // idle for a whole item.  If that round is at most half full, its tiles are split in
           // two: one more round of half the length, on twice as many blocks.

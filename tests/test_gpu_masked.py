@@ -291,3 +291,13 @@ def test_tail_round_split_into_half_tiles_bit_exact():
     c = gen_masked_int8(G, max_m, n, k, mm, seed=78)
     bp = P.marlin_i8_masked_weight(c["b"].clone())
     _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=256, what="tail split, 256-column tiles")
+
+
+def test_tail_round_split_with_128_column_tiles():
+    """The same split for the 128-column instantiation: 40 groups x 4 tiles of 128 columns."""
+    G, max_m, n, k = 40, 32, 512, 256
+    gen = torch.Generator().manual_seed(79)
+    mm = torch.randint(1, max_m + 1, (G,), generator=gen)
+    c = gen_masked_int8(G, max_m, n, k, mm, seed=80)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=128, what="tail split, 128-column tiles")
