@@ -102,14 +102,18 @@ def expert_mlp_contiguous(a: torch.Tensor, a_scale: torch.Tensor, m_indices: tor
     """Both GEMMs of the experts on rows already quantised and grouped (the outputs of
     ``quantize_group_rows``): ``w13`` = (packed ``[E, 2I, K]`` gate|up weight, scale ``[E, 2I]``),
     ``w2`` = (packed ``[E, K_out, I]``, scale ``[E, K_out]``).  Returns bf16 ``[M, K_out]``; padding
-    rows hold zeros."""
+    rows (``m_indices < 0``) are not written and hold whatever the allocator returned."""
     from .m_group_gemm_nt_contiguous import m_grouped_fp8_gemm_nt_contiguous, m_grouped_i8_gemm_nt_contiguous
     gemm = m_grouped_fp8_gemm_nt_contiguous if kind == "fp8" else m_grouped_i8_gemm_nt_contiguous
     m = a.shape[0]
     h13 = torch.empty((m, w13[1].shape[1]), dtype=torch.bfloat16, device=a.device)
     gemm((a, a_scale), w13, h13, m_indices)
-    q, s = silu_mul_quant(h13, kind=kind, m_indices=m_indices)
-    y = torch.zeros((m, w2[1].shape[1]), dtype=torch.bfloat16, device=a.device)
+    # padding rows of the activation operand are never stored by the GEMM: no need to clear them
+    qdtype = torch.float8_e4m3fn if kind == "fp8" else torch.int8
+    q, s = silu_mul_quant(h13, kind=kind, m_indices=m_indices,
+                          out=(torch.empty((m, h13.shape[1] // 2), dtype=qdtype, device=a.device),
+                               torch.empty((m,), dtype=torch.float32, device=a.device)))
+    y = torch.empty((m, w2[1].shape[1]), dtype=torch.bfloat16, device=a.device)
     gemm((q, s), w2, y, m_indices)
     return y
 

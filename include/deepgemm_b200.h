@@ -2,8 +2,12 @@
  * deepgemm_b200.h -- C ABI of libdeepgemm_b200.so
  *
  * Grouped MoE GEMM for NVIDIA B200 (sm_100a): D = bf16( a_scale * (A . B^T) * b_scale )
- * over groups ("experts"), in the two row layouts the HYGON-AI/deepgemm-das library
- * exposes (masked and contiguous), for INT8, FP8-e4m3, W4A8 and BF16 operands.
+ * over groups ("experts"), in the row layouts the HYGON-AI/deepgemm-das library exposes
+ * (masked, contiguous, compact page), for INT8, FP8-e4m3, W4A8 and BF16 operands; the same
+ * kernels as a plain batched GEMM on unpacked weights (dg_dense_gemm); and the memory-bound
+ * steps of an MoE layer around them: quantise + group + pad (dg_quant_group_rows, also for a
+ * vLLM-style routing list: dg_group_sorted_rows), SiLU * up + requantise
+ * (dg_silu_mul_quant_rows), weighted top-k sum (dg_combine_rows), weight packing.
  *
  * The reference library has no C ABI of its own: its shared object is a PyTorch
  * extension whose C++ entry points take at::Tensor.  Each function below names the

@@ -54,6 +54,32 @@ def test_compact_masked_matches_oracle_and_leaves_other_rows_alone(bn):
     assert torch.isnan(out[~written].float()).all(), "rows outside every expert's range were written"
 
 
+def test_compact_page_with_more_items_than_sms_and_a_split_last_round():
+    """44 experts x 4 column tiles of 256 = 176 items: the 28 of the second round run as 56 half
+    tiles (on a 148-SM GPU).  Result rows and untouched rows as above."""
+    gen = torch.Generator().manual_seed(9)
+    counts = torch.randint(0, 25, (44,), generator=gen).clamp_min(1).tolist()
+    offsets, run = [], 0
+    for c in counts:
+        offsets.append(run)
+        run += c + 3                                           # gaps between experts stay untouched
+    cap, K, N = run + 5, 256, 1024
+    q_x, x_s, w, w_s = _page(counts, offsets, cap, K, N, 11)
+    bp = deepgemm.marlin_i8_masked_weight(w.clone().to(DEV))
+    out = torch.full((cap, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _core.grouped_gemm_compact(_cabi.KIND_I8, 0, q_x.to(DEV), bp, out, x_s.to(DEV), w_s.to(DEV),
+                               torch.tensor(counts, dtype=torch.int32, device=DEV),
+                               torch.tensor(offsets, dtype=torch.int32, device=DEV), 24, block_n=256)
+    out = out.cpu()
+    written = torch.zeros(cap, dtype=torch.bool)
+    for e, (c, o) in enumerate(zip(counts, offsets)):
+        rows = slice(o, o + c)
+        want = O.epilogue_from_acc(O.exact_int_acc(q_x[rows], w[e]), x_s[rows], w_s[e].reshape(-1))
+        assert_bf16_within_ulp(out[rows], want, 0, f"compact expert {e}")
+        written[rows] = True
+    assert torch.isnan(out[~written].float()).all()
+
+
 def test_compact_masked_empty_page_is_untouched():
     q_x = torch.zeros(256, 2048, dtype=torch.int8, device=DEV)
     x_s = torch.ones(256, 1, device=DEV)
