@@ -254,3 +254,47 @@ def m_grouped_w16a16_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_sca
 def m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
     return _ops.m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
                                                  m_indices, int(mode), 256, 4)
+
+
+# --------------------------------------------------------------------------- dense GEMM, einsum
+def _check_identity_epilogue(alpha, beta, bias, where: str) -> None:
+    if bias is not None:
+        raise RuntimeError(f"{where}: bias is not supported")
+    if float(alpha) != 1.0 or float(beta) != 0.0:
+        raise RuntimeError(f"{where}: only alpha = 1, beta = 0 are supported")
+
+
+def fp8_gemm(mat_a, mat_b, scale_a, scale_b, output, m, n, k, batch, transpose_flag, alpha, beta,
+             bias=None):
+    """Pybind name and argument order of the reference (csrc/include/deepgemm_ops.hpp; called
+    from deepgemm/gemm.py:42 as ``op.fp8_gemm(B, A, scale_B, scale_A, d, n, m, k, batch, "TN",
+    alpha, beta, None)``): the first operand is the [N, K] matrix, the second the [M, K] one."""
+    from .gemm import _dense
+    _check_identity_epilogue(alpha, beta, bias, "fp8_gemm")
+    if transpose_flag != "TN":
+        raise RuntimeError(f"fp8_gemm: only the TN layout is supported, got {transpose_flag!r}")
+    _dense((mat_b, scale_b), (mat_a, scale_a), output, "fp8_gemm", (torch.float8_e4m3fn, torch.int8))
+    return output
+
+
+def fp8_gemm_hipc(mat_a, mat_b, scale_a, scale_b, output, m, n, k, batch, transpose_flag, alpha,
+                  beta, bias=None):
+    """As ``fp8_gemm``, e4m3 only (reference deepgemm/gemm.py:83)."""
+    from .gemm import _dense
+    _check_identity_epilogue(alpha, beta, bias, "fp8_gemm_hipc")
+    if transpose_flag != "TN":
+        raise RuntimeError(f"fp8_gemm_hipc: only the TN layout is supported, got {transpose_flag!r}")
+    _dense((mat_b, scale_b), (mat_a, scale_a), output, "fp8_gemm_hipc", (torch.float8_e4m3fn,))
+    return output
+
+
+def einsum(expr, a, b, d, c=None):
+    """Reference csrc/arch/gfx938/einsum.cu:157-183."""
+    from .einsum import einsum as _einsum
+    return _einsum(expr, a, b, d, c)
+
+
+def fp8_einsum(expr, a, b, d, c=None, recipe=(1, 128, 128)):
+    """Reference csrc/arch/gfx938/einsum.cu:185-222."""
+    from .einsum import fp8_einsum as _fp8_einsum
+    return _fp8_einsum(expr, a, b, d, c, recipe)
