@@ -29,11 +29,6 @@ _B_DTYPES = {KIND_I8: (torch.int8, torch.uint8), KIND_E4M3: (_FP8, torch.int8, t
 KIND_NAMES = {KIND_I8: "int8", KIND_E4M3: "fp8_e4m3", KIND_W4A8: "w4a8", KIND_BF16: "bf16"}
 
 
-def _chk(cond: bool, msg: str) -> None:
-    if not cond:
-        raise RuntimeError(msg)
-
-
 def packed_weight_dims(b: torch.Tensor, kind: int, k_hint: Optional[int] = None
                        ) -> Tuple[int, int, int]:
     """(G, N, K) of a packed weight tensor; rejects tensors that do not carry the packed shape.
@@ -57,30 +52,58 @@ def packed_weight_dims(b: torch.Tensor, kind: int, k_hint: Optional[int] = None
 
 
 def _common_checks(kind, a, b, d, sched, what):
-    _chk(a.is_cuda and b.is_cuda and d.is_cuda and sched.is_cuda,
-         f"{what}: all tensors must be CUDA tensors (there is no CPU implementation)")
-    _chk(a.device == b.device == d.device == sched.device, f"{what}: tensors on different devices")
-    _chk(a.dtype in _A_DTYPES[kind], f"{what}: activation dtype {a.dtype} does not fit {KIND_NAMES[kind]}")
-    _chk(b.dtype in _B_DTYPES[kind], f"{what}: weight dtype {b.dtype} does not fit {KIND_NAMES[kind]}")
-    _chk(d.dtype == torch.bfloat16, f"{what}: output must be torch.bfloat16, got {d.dtype}")
-    _chk(a.is_contiguous(), f"{what}: activation must be contiguous")
-    _chk(b.is_contiguous(), f"{what}: packed weight must be contiguous")
-    _chk(d.is_contiguous(), f"{what}: output must be contiguous")
-    _chk(sched.dtype == torch.int32 and sched.is_contiguous(),
-         f"{what}: masked_m / m_indices must be contiguous torch.int32")
+    if not (a.is_cuda and b.is_cuda and d.is_cuda and sched.is_cuda):
+        raise RuntimeError(f"{what}: all tensors must be CUDA tensors (there is no CPU implementation)")
+    if not (a.device == b.device == d.device == sched.device):
+        raise RuntimeError(f"{what}: tensors on different devices")
+    if not (a.dtype in _A_DTYPES[kind]):
+        raise RuntimeError(f"{what}: activation dtype {a.dtype} does not fit {KIND_NAMES[kind]}")
+    if not (b.dtype in _B_DTYPES[kind]):
+        raise RuntimeError(f"{what}: weight dtype {b.dtype} does not fit {KIND_NAMES[kind]}")
+    if not (d.dtype == torch.bfloat16):
+        raise RuntimeError(f"{what}: output must be torch.bfloat16, got {d.dtype}")
+    if not (a.is_contiguous()):
+        raise RuntimeError(f"{what}: activation must be contiguous")
+    if not (b.is_contiguous()):
+        raise RuntimeError(f"{what}: packed weight must be contiguous")
+    if not (d.is_contiguous()):
+        raise RuntimeError(f"{what}: output must be contiguous")
+    if not (sched.dtype == torch.int32 and sched.is_contiguous()):
+        raise RuntimeError(f"{what}: masked_m / m_indices must be contiguous torch.int32")
 
 
 def _scale(t: torch.Tensor, shape: Tuple[int, ...], name: str, what: str) -> torch.Tensor:
-    _chk(t.is_cuda, f"{what}: {name} must be a CUDA tensor")
-    _chk(t.dtype == torch.float32, f"{what}: {name} must be torch.float32, got {t.dtype}")
+    if not (t.is_cuda):
+        raise RuntimeError(f"{what}: {name} must be a CUDA tensor")
+    if not (t.dtype == torch.float32):
+        raise RuntimeError(f"{what}: {name} must be torch.float32, got {t.dtype}")
     if t.dim() == len(shape) + 1 and t.shape[-1] == 1:
-        t = t.squeeze(-1)
-    _chk(tuple(t.shape) == tuple(shape), f"{what}: {name} must have shape {tuple(shape)} "
-         f"(optionally with a trailing 1), got {tuple(t.shape)}")
-    t = t.contiguous()
+        t = t.squeeze(-1)  # a view: same storage
+    if not (tuple(t.shape) == tuple(shape)):
+        raise RuntimeError(f"{what}: {name} must have shape {tuple(shape)} "
+                       f"(optionally with a trailing 1), got {tuple(t.shape)}")
+    if not t.is_contiguous():
+        t = t.contiguous()
     if t.data_ptr() % 16 != 0:  # a sliced view can be misaligned for the float4 loads
         t = t.clone()
     return t
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _launch(entry, args, device: torch.device, what: str) -> None:
+    """Calls a C-ABI entry point on the current stream of `device`.  The common case (the
+    tensors live on the current device) avoids the device context manager and the Stream
+    object: together they cost more host time than the library call itself."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index == torch.cuda.current_device():
+        stream = _raw_stream(index) if _raw_stream is not None else torch.cuda.current_stream(device).cuda_stream
+        _cabi.check(entry(C.byref(args), C.c_void_p(stream)), what)
+        return
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        _cabi.check(entry(C.byref(args), C.c_void_p(stream)), what)
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -89,13 +112,11 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 def _debug_and_status(debug_acc, status, rows, n, dev, what):
     if debug_acc is not None:
-        _chk(debug_acc.is_cuda and debug_acc.device == dev and debug_acc.is_contiguous()
-             and debug_acc.element_size() == 4 and debug_acc.numel() == rows * n,
-             f"{what}: debug_acc must be a contiguous 32-bit tensor of {rows}x{n} on the same device")
+        if not (debug_acc.is_cuda and debug_acc.device == dev and debug_acc.is_contiguous() and debug_acc.element_size() == 4 and debug_acc.numel() == rows * n):
+            raise RuntimeError(f"{what}: debug_acc must be a contiguous 32-bit tensor of {rows}x{n} on the same device")
     if status is not None:
-        _chk(status.is_cuda and status.device == dev and status.dtype == torch.int32
-             and status.is_contiguous() and status.numel() >= _cabi.STATUS_WORDS,
-             f"{what}: status must be int32[{_cabi.STATUS_WORDS}] on the same device")
+        if not (status.is_cuda and status.device == dev and status.dtype == torch.int32 and status.is_contiguous() and status.numel() >= _cabi.STATUS_WORDS):
+            raise RuntimeError(f"{what}: status must be int32[{_cabi.STATUS_WORDS}] on the same device")
 
 
 def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Tensor,
@@ -106,19 +127,26 @@ def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Te
                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """d[g, :masked_m[g]] = bf16((A[g] @ B[g]^T) * a_scale[g] * b_scale[g]) via dg_masked_gemm."""
     what = f"masked {KIND_NAMES[kind]} grouped GEMM"
-    _chk(a.dim() == 3, f"{what}: activation must be [G, max_m, K], got {tuple(a.shape)}")
-    _chk(d.dim() == 3, f"{what}: output must be [G, max_m, N], got {tuple(d.shape)}")
+    if not (a.dim() == 3):
+        raise RuntimeError(f"{what}: activation must be [G, max_m, K], got {tuple(a.shape)}")
+    if not (d.dim() == 3):
+        raise RuntimeError(f"{what}: output must be [G, max_m, N], got {tuple(d.shape)}")
     g, max_m, k = (int(x) for x in a.shape)
     bg, n, bk = packed_weight_dims(b, kind)
     _common_checks(kind, a, b, d, masked_m, what)
-    _chk(bg == g, f"{what}: weight has {bg} groups, activation has {g}")
-    _chk(bk == k, f"{what}: weight K={bk} does not match activation K={k}")
-    _chk(tuple(d.shape) == (g, max_m, n), f"{what}: output must be {(g, max_m, n)}, got {tuple(d.shape)}")
-    _chk(masked_m.numel() == g, f"{what}: masked_m must have {g} entries, got {masked_m.numel()}")
+    if not (bg == g):
+        raise RuntimeError(f"{what}: weight has {bg} groups, activation has {g}")
+    if not (bk == k):
+        raise RuntimeError(f"{what}: weight K={bk} does not match activation K={k}")
+    if not (tuple(d.shape) == (g, max_m, n)):
+        raise RuntimeError(f"{what}: output must be {(g, max_m, n)}, got {tuple(d.shape)}")
+    if not (masked_m.numel() == g):
+        raise RuntimeError(f"{what}: masked_m must have {g} entries, got {masked_m.numel()}")
     if scale_mode == SCALE_NONE:
         a_s = b_s = None
     else:
-        _chk(a_scale is not None and b_scale is not None, f"{what}: scales are required")
+        if not (a_scale is not None and b_scale is not None):
+            raise RuntimeError(f"{what}: scales are required")
         a_s = _scale(a_scale, (g, max_m), "a_scale", what)
         b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
     _debug_and_status(debug_acc, status, g * max_m, n, a.device, what)
@@ -128,9 +156,7 @@ def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Te
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), masked_m=masked_m.data_ptr(), num_groups=g,
         max_m=max_m, n=n, k=k, expected_m=int(expected_m), block_n=int(block_n),
         debug_acc=_ptr(debug_acc), status=_ptr(status))
-    with torch.cuda.device(a.device):
-        stream = torch.cuda.current_stream(a.device).cuda_stream
-        _cabi.check(_cabi.lib.dg_masked_gemm(C.byref(args), C.c_void_p(stream)), what)
+    _launch(_cabi.lib.dg_masked_gemm, args, a.device, what)
     return d
 
 
@@ -141,18 +167,24 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
                             status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """d[i] = bf16((A[i] @ B[m_indices[i]]^T) * a_scale[i] * b_scale[m_indices[i]]) via dg_contig_gemm."""
     what = f"contiguous {KIND_NAMES[kind]} grouped GEMM"
-    _chk(a.dim() == 2, f"{what}: activation must be [M, K], got {tuple(a.shape)}")
-    _chk(d.dim() == 2, f"{what}: output must be [M, N], got {tuple(d.shape)}")
+    if not (a.dim() == 2):
+        raise RuntimeError(f"{what}: activation must be [M, K], got {tuple(a.shape)}")
+    if not (d.dim() == 2):
+        raise RuntimeError(f"{what}: output must be [M, N], got {tuple(d.shape)}")
     m_total, k = (int(x) for x in a.shape)
     g, n, bk = packed_weight_dims(b, kind)
     _common_checks(kind, a, b, d, m_indices, what)
-    _chk(bk == k, f"{what}: weight K={bk} does not match activation K={k}")
-    _chk(tuple(d.shape) == (m_total, n), f"{what}: output must be {(m_total, n)}, got {tuple(d.shape)}")
-    _chk(m_indices.numel() == m_total, f"{what}: m_indices must have {m_total} entries")
+    if not (bk == k):
+        raise RuntimeError(f"{what}: weight K={bk} does not match activation K={k}")
+    if not (tuple(d.shape) == (m_total, n)):
+        raise RuntimeError(f"{what}: output must be {(m_total, n)}, got {tuple(d.shape)}")
+    if not (m_indices.numel() == m_total):
+        raise RuntimeError(f"{what}: m_indices must have {m_total} entries")
     if scale_mode == SCALE_NONE:
         a_s = b_s = None
     else:
-        _chk(a_scale is not None and b_scale is not None, f"{what}: scales are required")
+        if not (a_scale is not None and b_scale is not None):
+            raise RuntimeError(f"{what}: scales are required")
         a_s = _scale(a_scale, (m_total,), "a_scale", what)
         b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
     _debug_and_status(debug_acc, status, m_total, n, a.device, what)
@@ -162,9 +194,7 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), m_indices=m_indices.data_ptr(), num_groups=g,
         m_total=m_total, n=n, k=k, block_n=int(block_n), reserved=0,
         debug_acc=_ptr(debug_acc), status=_ptr(status))
-    with torch.cuda.device(a.device):
-        stream = torch.cuda.current_stream(a.device).cuda_stream
-        _cabi.check(_cabi.lib.dg_contig_gemm(C.byref(args), C.c_void_p(stream)), what)
+    _launch(_cabi.lib.dg_contig_gemm, args, a.device, what)
     return d
 
 
@@ -178,20 +208,26 @@ def grouped_gemm_compact(kind: int, scale_mode: int, a: torch.Tensor, b: torch.T
     m < counts[g], via dg_compact_gemm; checks follow the reference's
     (csrc/arch/gfx936_gfx938_shared/m_grouped_w8a8_gemm_nt_masked.cu:1778-1838)."""
     what = f"compact {KIND_NAMES[kind]} grouped GEMM"
-    _chk(a.dim() == 2, f"{what}: input must be [capacity, K], got {tuple(a.shape)}")
-    _chk(d.dim() == 2, f"{what}: output must be [capacity, N], got {tuple(d.shape)}")
+    if not (a.dim() == 2):
+        raise RuntimeError(f"{what}: input must be [capacity, K], got {tuple(a.shape)}")
+    if not (d.dim() == 2):
+        raise RuntimeError(f"{what}: output must be [capacity, N], got {tuple(d.shape)}")
     cap, k = (int(x) for x in a.shape)
     g, n, bk = packed_weight_dims(b, kind)
     _common_checks(kind, a, b, d, counts, what)
-    _chk(bk == k, f"{what}: weight K={bk} does not match activation K={k}")
-    _chk(tuple(d.shape) == (cap, n), f"{what}: output must be {(cap, n)}, got {tuple(d.shape)}")
-    _chk(counts.dim() == 1 and counts.numel() == g, f"{what}: masked_m must be int32 [{g}]")
-    _chk(offsets.is_cuda and offsets.dtype == torch.int32 and offsets.is_contiguous()
-         and offsets.shape == counts.shape, f"{what}: expert_offsets must be contiguous CUDA int32 [{g}]")
+    if not (bk == k):
+        raise RuntimeError(f"{what}: weight K={bk} does not match activation K={k}")
+    if not (tuple(d.shape) == (cap, n)):
+        raise RuntimeError(f"{what}: output must be {(cap, n)}, got {tuple(d.shape)}")
+    if not (counts.dim() == 1 and counts.numel() == g):
+        raise RuntimeError(f"{what}: masked_m must be int32 [{g}]")
+    if not (offsets.is_cuda and offsets.dtype == torch.int32 and offsets.is_contiguous() and offsets.shape == counts.shape):
+        raise RuntimeError(f"{what}: expert_offsets must be contiguous CUDA int32 [{g}]")
     if scale_mode == SCALE_NONE:
         a_s = b_s = None
     else:
-        _chk(a_scale is not None and b_scale is not None, f"{what}: scales are required")
+        if not (a_scale is not None and b_scale is not None):
+            raise RuntimeError(f"{what}: scales are required")
         a_s = _scale(a_scale, (cap,), "a_scale", what)
         b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
     _debug_and_status(debug_acc, status, cap, n, a.device, what)
@@ -200,9 +236,7 @@ def grouped_gemm_compact(kind: int, scale_mode: int, a: torch.Tensor, b: torch.T
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), counts=counts.data_ptr(), offsets=offsets.data_ptr(),
         num_groups=g, capacity=cap, n=n, k=k, expected_m=int(expected_m), block_n=int(block_n),
         debug_acc=_ptr(debug_acc), status=_ptr(status))
-    with torch.cuda.device(a.device):
-        stream = torch.cuda.current_stream(a.device).cuda_stream
-        _cabi.check(_cabi.lib.dg_compact_gemm(C.byref(args), C.c_void_p(stream)), what)
+    _launch(_cabi.lib.dg_compact_gemm, args, a.device, what)
     return d
 
 

@@ -11,12 +11,12 @@ their natural row-major order (``dg_dense_gemm``); ``c``, ``recipe``, ``compiled
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Optional, Tuple
 
 import torch
 
 from . import _cabi
+from ._core import _launch
 
 _OUT_KIND = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
@@ -65,9 +65,7 @@ def _dense(a, b, d, where: str, allowed) -> torch.Tensor:
         a_scale=scale_a.data_ptr() if (has_a or has_b) else None,
         b_scale=scale_b.data_ptr() if (has_a or has_b) else None,
         batch=batch, m=m, n=n, k=k, block_n=0, reserved=0, debug_acc=None, status=None)
-    with torch.cuda.device(mat_a.device):
-        stream = torch.cuda.current_stream(mat_a.device).cuda_stream
-        _cabi.check(_cabi.lib.dg_dense_gemm(C.byref(args), C.c_void_p(stream)), where)
+    _launch(_cabi.lib.dg_dense_gemm, args, mat_a.device, where)
     return d
 
 

@@ -8,17 +8,13 @@ here are ``dg_silu_mul_quant_rows`` and ``dg_combine_rows`` of the C ABI.  CUDA 
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Optional, Tuple
 
 import torch
 
 from . import _cabi
+from ._core import _launch
 from ._cabi import KIND_E4M3, KIND_I8
-
-
-def _stream(dev) -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
 def silu_mul_quant(x: torch.Tensor, *, kind: str = "fp8", m_indices: Optional[torch.Tensor] = None,
@@ -64,9 +60,7 @@ def silu_mul_quant(x: torch.Tensor, *, kind: str = "fp8", m_indices: Optional[to
         m_indices=m_indices.contiguous().data_ptr() if m_indices is not None else None,
         masked_m=masked_m.contiguous().data_ptr() if masked_m is not None else None,
         q_out=q.data_ptr(), scale_out=scale.data_ptr())
-    with torch.cuda.device(x.device):
-        _cabi.check(_cabi.lib.dg_silu_mul_quant_rows(C.byref(args), _stream(x.device)),
-                    "dg_silu_mul_quant_rows")
+    _launch(_cabi.lib.dg_silu_mul_quant_rows, args, x.device, "dg_silu_mul_quant_rows")
     return q, scale
 
 
@@ -91,8 +85,7 @@ def combine_rows(y: torch.Tensor, src_row: torch.Tensor, weights: Optional[torch
         num_tokens=t, top_k=k, n=int(y.shape[1]), num_rows=int(y.shape[0]), y=y.data_ptr(),
         src_row=src_row.contiguous().data_ptr(),
         weights=weights.contiguous().data_ptr() if weights is not None else None, out=out.data_ptr())
-    with torch.cuda.device(y.device):
-        _cabi.check(_cabi.lib.dg_combine_rows(C.byref(args), _stream(y.device)), "dg_combine_rows")
+    _launch(_cabi.lib.dg_combine_rows, args, y.device, "dg_combine_rows")
     return out
 
 

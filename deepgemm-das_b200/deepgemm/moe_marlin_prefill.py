@@ -16,7 +16,6 @@ are written as zeros (the reference leaves them untouched).
 """
 from __future__ import annotations
 
-import ctypes as C
 
 import torch
 
@@ -78,9 +77,7 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
         a_out=a.data_ptr(), a_scale_out=a_s.data_ptr(), m_indices_out=m_idx.data_ptr(),
         dest_out=dest.data_ptr(), m_total_out=None, scratch=scratch.data_ptr(),
         scratch_bytes=scratch.numel())
-    with torch.cuda.device(dev):
-        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-        _cabi.check(_cabi.lib.dg_group_sorted_rows(C.byref(args), stream), "dg_group_sorted_rows")
+    _core._launch(_cabi.lib.dg_group_sorted_rows, args, dev, "dg_group_sorted_rows")
     y = torch.empty((m_cap, size_n), dtype=torch.bfloat16, device=dev)
     _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, a, b_qweight, y, a_s,
                                   b_scale.reshape(experts, size_n).contiguous(), m_idx)

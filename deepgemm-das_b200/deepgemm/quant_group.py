@@ -8,12 +8,12 @@ the ``[M, K]`` operand, with ``m_indices`` and the per-row scales, without a hos
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Optional, Tuple
 
 import torch
 
 from . import _cabi
+from ._core import _launch
 from ._cabi import KIND_E4M3, KIND_I8
 
 
@@ -82,9 +82,7 @@ def quantize_group_rows(rows: torch.Tensor, expert: torch.Tensor, num_groups: in
         scratch_bytes=scratch.numel() * scratch.element_size(),
         src_index=src_index.data_ptr() if src_index is not None else None,
         row_scale=row_scale.data_ptr() if row_scale is not None else None)
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        _cabi.check(_cabi.lib.dg_quant_group_rows(C.byref(args), C.c_void_p(stream)), "dg_quant_group_rows")
+    _launch(_cabi.lib.dg_quant_group_rows, args, dev, "dg_quant_group_rows")
     return a, a_scale, m_indices, dest, m_total
 
 
