@@ -140,7 +140,7 @@ struct Problem {
   const int32_t* sched;
   const int32_t* offsets;
   int G, M, N, K, block_n, expected_m;
-  int narrow;  // filled by validate_and_launch: KernelParams::narrow for the BN = 128 tile
+  int narrow;  // filled by validate_and_launch: KernelParams::narrow
   int dense;     // 1: dg_dense_gemm (row-major weights, no masked_m, any N, out_kind honoured)
   int out_kind;  // DG_OUT_BF16 / DG_OUT_F16 / DG_OUT_F32
   void* debug_acc;
@@ -192,7 +192,7 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   const CUtensorMapDataType dt_a =
       (KIND == DG_KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   // tm_a64 / tm_a32 fetch the first 64 / 32 rows of it, for tiles with no more valid rows.
-  CUtensorMap tm_a, tm_a64, tm_a32, tm_b;
+  CUtensorMap tm_a, tm_a64, tm_a32, tm_a8, tm_b;
   int rc;
   if (pr.mode == MODE_MASKED) {
     const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
@@ -200,7 +200,10 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
     const uint32_t box[3] = {(uint32_t)elems_per_row, (uint32_t)kBM, 1u};
     const uint32_t box64[3] = {(uint32_t)elems_per_row, 64u, 1u};
     const uint32_t box32[3] = {(uint32_t)elems_per_row, 32u, 1u};
-    rc = encode_map(&tm_a, dt_a, 3, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    const uint32_t box8[3] = {(uint32_t)elems_per_row, 8u, 1u};
+    rc = encode_map(&tm_a8, dt_a, 3, pr.a, dims, strides, box8, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_a, dt_a, 3, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
       rc = encode_map(&tm_a64, dt_a, 3, pr.a, dims, strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
@@ -211,7 +214,10 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
     const uint32_t box[2] = {(uint32_t)elems_per_row, (uint32_t)kBM};
     const uint32_t box64[2] = {(uint32_t)elems_per_row, 64u};
     const uint32_t box32[2] = {(uint32_t)elems_per_row, 32u};
-    rc = encode_map(&tm_a, dt_a, 2, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    const uint32_t box8[2] = {(uint32_t)elems_per_row, 8u};
+    rc = encode_map(&tm_a8, dt_a, 2, pr.a, dims, strides, box8, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_a, dt_a, 2, pr.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
       rc = encode_map(&tm_a64, dt_a, 2, pr.a, dims, strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
@@ -228,20 +234,19 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
     rc = encode_map(&tm_b, dt_a, 2, pr.b, b_dims, b_strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (rc != DG_OK) return rc;
-  // Narrow weight boxes (64 and 32 rows) for sparse routing; only the BN = 128 tile uses them.
-  CUtensorMap tm_b64 = tm_b, tm_b32 = tm_b;
-  p.narrow = (BN == 128 && pr.mode != MODE_CONTIG) ? pr.narrow : 0;
+  // Weight boxes of 128, 64 and 32 rows: narrowed tiles (sparse routing) and the half items of a
+  // split last round.
+  CUtensorMap tm_b128 = tm_b, tm_b64 = tm_b, tm_b32 = tm_b;
+  p.narrow = (pr.mode != MODE_CONTIG) ? pr.narrow : 0;
   p.split_tail = (pr.mode != MODE_CONTIG) ? 1 : 0;
-  if (p.split_tail) {  // weight box of BN / 2 rows for the half items of the last round
-    const uint32_t box_half[2] = {(uint32_t)elems_per_row, (uint32_t)(BN / 2)};
-    rc = encode_map(&tm_b64, dt_a, 2, pr.b, b_dims, b_strides, box_half, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != DG_OK) return rc;
-  }
-  if (p.narrow) {
+  if (p.narrow || p.split_tail) {
+    const uint32_t box128[2] = {(uint32_t)elems_per_row, 128u};
     const uint32_t box64[2] = {(uint32_t)elems_per_row, 64u};
     const uint32_t box32[2] = {(uint32_t)elems_per_row, 32u};
-    rc = encode_map(&tm_b64, dt_a, 2, pr.b, b_dims, b_strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = encode_map(&tm_b128, dt_a, 2, pr.b, b_dims, b_strides, box128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == DG_OK)
+      rc = encode_map(&tm_b64, dt_a, 2, pr.b, b_dims, b_strides, box64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == DG_OK && p.narrow)
       rc = encode_map(&tm_b32, dt_a, 2, pr.b, b_dims, b_strides, box32, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != DG_OK) return rc;
   }
@@ -261,7 +266,7 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // With narrowing allowed the item count can reach max_blocks * ceil(N / 32).
   const long long grid_items = p.narrow ? max_blocks * ((pr.N + 31) / 32) : max_items;  // split tails need no more
   const int grid = static_cast<int>(grid_items < dev.sm_count ? grid_items : dev.sm_count);
-  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_a64, tm_a32, tm_b, tm_b64, tm_b32, p);
+  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_a64, tm_a32, tm_a8, tm_b, tm_b128, tm_b64, tm_b32, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -486,8 +491,8 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
   // operand traffic per flop: two-CTA 256x256 tiles when there are enough of them to fill
   // every SM pair twice, else one-CTA 128x256 tiles.
   int bn = pr.block_n;
-  // 128-column tiles may narrow on the device when few groups have rows: always when the
-  // library chooses, never when the caller asked for exactly 128, to a fixed width for 32 / 64.
+  // Tiles may narrow on the device when few groups have rows: always when the library chooses,
+  // never when the caller asked for an exact width (128 / 256), to a fixed width for 32 / 64.
   pr.narrow = (bn == 0) ? 1 : ((bn == 32 || bn == 64) ? bn : 0);
   if (bn == 32 || bn == 64) bn = 128;
   if (bn == 0) {
@@ -506,14 +511,12 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
       bn = (pr.N >= 256 && (rows / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
     else {
       // Weight-streaming (decode) shapes.  256-column tiles move half the activation bytes from
-      // L2 and issue half the UMMAs per weight byte: within 1 % of the 128-column tiles at the
-      // full SM clock and 10-15 % faster when the GPU runs power-capped (measured on the
-      // 32 x 4096 x 7168 decode shape), as long as they still give every SM three or more
-      // items.  Few expected rows per group (sparse routing) keep 128-column tiles, which can
-      // narrow on the device.
-      const long long items256 =
-          (long long)pr.G * ((pr.expected_m > 0 ? pr.expected_m : 1) + kBM - 1) / kBM * (pr.N / 256);
-      bn = (pr.N % 256 == 0 && pr.expected_m >= 16 && items256 >= 3LL * dev->sm_count) ? 256 : 128;
+      // L2, issue half the UMMAs per weight byte and keep more weight bytes in flight per SM
+      // (4 x 32 KB against 6 x 16 KB): within 1 % of 128-column tiles at the full SM clock on
+      // the 32 x 4096 x 7168 decode shape, 10-15 % faster on a power-capped GPU, 27 % faster
+      // with 8 rows in every expert.  With few active experts the kernel narrows them on the
+      // device, so they serve every row count.
+      bn = (pr.N % 256 == 0) ? 256 : 128;
     }
   }
   if (bn == 512 && (pr.N < 256 || pr.mode == MODE_COMPACT)) bn = 128;

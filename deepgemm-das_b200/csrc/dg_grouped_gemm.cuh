@@ -76,22 +76,21 @@ struct KernelParams {
   int b_rowmajor;  // 1: weights are plain [G][N][K] rows (dense GEMM), 0: the packed layout
   int out_kind;    // 0 = bf16 output; 1 = fp16, 2 = fp32 (dense GEMM only, scalar stores)
   int split_tail;  // masked / compact: 1 = the items of a last round that is at most half full are
-                   // split into two halves of BN / 2 columns (the weight map of that height
-                   // travels in the tm_b64 argument)
-  int narrow;  // BN = 128, masked / compact: 0 = tiles stay 128 columns wide, 1 = the kernel may
-               // narrow them to 64 / 32 columns when few groups have rows, 64 / 32 = forced width
+                   // split into two halves of BN / 2 columns
+  int narrow;  // masked / compact: 0 = tiles stay BN columns wide, 1 = the kernel may narrow them
+               // (down to 32 columns) when few groups have rows, 128 / 64 / 32 = forced width
 };
 
 // Shape of one pipeline stage for a tile with `rows_valid` rows and `bn_eff` columns.  A tile
-// with at most 32 / 64 valid rows fetches only a 32 / 64-row slice of A with one TMA box of
-// that height (the UMMA still reads 128 rows; what it reads beyond the slice is stale shared
+// with at most 8 / 32 / 64 valid rows (decode steps mostly have one or two rows per active
+// expert) fetches only an 8 / 32 / 64-row slice of A with one TMA box of that height (the UMMA still reads 128 rows; what it reads beyond the slice is stale shared
 // memory that only reaches accumulator rows nobody stores).  Several 32-row copies per tile
 // were measured 18 % slower on the decode workload than one copy, so there is one box per
 // height.  When both operands
 // are narrow, several K blocks share one stage slot so the bytes in flight per stage stay
 // near 32 KB.
 struct StageShape {
-  int a_rows;         // rows of A fetched per K block: 32, 64 or 128 (one TMA box each)
+  int a_rows;         // rows of A fetched per K block: 8, 32, 64 or 128 (one TMA box each)
   int kps;            // K blocks per stage
   uint32_t a_stride;  // bytes between the A sub-tiles of consecutive K blocks in a slot
   uint32_t b_stride;  // same for the weight sub-tiles
@@ -99,7 +98,7 @@ struct StageShape {
 };
 __device__ __forceinline__ StageShape stage_shape(int rows_valid, int bn_eff, int bn) {
   StageShape sh;
-  sh.a_rows = rows_valid <= 32 ? 32 : (rows_valid <= 64 ? 64 : kBM);
+  sh.a_rows = rows_valid <= 8 ? 8 : (rows_valid <= 32 ? 32 : (rows_valid <= 64 ? 64 : kBM));
   sh.kps = min(bn / bn_eff, kBM / sh.a_rows);
   sh.a_stride = static_cast<uint32_t>(sh.a_rows) * kRowBytes;
   sh.b_stride = static_cast<uint32_t>(bn_eff) * kRowBytes;
@@ -389,7 +388,9 @@ __global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_a64,
                     const __grid_constant__ CUtensorMap tm_a32,
+                    const __grid_constant__ CUtensorMap tm_a8,
                     const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_b128,
                     const __grid_constant__ CUtensorMap tm_b64,
                     const __grid_constant__ CUtensorMap tm_b32, const KernelParams p) {
   using L = SmemLayout<KIND, BN, STAGES>;
@@ -468,13 +469,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         // Sparse routing (few groups with rows): narrow the tiles until there is an item for
         // every block, so that all SMs take part in streaming the few weight panels.
         int bn_eff = BN;
-        if (BN == 128 && p.narrow > 1) {
+        if (p.narrow > 1 && p.narrow < BN) {
           bn_eff = p.narrow;
-        } else if (BN == 128 && p.narrow == 1) {
+        } else if (p.narrow == 1) {
           // Narrow only while every item still finds a block of its own: with more items
-          // than blocks the 128-column tiles win (measured: a second round of narrow items
-          // costs more than idle SMs do, as each item pays the same UMMA issue time).
-          for (int bn = 64; bn >= 32; bn >>= 1)
+          // than blocks the wide tiles win (measured: a second round of narrow items costs
+          // more than idle SMs do, as each item pays the same UMMA issue time).
+          for (int bn = BN / 2; bn >= 32; bn >>= 1)
             if (running * ((p.N + bn - 1) / bn) <= static_cast<int>(gridDim.x)) bn_eff = bn;
         }
         *bn_eff_s = bn_eff;
@@ -548,10 +549,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         ItemDecoder dec(p, tbl, bn_eff, nt_eff, split_from);
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
           const TileCoord t = dec.get(item);
-          // weight box of the item's width (a 256-column kernel's half items: 128 rows, in tm_b64)
-          const CUtensorMap* tm_w = t.width == BN ? &tm_b : ((BN == 256 || t.width == 64) ? &tm_b64 : &tm_b32);
+          // weight box of the item's width
+          const CUtensorMap* tm_w = t.width == BN ? &tm_b
+                                    : (t.width == 128 ? &tm_b128 : (t.width == 64 ? &tm_b64 : &tm_b32));
           const StageShape sh = stage_shape(t.rows_valid, t.width, BN);
-          const CUtensorMap* tm_act = (sh.a_rows == kBM) ? &tm_a : (sh.a_rows == 64 ? &tm_a64 : &tm_a32);
+          const CUtensorMap* tm_act = (sh.a_rows == kBM) ? &tm_a
+                                      : (sh.a_rows == 64 ? &tm_a64 : (sh.a_rows == 32 ? &tm_a32 : &tm_a8));
           const int kps = kNarrow ? sh.kps : 1;
           for (int kb0 = 0; kb0 < p.kblocks; kb0 += kps, ++it) {
             const int s = it % STAGES;
