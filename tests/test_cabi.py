@@ -76,3 +76,27 @@ def test_missing_library_is_a_loud_import_error(tmp_path, monkeypatch):
     mod = importlib.util.module_from_spec(spec)
     with pytest.raises(ImportError, match="no fallback"):
         spec.loader.exec_module(mod)
+
+
+def test_header_is_valid_c99_and_cxx(tmp_path):
+    """The boundary is a C ABI: the header must compile as plain C (what a cgo / JNI / FFI binding
+    generator reads) and as C++, with no CUDA or torch headers."""
+    import shutil
+    import subprocess
+    inc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    body = (
+        '#include "deepgemm_b200.h"\n'
+        "int use(void) {\n"
+        "  dg_masked_args m; dg_contig_args c; dg_compact_args p; dg_dense_args d; dg_quant_group_args q;\n"
+        "  dg_group_sorted_args s; dg_act_quant_args a; dg_combine_args b;\n"
+        "  (void)m; (void)c; (void)p; (void)d; (void)q; (void)s; (void)a; (void)b;\n"
+        "  return (int)sizeof(dg_masked_args) + DG_STATUS_WORDS + DG_ABI_VERSION;\n"
+        "}\n")
+    for compiler, name, std in (("gcc", "t.c", "-std=c99"), ("g++", "t.cpp", "-std=c++11")):
+        if shutil.which(compiler) is None:
+            pytest.skip(f"{compiler} not available")
+        src = tmp_path / name
+        src.write_text(body)
+        r = subprocess.run([compiler, std, "-Wall", "-Werror", "-pedantic", "-fsyntax-only", "-I", inc, str(src)],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
