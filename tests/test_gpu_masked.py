@@ -328,3 +328,22 @@ def test_decode_like_sparse_histogram(seed):
         if m:
             assert_calc_diff(d[g, :m], ref[g, :m], 1e-3, f"fp8 sparse group {g}")   # calc_diff < 1e-3
         assert torch.all(d[g, m:].float() == SENTINEL)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_shapes_and_tile_choices_bit_exact(seed):
+    """Seeded random problems over every tile option (library's choice, forced narrow widths,
+    one-CTA 128 / 256 columns, two-CTA): group count, rows, N (any multiple of 16) and K vary, a
+    third of the groups are empty.  INT8: accumulators bit-exact, output 0 ulp from the exact
+    epilogue."""
+    gen = torch.Generator().manual_seed(1000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=gen))
+    G, max_m = r(1, 12), r(1, 200)
+    n, k = 16 * r(1, 40), 128 * r(1, 6)
+    mm = torch.randint(0, max_m + 1, (G,), generator=gen)
+    mm[torch.rand(G, generator=gen) < 0.33] = 0
+    bn = (0, 32, 64, 128, 256, 512)[seed % 6]
+    c = gen_masked_int8(G, max_m, n, k, mm, seed=2000 + seed)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn,
+                    what=f"random G={G} max_m={max_m} N={n} K={k} block_n={bn} masked_m={mm.tolist()}")
