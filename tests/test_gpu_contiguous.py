@@ -160,3 +160,29 @@ def test_out_of_range_group_index_is_reported_not_read():
     assert torch.all(d[128:].float() == SENTINEL)
     ref = O.ref_contiguous(c["a"], c["b"], c["a_scale"], c["b_scale"], c["m_indices"])
     assert_bf16_within_ulp(d[:128], ref[:128], 1, "valid block next to a bad one")
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_group_sizes_and_tile_choices_bit_exact(seed):
+    """Seeded random group counts, ragged group sizes (empty groups included), N and K, each
+    with one of the tile options and one of the two paddings; a random cut of the trailing
+    padding makes the last row block ragged."""
+    gen = torch.Generator().manual_seed(3000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=gen))
+    G = r(1, 10)
+    rows = [0 if r(0, 3) == 0 else r(1, 600) for _ in range(G)]
+    if sum(rows) == 0:
+        rows[0] = r(1, 600)
+    n, k = 16 * r(1, 48), 128 * r(1, 5)
+    align = (128, 256)[r(0, 1)]
+    bn = (0, 128, 256, 512)[seed % 4]
+    c = gen_contig("int8", rows, n, k, seed=4000 + seed, align=align)
+    idx = c["m_indices"]
+    trailing = 0
+    while trailing < idx.numel() and int(idx[idx.numel() - 1 - trailing]) < 0:
+        trailing += 1
+    cut = idx.numel() - (r(0, trailing) if trailing else 0)
+    c = dict(a=c["a"][:cut].contiguous(), a_scale=c["a_scale"][:cut].contiguous(), b=c["b"],
+             b_scale=c["b_scale"], m_indices=idx[:cut].contiguous())
+    _check_int8_contig(c, rows, block_n=bn,
+                       what=f"seed {seed}: rows={rows} N={n} K={k} align={align} BN={bn} cut={cut}")
