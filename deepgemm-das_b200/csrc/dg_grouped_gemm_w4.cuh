@@ -16,10 +16,14 @@
 //            becomes `x & 0xF0F0F0F0` and `(x << 4) & 0xF0F0F0F0`, i.e. every nibble becomes
 //            the int8 value 16*w -- the reference's rule
 //            (csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_masked_hipc.cu:378-381).
-//            One mbarrier per slot collects the token bytes and the four unpack-warp arrivals,
-//            so the UMMA thread does one wait, eight tcgen05.mma (A from TMEM, B from shared
-//            memory) and one tcgen05.commit per round: barrier operations cost a single thread
-//            a few hundred cycles, which a 128-value round would not amortise.
+//            One mbarrier per slot collects the token bytes and the four unpack-warp arrivals.
+//            The UMMA thread's instruction stream is what bounds the kernel (about 50 cycles per
+//            tcgen05.mma whatever N is, plus everything else it executes between them), so it
+//            does nothing but issue: per round eight tcgen05.mma (A from TMEM, B from shared
+//            memory) and one tcgen05.commit.  A watcher warp waits on the round-full and
+//            accumulator-empty barriers in its place, decodes the work items, and posts the
+//            number of rounds / items that may be issued (and each item's instruction
+//            descriptor) in plain shared-memory words.
 // Unpacked weights never touch shared memory.
 //
 // TMEM: columns [0,256) two accumulators (128 channels x 128 tokens), columns [256,512) the
@@ -44,6 +48,7 @@ constexpr int kW4Groups = 2;
 constexpr int kW4EpiWarp0 = 2;                            // warps 2..9
 constexpr int kW4UnpWarp0 = kW4EpiWarp0 + 4 * kW4Groups;  // warps 10..17
 constexpr int kW4TokWarp = kW4UnpWarp0 + 4 * kW4Groups;   // warp 18
+constexpr int kW4ChkWarp = kW4TokWarp + 1;                // warp 19
 
 enum : int { SITE_W4_WEMPTY = 8, SITE_W4_TEMPTY = 9, SITE_W4_SLOT_EMPTY = 10 };
 
@@ -58,10 +63,11 @@ struct W4Smem {
   static constexpr int off_misc = off_bar + kNumBars * 8;
   // epilogue transposition strips: [16 tokens][32 channels] bf16 per epilogue warp
   static constexpr int kEpiStripBytes = 16 * 32 * 2;
-  static constexpr int off_epi = (off_misc + 16 + 15) & ~15;
+  // misc: tmem slot, abort, n_items, rounds ready, items ready, 8 instruction descriptors
+  static constexpr int off_epi = (off_misc + 64 + 15) & ~15;
   static constexpr int off_table = off_epi + 4 * kW4Groups * kEpiStripBytes;
   static_assert(off_epi % 16 == 0 && off_table % 4 == 0, "strips are read with 16-byte loads");
-  static constexpr int kThreads = 32 * (kW4TokWarp + 1);
+  static constexpr int kThreads = 32 * (kW4ChkWarp + 1);
   __host__ __device__ static constexpr int total(int table_bytes) {
     return off_table + table_bytes + 1024;
   }
@@ -97,10 +103,15 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
   volatile int* n_items_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 8);
+  const uint32_t ready_addr = base + L::off_misc + 12;  // rounds whose round-full barrier was seen complete
+  const uint32_t items_addr = base + L::off_misc + 16;  // items whose accumulator is free and whose descriptor is posted
+  volatile uint32_t* idesc_ring = reinterpret_cast<volatile uint32_t*>(smem + L::off_misc + 20);
   int32_t* tbl = reinterpret_cast<int32_t*>(smem + L::off_table);
 
   if (tid == 0) {
     *abort_flag = 0;
+    *reinterpret_cast<volatile uint32_t*>(smem + L::off_misc + 12) = 0;
+    *reinterpret_cast<volatile uint32_t*>(smem + L::off_misc + 16) = 0;
     for (int s = 0; s < WS; ++s) {
       mbar_init(bar_wfull(s), 1);
       mbar_init(bar_wempty(s), 4);  // the four warps of the unpack group that owns the stage
@@ -249,32 +260,81 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kW4ChkWarp) {
     if (lane == 0) {
-      // ---- UMMA issuer: per round, A (weights) from TMEM slot s, B (tokens) from token stage s
+      // ---- barrier watcher: waits for the round-full barriers in order and publishes the
+      // number of complete rounds in a plain shared-memory word, which is all the UMMA thread
+      // reads
       ItemDecoder dec(p, tbl, 128, p.n_tiles);
       uint32_t it = 0, tile = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++tile) {
+        // the item's instruction descriptor (s8 x s8 -> s32, M = 128, N = its tokens rounded up
+        // to 16) and its accumulator, posted before its rounds
         const TileCoord t = dec.get(item);
-        const uint32_t n_tok = static_cast<uint32_t>((max(t.rows_valid, 1) + 15) & ~15);  // UMMA N
-        const uint32_t idesc = kIdescBase | ((n_tok >> 3) << 17);
-        const uint32_t buf = tile & 1u;
-        const uint32_t aph = (tile >> 1) & 1u;
-        if (!mbar_wait_bounded(bar_acc_empty(buf), aph ^ 1u, abort_flag, SITE_MMA_ACC_EMPTY)) {
+        const uint32_t n_tok = static_cast<uint32_t>((max(t.rows_valid, 1) + 15) & ~15);
+        if (!mbar_wait_bounded(bar_acc_empty(tile & 1u), ((tile >> 1) & 1u) ^ 1u, abort_flag,
+                               SITE_MMA_ACC_EMPTY))
+          break;
+        idesc_ring[tile & 7u] = kIdescBase | ((n_tok >> 3) << 17);
+        asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(items_addr), "r"(tile + 1u) : "memory");
+        for (int wb = 0; wb < wblocks; ++wb) {
+          if (!mbar_wait_bounded(bar_rfull(it % RS), (it / RS) & 1u, abort_flag, SITE_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          ++it;
+          asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(ready_addr), "r"(it) : "memory");
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- UMMA issuer: per round, A (weights) from TMEM slot s, B (tokens) from token stage s.
+      // This thread's instruction stream bounds the kernel, so it neither decodes work items
+      // nor touches an mbarrier: the watcher warp posts, in plain shared-memory words, how
+      // many items (descriptor ready, accumulator free) and rounds (weights and tokens in
+      // place) may be issued, and this thread re-reads a word only when its last copy is used up.
+      auto poll_above = [&](uint32_t addr, uint32_t have, int site) -> uint32_t {
+        // returns a value > have, or 0 after giving up (abort flag set); the timer is only read
+        // once the word has been found unchanged a few times (reading it costs ~100 cycles)
+        uint32_t v;
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+          asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+          if (v > have) return v;
+        }
+        const uint64_t t0 = global_timer_ns();
+        uint32_t spins = 0;
+        while (true) {
+          asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+          if (v > have) return v;
+          if ((++spins & 63u) == 0 && (*abort_flag || global_timer_ns() - t0 > 1500000000ull)) {
+            if (!*abort_flag) *abort_flag = site;
+            return 0;
+          }
+        }
+      };
+      uint32_t it = 0, tile = 0, rounds_known = 0, items_known = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++tile) {
+        if (items_known <= tile && (items_known = poll_above(items_addr, tile, SITE_MMA_ACC_EMPTY)) == 0) {
           ok = false;
           break;
         }
+        const uint32_t idesc = idesc_ring[tile & 7u];
+        const uint32_t buf = tile & 1u;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kW4AccCols;
         for (int wb = 0; wb < wblocks; ++wb, ++it) {
           const int s = it % RS;
-          const uint32_t ph = (it / RS) & 1u;
-          if (!mbar_wait_bounded(bar_rfull(s), ph, abort_flag, SITE_MMA_FULL)) {
-            ok = false;
-            break;
+          if (rounds_known <= it) {
+            if ((rounds_known = poll_above(ready_addr, it, SITE_MMA_FULL)) == 0) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();  // orders the UMMAs of every round learnt of here after the unpack warps' stores
           }
-          tc_fence_after_sync();
           const uint32_t a_tmem = tmem_base + kW4SlotBase + s * 64;
           const uint64_t b_desc = umma_desc_sw128(base + L::off_tok + s * L::kTokBytes);
 #pragma unroll
