@@ -347,3 +347,22 @@ def test_random_shapes_and_tile_choices_bit_exact(seed):
     bp = P.marlin_i8_masked_weight(c["b"].clone())
     _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn,
                     what=f"random G={G} max_m={max_m} N={n} K={k} block_n={bn} masked_m={mm.tolist()}")
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_w4a8_random_shapes_bit_exact(seed):
+    """Seeded random W4A8 cases: group counts, ragged masked_m with empty experts and experts of
+    more than 128 rows (two token tiles), N not a multiple of the 128-channel tile, K of one to
+    five 256-value rounds (odd round counts change which unpack group starts an item)."""
+    gen = torch.Generator().manual_seed(5000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=gen))
+    G, max_m = r(1, 10), r(1, 300)
+    n, k = 16 * r(1, 40), 256 * r(1, 5)
+    mm = torch.randint(0, max_m + 1, (G,), generator=gen)
+    mm[torch.rand(G, generator=gen) < 0.25] = 0
+    order = ("high_first", "low_first")[seed % 2]
+    c = gen_masked_w4a8(G, max_m, n, k, mm, seed=6000 + seed, nibble_order=order)
+    bp = P.pack_w4a8_moe_hipc_weight(c["b_framework"].clone().to(DEV), nibble_order=order).cpu()
+    w_x16 = (c["w4"].to(torch.int16) * 16).to(torch.int8)
+    _check_int_case(c, _cabi.KIND_W4A8, w_x16, bp, c["b_scale"] / 16.0,
+                    what=f"seed {seed}: G={G} max_m={max_m} N={n} K={k} masked_m={mm.tolist()} {order}")
