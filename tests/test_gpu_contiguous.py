@@ -186,3 +186,32 @@ def test_random_group_sizes_and_tile_choices_bit_exact(seed):
              b_scale=c["b_scale"], m_indices=idx[:cut].contiguous())
     _check_int8_contig(c, rows, block_n=bn,
                        what=f"seed {seed}: rows={rows} N={n} K={k} align={align} BN={bn} cut={cut}")
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_contiguous_w4a8_random_group_sizes(seed):
+    """Seeded random contiguous W4A8 cases: ragged groups (empty ones included) padded to 128
+    rows, N not a multiple of the 128-channel tile, one to four 256-value rounds of K."""
+    gen = torch.Generator().manual_seed(7000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=gen))
+    G = r(1, 8)
+    rows = [0 if r(0, 3) == 0 else r(1, 400) for _ in range(G)]
+    if sum(rows) == 0:
+        rows[0] = r(1, 400)
+    n, k = 16 * r(1, 30), 256 * r(1, 4)
+    idx, M = O.build_contiguous_layout(rows, 128)
+    cw = gen_masked_w4a8(G, 1, n, k, [1] * G, seed=7100 + seed)                 # weights only
+    a, a_s = O.per_token_quant_int8(torch.randn(M, k, generator=gen))
+    bp = P.pack_w4a8_moe_hipc_weight(cw["b_framework"].clone().to(DEV))
+    out = torch.full((M, n), SENTINEL, dtype=torch.bfloat16, device=DEV)
+    deepgemm.m_grouped_w4a8_gemm_nt_contiguous_hipc(
+        (a.to(DEV), a_s.to(DEV)), (bp, (cw["b_scale"] / 16.0).unsqueeze(-1).to(DEV)), out, idx.to(DEV))
+    out = out.cpu()
+    w_x16 = (cw["w4"].to(torch.int16) * 16).to(torch.int8)
+    for g in range(G):
+        r_ = torch.nonzero(idx == g).flatten()
+        if r_.numel() == 0:
+            continue
+        want = O.epilogue_from_acc(O.exact_int_acc(a[r_], w_x16[g]), a_s.reshape(-1)[r_], cw["b_scale"][g] / 16.0)
+        assert_bf16_within_ulp(out[r_], want, 0, f"seed {seed}: rows={rows} N={n} K={k} group {g}")
+    assert torch.all(out[idx < 0].float() == SENTINEL), f"seed {seed}: padding rows were written"
