@@ -269,6 +269,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       // long ago costs this thread about 200 cycles, comparable with the four UMMAs of a
       // stage: the watcher warp does the waits and posts "stages ready" / "items ready" in
       // plain shared-memory words, which this thread re-reads only when its copy is used up.
+      // Ordering: the watcher observes the mbarrier (acquire), then publishes with st.release;
+      // this thread's volatile loads of one shared-memory word after another are performed in
+      // program order, and tcgen05.fence::after_thread_sync orders the UMMAs after the load
+      // that saw the new count.  The operands themselves are read by the tensor core only.
       auto poll_above = [&](uint32_t addr, uint32_t have, int site) -> uint32_t {
         uint32_t v;
 #pragma unroll 1

@@ -295,6 +295,10 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
       // nor touches an mbarrier: the watcher warp posts, in plain shared-memory words, how
       // many items (descriptor ready, accumulator free) and rounds (weights and tokens in
       // place) may be issued, and this thread re-reads a word only when its last copy is used up.
+      // Ordering: the watcher observes the mbarrier (acquire), then publishes with st.release;
+      // this thread's volatile loads of one shared-memory word after another are performed in
+      // program order, and tcgen05.fence::after_thread_sync orders the UMMAs after the load
+      // that saw the new count.  The operands themselves are read by the tensor core only.
       auto poll_above = [&](uint32_t addr, uint32_t have, int site) -> uint32_t {
         // returns a value > have, or 0 after giving up (abort flag set); the timer is only read
         // once the word has been found unchanged a few times (reading it costs ~100 cycles)
