@@ -601,7 +601,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
           const TileCoord t = dec.get(item);
           const StageShape sh = stage_shape(t.rows_valid, t.width, BN);
-          const uint32_t idesc = (kIdesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>(t.width >> 3) << 17);
+          // N = the tile's width; M = 64 when the item has no more than 64 rows: the tensor
+          // cores then work on half the rows, which on a GPU held back by its power cap buys SM
+          // clock (decode workload, all items at M = 64 for the comparison: 152-156 us at
+          // 1.3-1.9 GHz against 168-178 us at 0.86-1.05 GHz).  With M = 64 row r of the tile is
+          // TMEM lane 32 * (r / 16) + r % 16.
+          const uint32_t idesc = (kIdesc & ~(0x3Fu << 17) & ~(0x1Fu << 24)) |
+                                 (static_cast<uint32_t>(t.width >> 3) << 17) |
+                                 ((t.rows_valid <= 64 ? 4u : 8u) << 24);
           const int kps = kNarrow ? sh.kps : 1;
           const uint32_t buf = tile & 1u;
           const uint32_t aph = (tile >> 1) & 1u;
@@ -645,17 +652,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   } else if (warp < 6) {
     // ---- epilogue: this warp may touch TMEM lanes [32q, 32q+32)
     const int q = warp & 3;
-    const int row_in_tile = q * 32 + lane;
     ItemDecoder dec(p, tbl, bn_eff, nt_eff, split_from);
     uint32_t tile = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++tile) {
       const TileCoord t = dec.get(item);
+      // M = 128: this warp's lanes hold rows 32q .. 32q+31.  M = 64 (items of at most 64 rows):
+      // its lanes 0..15 hold rows 16q .. 16q+15 and the other lanes nothing.
+      const bool m64 = t.rows_valid <= 64;
+      const int rows_per_warp = m64 ? 16 : 32;
+      const int row_in_tile = q * rows_per_warp + lane;
       const uint32_t buf = tile & 1u;
       const uint32_t aph = (tile >> 1) & 1u;
       // Everything that depends only on the tile's coordinates is fetched before the wait for
       // the accumulator, so that the global-load latency hides behind the main loop.
       float* bs_s = reinterpret_cast<float*>(smem + L::off_bs) + q * BN;
-      const bool warp_has_rows = t.rows_valid > q * 32;  // warp-uniform
+      const bool warp_has_rows = t.rows_valid > q * rows_per_warp;  // warp-uniform
       bool rv = false;
       size_t grow = 0;
       EpiRow row;
@@ -664,7 +675,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (warp_has_rows) {
         stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, t.width, p.N, lane,
                           p.scale_mode == DG_SCALE_PER_CHANNEL);
-        rv = row_in_tile < t.rows_valid;
+        rv = lane < rows_per_warp && row_in_tile < t.rows_valid;
         grow = (p.mode == MODE_MASKED ? (size_t)t.g * p.M : (size_t)0) + t.row0 + row_in_tile;
         if (p.mode == MODE_CONTIG && rv) rv = p.sched[grow] >= 0;
         if (rv && p.scale_mode != DG_SCALE_NONE) row.as = p.a_scale[grow];
