@@ -101,6 +101,17 @@ class ClockSampler:
         except Exception:
             return None
 
+    def read_throttled(self) -> bool:
+        """True when a power or thermal limit (not idleness) is holding the clock right now."""
+        try:
+            try:
+                rs = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            except Exception:
+                rs = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            return bool(int(rs) & (0x4 | 0x8 | 0x20 | 0x40 | 0x80))
+        except Exception:
+            return False
+
     def start(self):
         if self.h is not None:
             self._thread = threading.Thread(target=self._loop, daemon=True)
@@ -400,8 +411,9 @@ def main():
     # Bring the SM clock up from idle before the W warm-up steps (a freshly acquired GPU sits
     # at its idle clock and a few milliseconds of warm-up do not ramp it): untimed launches
     # of the same step for PREHEAT_S seconds.
-    # If NVML still reports an SM clock below 90 % of the maximum after that, keep going for
-    # up to PREHEAT_MAX_S (the clock is only read, never set).
+    # If NVML still reports an SM clock below 90 % of the maximum after that and no power or
+    # thermal limit explains it, keep going for up to PREHEAT_MAX_S (the clock is only read,
+    # never set).
     sampler = ClockSampler(local_rank)
     t_pre = time.perf_counter()
     while True:
@@ -413,6 +425,8 @@ def main():
             continue
         mhz = sampler.read_mhz()
         if mhz is None or sampler.max_mhz is None or mhz >= 0.9 * sampler.max_mhz or spent >= PREHEAT_MAX_S:
+            break
+        if sampler.read_throttled():   # a power or thermal limit, not the ramp from idle: more launches only deepen it
             break
     config["preheat_s"] = round(time.perf_counter() - t_pre, 3)
 
