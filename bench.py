@@ -31,15 +31,23 @@ sys.path.insert(0, os.path.join(REPO, "deepgemm-das_b200"))
 
 import torch  # noqa: E402
 
-# DRAM bytes (read + write) one decode launch moves per expert, from the ncu capture of the
-# 8-expert case summarised in profiles/grouped_gemm_e4m3_bn128_masked_fp8_decode.md
-# (246.03 MB per launch); traffic grows in proportion to the number of experts.
-NCU_DECODE_DRAM_BYTES_PER_EXPERT = 966.73e6 / 32   # ncu dram read+write of a full launch (profiles/)
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size decode launch (32 experts), from an
+# ncu capture of this kernel; DRAM traffic grows in proportion to the number of experts.
+NCU_DECODE_DRAM_BYTES_PER_EXPERT = 966.73e6 / 32
 PREHEAT_S = 0.1
 PREHEAT_MAX_S = 0.3   # long preheats push a power-capped GPU deeper into its cap
 METRIC = "masked_fp8_decode_hbm_bandwidth"
 UNIT = "GB/s"
 C2 = dict(G=32, K=7168, N=4096, max_m=128, tokens=256, top_k=8)
+
+
+def algorithmic_bytes(valid_rows, groups_with_rows, groups, n, k, a_bytes, b_bytes, tensor_wise=False,
+                      index_entries=0):
+    """Bytes a grouped GEMM must move at minimum: activations and outputs of valid rows, weights
+    of groups that have rows, scales, and the masked_m / m_indices array."""
+    v, gp = valid_rows, groups_with_rows
+    return (v * k * a_bytes + gp * n * k * b_bytes + v * n * 2 + 4 * v +
+            (4 * gp if tensor_wise else 4 * gp * n) + 4 * (index_entries or groups))
 
 
 def _peaks():
@@ -164,7 +172,6 @@ def make_decode_workload(device, seed: int, cfg=C2, tensor_wise: bool = False):
 
 
 def decode_bytes(w) -> float:
-    from deepgemm.quant_utils import algorithmic_bytes
     cfg, mm = w["cfg"], w["masked_m_cpu"]
     return algorithmic_bytes(int(mm.sum()), int((mm > 0).sum()), cfg["G"], cfg["N"], cfg["K"], 1, 1,
                              tensor_wise=w["tensor_wise"])
@@ -202,7 +209,7 @@ def make_contig_int8_prefill(device, small=False):
     """Contiguous INT8 prefill: 32 experts, K=7168, N=4096, 4096 tokens top-8, groups padded to
     256 (small: 8 experts, 1024 tokens).  Returns (launch function, info)."""
     import deepgemm
-    from deepgemm.quant_utils import algorithmic_bytes, contiguous_layout, per_token_quant_int8
+    from deepgemm.quant_utils import contiguous_layout, per_token_quant_int8
     G, K, N, tokens = (8, 7168, 4096, 1024) if small else (32, 7168, 4096, 4096)
     cpu_gen = torch.Generator().manual_seed(3)
     picks = torch.rand(tokens, G, generator=cpu_gen).topk(8, dim=1).indices
@@ -243,8 +250,7 @@ def make_masked_w4a8(device, small=False):
     """Masked W4A8 down projection: 32 experts, N=7168, K=2048, max_m=256, masked_m uniform in
     [0,256]; int4 source bytes low-nibble-first.  Returns (launch function, info)."""
     import deepgemm
-    from deepgemm.quant_utils import (algorithmic_bytes, pack_int4_pairs, per_channel_quant_int4,
-                                      per_token_quant_int8)
+    from deepgemm.quant_utils import pack_int4_pairs, per_channel_quant_int4, per_token_quant_int8
     G, N, K, max_m = 32, 7168, 2048, 256
     cpu_gen = torch.Generator().manual_seed(4)
     mm = torch.randint(0, max_m + 1, (G,), generator=cpu_gen).to(torch.int32)
@@ -288,7 +294,6 @@ def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 120.0):
     of the headline workload: `ge` experts x `nc` output channels, same K, same routing."""
     sys.path.insert(0, os.path.join(REPO, "oracle"))
     import dg_oracle as O
-    from deepgemm.quant_utils import algorithmic_bytes
     cfg = C2
     K, max_m = cfg["K"], cfg["max_m"]
     cpu_gen = torch.Generator().manual_seed(0)
@@ -356,8 +361,8 @@ def main():
         cfg["G"], cfg["K"], cfg["N"], cfg["max_m"], cfg["tokens"], cfg["top_k"]),
         "sharding": "expert parallel, %d local experts per GPU" % cfg["G"],
         "l2": "inputs (%.0f MB per GPU) exceed the 126 MB L2; no flush" % (
-            cfg["G"] * cfg["N"] * cfg["K"] / 1e6),
-        "preheat_s": PREHEAT_S}
+            cfg["G"] * cfg["N"] * cfg["K"] / 1e6)}
+    measurement = {}   # how this run measured (not part of the workload's description)
 
     if args.impl == "reference":
         if rank != 0:
@@ -428,7 +433,7 @@ def main():
             break
         if sampler.read_throttled():   # a power or thermal limit, not the ramp from idle: more launches only deepen it
             break
-    config["preheat_s"] = round(time.perf_counter() - t_pre, 3)
+    measurement["preheat_s"] = round(time.perf_counter() - t_pre, 3)
 
     sampler.start()
     launches0 = _cabi.query(_cabi.QUERY_LAUNCH_COUNT)
@@ -446,11 +451,15 @@ def main():
         # launches.  A genuinely capped clock (a reason is reported) is kept as it is.  All
         # ranks take the decision together.
         attempts = 0
+        measurement["attempts"] = []   # every timed region, kept or not: ms per step, clock, reasons
         while True:
             attempts += 1
             launches0 = _cabi.query(_cabi.QUERY_LAUNCH_COUNT)
             ms, t0, t1 = time_launches(step, args.steps, warmup, barrier)
             c = sampler.summary(t0, t1)
+            measurement["attempts"].append({
+                "ms_per_step": ms / args.steps, "sm_mhz": c["sm_mhz"], "reasons": c["reasons"],
+                "ms_x_mhz": (ms / args.steps * c["sm_mhz"]) if c["sm_mhz"] else None})
             low = (c["sm_mhz"] is not None and c["sm_max_mhz"] and c["sm_mhz"] < 0.9 * c["sm_max_mhz"]
                    and not c["reasons"])
             flag = torch.tensor([1 if low else 0], device=device)
@@ -463,7 +472,7 @@ def main():
                 for _ in range(50):
                     step()
                 torch.cuda.synchronize()
-        config["measurement_attempts"] = attempts
+        measurement["reported_attempt"] = attempts
     launches = _cabi.query(_cabi.QUERY_LAUNCH_COUNT) - launches0
     sampler.stop()
     clocks = sampler.summary(t0, t1)
@@ -553,7 +562,7 @@ def main():
                          "traffic_note": "ncu dram__bytes_read + write of one full-size launch (32 experts), per expert x local experts",
                          "kernel": "grouped_gemm_kernel<E4M3,BN=256,4 stages> (rank 0)",
                          "algorithmic_bytes_per_launch": bytes_per_step},
-            "clocks": clocks,
+            "clocks": clocks, "measurement": measurement,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "pipeline": "double-buffered: H2D, kernel and D2H of neighbouring steps overlap",

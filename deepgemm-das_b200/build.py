@@ -22,8 +22,8 @@ LIB_PATH = os.path.join(LIB_DIR, "libdeepgemm_b200.so")
 STAMP_PATH = LIB_PATH + ".stamp"
 
 SOURCES = ["dg_api.cu"]
-HEADERS = ["dg_ptx.cuh", "dg_grouped_gemm.cuh", "dg_grouped_gemm_pair.cuh", "dg_grouped_gemm_w4.cuh",
-           "dg_pack.cuh", "dg_quant_group.cuh", "dg_moe_chain.cuh"]
+HEADERS = ["dg_ptx.cuh", "dg_grouped_gemm.cuh", "dg_grouped_gemm_pair.cuh", "dg_grouped_gemm_w4.cuh", "dg_grouped_gemm_w4s.cuh",
+           "dg_pack.cuh", "dg_quant_group.cuh", "dg_moe_chain.cuh", "dg_ep.cuh"]
 
 
 def _nvcc() -> str:

@@ -4,15 +4,18 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "deepgemm_b200.h"
 #include "dg_grouped_gemm.cuh"
 #include "dg_grouped_gemm_pair.cuh"
 #include "dg_grouped_gemm_w4.cuh"
+#include "dg_grouped_gemm_w4s.cuh"
 #include "dg_pack.cuh"
 #include "dg_moe_chain.cuh"
 #include "dg_quant_group.cuh"
+#include "dg_ep.cuh"
 
 namespace {
 
@@ -145,6 +148,9 @@ struct Problem {
   int out_kind;  // DG_OUT_BF16 / DG_OUT_F16 / DG_OUT_F32
   void* debug_acc;
   int32_t* status;
+  const int32_t* scatter_tag;
+  void* const* scatter_base;  // host array
+  int scatter_world;
 };
 
 template <int KIND, int BN>
@@ -175,6 +181,8 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.status = pr.status;
   p.b_rowmajor = pr.dense;
   p.out_kind = pr.out_kind;
+  p.scatter_tag = pr.scatter_tag;
+  for (int r = 0; r < pr.scatter_world && pr.scatter_tag != nullptr; ++r) p.scatter_base[r] = pr.scatter_base[r];
 
   const long long max_blocks = pr.mode == MODE_MASKED    ? (long long)pr.G * p.m_blocks
                                : pr.mode == MODE_COMPACT ? (long long)p.m_blocks + pr.G
@@ -297,6 +305,8 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
   p.status = pr.status;
   p.b_rowmajor = pr.dense;
+  p.scatter_tag = pr.scatter_tag;
+  for (int r = 0; r < pr.scatter_world && pr.scatter_tag != nullptr; ++r) p.scatter_base[r] = pr.scatter_base[r];
 
   const long long max_items =
       (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : 2LL * p.m_blocks) * p.n_tiles;
@@ -449,6 +459,99 @@ int launch_w4(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   return DG_OK;
 }
 
+// W4A8, tokens on UMMA M, 256 channels on N, int4 -> int8 unpack in shared memory.
+template <int SLOTS, int TOKS, int NG>
+int launch_w4_smem(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
+  using L = WsSmem<SLOTS, TOKS>;
+  auto kernel = grouped_gemm_w4_smem_kernel<SLOTS, TOKS, NG>;
+  KernelParams p{};
+  p.mode = pr.mode;
+  p.scale_mode = pr.scale_mode;
+  p.G = pr.G;
+  p.M = pr.M;
+  p.N = pr.N;
+  p.K = pr.K;
+  p.kblocks = pr.K / 128;  // K blocks of 128 values; a packed row covers two of them
+  p.n_tiles = (pr.N + kWsBN - 1) / kWsBN;
+  p.m_blocks = (pr.M + kBM - 1) / kBM;
+  p.sched = pr.sched;
+  p.a_scale = pr.a_scale;
+  p.b_scale = pr.b_scale;
+  p.d = static_cast<__nv_bfloat16*>(pr.d);
+  p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
+  p.status = pr.status;
+  p.out_kind = pr.out_kind;
+  p.split_tail = (pr.mode == MODE_MASKED) ? 1 : 0;
+  const long long max_items =
+      (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : (long long)p.m_blocks) * p.n_tiles;
+  if (max_items <= 0) return DG_OK;
+  const int table_bytes = (pr.mode == MODE_MASKED) ? (2 * pr.G + 1) * 4 : p.m_blocks * 4;
+  // the packed ring takes what the opt-in shared-memory limit leaves after the slots and the table
+  const int limit = dev.max_smem < kMaxSmem ? dev.max_smem : kMaxSmem;
+  int stages = (limit - L::total(table_bytes, 0)) / kWsPackStageBytes;
+  if (stages > kWsMaxPackStages) stages = kWsMaxPackStages;
+  if (stages < 2) return DG_ERR_TOO_LARGE;
+  p.pack_stages = stages;
+  p.pack_off = L::pack_offset(table_bytes);
+#ifdef DG_WS_PROF
+  if (const char* e = getenv("DG_PROF_PTR")) p.prof = reinterpret_cast<unsigned long long*>(strtoull(e, nullptr, 16));
+#endif
+  const int smem_bytes = L::total(table_bytes, stages);
+
+  // Token tiles: boxes of 128, 64, 32 and 8 rows, so an item fetches little more than its rows.
+  CUtensorMap tm_tok[4], tm_w, tm_w128;
+  int rc = DG_OK;
+  const uint32_t tok_rows[4] = {128u, 64u, 32u, 8u};
+  for (int i = 0; i < 4 && rc == DG_OK; ++i) {
+    if (pr.mode == MODE_MASKED) {
+      const uint64_t dims[3] = {(uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.G};
+      const uint64_t strides[2] = {(uint64_t)pr.K, (uint64_t)pr.M * pr.K};
+      const uint32_t box[3] = {128u, tok_rows[i], 1u};
+      rc = encode_map(&tm_tok[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, pr.a, dims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      const uint64_t dims[2] = {(uint64_t)pr.K, (uint64_t)pr.M};
+      const uint64_t strides[1] = {(uint64_t)pr.K};
+      const uint32_t box[2] = {128u, tok_rows[i]};
+      rc = encode_map(&tm_tok[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.a, dims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+  }
+  if (rc != DG_OK) return rc;
+  {
+    // packed weights: G*(K/256)*N rows of 128 bytes (256 int4 values); a box is the 64-byte half
+    // of 256 (or 128) consecutive rows that holds one K block, stored linearly in shared memory
+    const uint64_t dims[2] = {128, (uint64_t)pr.G * (pr.K / 256) * pr.N};
+    const uint64_t strides[1] = {128};
+    const uint32_t box[2] = {64u, (uint32_t)kWsBN};
+    const uint32_t box128[2] = {64u, 128u};
+    rc = encode_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.b, dims, strides, box,
+                    CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc == DG_OK)
+      rc = encode_map(&tm_w128, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pr.b, dims, strides, box128,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+  }
+  if (rc != DG_OK) return rc;
+
+  static std::atomic<unsigned long long> configured{0};
+  int devid = 0;
+  cudaGetDevice(&devid);
+  const unsigned long long bit = 1ull << (devid & 63);
+  if ((configured.load(std::memory_order_acquire) & bit) == 0) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    if (e != cudaSuccess) return cuda_fail(e);
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  const int grid = static_cast<int>(max_items < dev.sm_count ? max_items : dev.sm_count);
+  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_tok[0], tm_tok[1], tm_tok[2], tm_tok[3], tm_w,
+                                                    tm_w128, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int validate_and_launch(Problem& pr, cudaStream_t stream) {
@@ -521,7 +624,10 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
   }
   if (bn == 512 && (pr.N < 256 || pr.mode == MODE_COMPACT)) bn = 128;
   if (bn == 512 && scalar_out) bn = 256;
-  if (pr.kind == DG_KIND_W4A8) return launch_w4(pr, *dev, stream);
+  if (pr.kind == DG_KIND_W4A8) {
+    if (pr.block_n == 512) return launch_w4_smem<3, 3, 4>(pr, *dev, stream);
+    return launch_w4(pr, *dev, stream);
+  }
 
   if (bn == 512) {  // two-CTA 256x256 tiles
     switch (pr.kind) {
@@ -645,6 +751,16 @@ int dg_contig_gemm(const dg_contig_args* a, void* stream) {
   pr.expected_m = 0;
   pr.debug_acc = a->debug_acc;
   pr.status = a->status;
+  if (a->scatter_tag != nullptr) {
+    if (a->scatter_base == nullptr) return DG_ERR_NULL_POINTER;
+    if (a->scatter_world < 1 || a->scatter_world > DG_EP_MAX_WORLD) return DG_ERR_BAD_ARGUMENT;
+    if (a->kind == DG_KIND_W4A8 || a->n % 8 != 0 || a->debug_acc != nullptr) return DG_ERR_BAD_ARGUMENT;
+    for (int r = 0; r < a->scatter_world; ++r)
+      if (a->scatter_base[r] == nullptr || !aligned16(a->scatter_base[r])) return DG_ERR_BAD_ALIGNMENT;
+    pr.scatter_tag = a->scatter_tag;
+    pr.scatter_base = a->scatter_base;
+    pr.scatter_world = a->scatter_world;
+  }
   return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
 }
 
@@ -855,6 +971,124 @@ int dg_quant_group_rows_noalloc(const dg_quant_group_args* a, void* stream) {
     scratch = g_noalloc_ptr[dev];
   }
   return quant_group_common(a, scratch, stream);
+}
+
+// ---- expert-parallel exchange over peer memory (dg_ep.cuh)
+static int ep_copy_peers(dg::EpPeers* dst, void* const* src, int world) {
+  if (src == nullptr) return DG_ERR_NULL_POINTER;
+  for (int r = 0; r < dg::kEpMaxWorld; ++r) dst->ptr[r] = nullptr;
+  for (int r = 0; r < world; ++r) {
+    if (src[r] == nullptr) return DG_ERR_NULL_POINTER;
+    dst->ptr[r] = src[r];
+  }
+  return DG_OK;
+}
+
+int dg_ep_plan(const dg_ep_plan_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->world < 1 || a->world > DG_EP_MAX_WORLD || a->rank < 0 || a->rank >= a->world)
+    return DG_ERR_BAD_ARGUMENT;
+  if (a->num_experts < a->world || a->num_experts % a->world != 0 || a->num_pairs < 0 || a->align < 1 ||
+      a->m_cap < a->align)
+    return DG_ERR_BAD_SHAPE;
+  if (a->num_experts > DG_MAX_GROUPS) return DG_ERR_TOO_LARGE;
+  if (!a->my_base || !a->cursor || !a->m_indices || !a->m_total || (a->num_pairs > 0 && !a->topk_ids))
+    return DG_ERR_NULL_POINTER;
+  dg::EpPlanParams p{};
+  int rc = ep_copy_peers(&p.peer_counts, a->peer_counts, a->world);
+  if (rc == DG_OK) rc = ep_copy_peers(&p.peer_flags, a->peer_flags, a->world);
+  if (rc != DG_OK) return rc;
+  p.topk_ids = a->topk_ids;
+  p.pairs = a->num_pairs;
+  p.E = a->num_experts;
+  p.world = a->world;
+  p.me = a->rank;
+  p.e_local = a->num_experts / a->world;
+  p.align = a->align;
+  p.m_cap = a->m_cap;
+  p.counts = static_cast<int32_t*>(p.peer_counts.ptr[a->rank]);
+  p.flags = static_cast<int32_t*>(p.peer_flags.ptr[a->rank]);
+  p.epoch = a->epoch;
+  if (a->phases < 0 || a->phases > 3) return DG_ERR_BAD_ARGUMENT;
+  p.phases = a->phases == 0 ? 3 : a->phases;
+  p.my_base = a->my_base;
+  p.cursor = a->cursor;
+  p.m_indices = a->m_indices;
+  p.m_total = a->m_total;
+  p.status = a->status;
+  dg::ep_plan_kernel<<<1, dg::kEpPlanThreads, 3 * a->num_experts * sizeof(int32_t),
+                       static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
+int dg_ep_push(const dg_ep_push_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->world < 1 || a->world > DG_EP_MAX_WORLD || a->rank < 0 || a->rank >= a->world)
+    return DG_ERR_BAD_ARGUMENT;
+  if (a->num_experts < a->world || a->num_experts % a->world != 0 || a->num_tokens < 0 || a->top_k < 1 ||
+      a->top_k > dg::kEpMaxTopK || a->row_bytes < 16 || a->row_bytes % 16 != 0 || a->m_cap < 1)
+    return DG_ERR_BAD_SHAPE;
+  if (a->row_bytes > 16 * dg::kEpPushThreads * dg::kEpMaxChunksPerThread || a->num_experts > DG_MAX_GROUPS ||
+      (long long)a->num_tokens * a->top_k >= (1 << 24))
+    return DG_ERR_TOO_LARGE;
+  if (a->num_tokens == 0) return DG_OK;
+  if (!a->rows || !a->row_scale || !a->topk_ids || !a->my_base || !a->cursor) return DG_ERR_NULL_POINTER;
+  if (!aligned16(a->rows)) return DG_ERR_BAD_ALIGNMENT;
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != DG_OK) return rc;
+  dg::EpPushParams p{};
+  rc = ep_copy_peers(&p.peer_a, a->peer_a, a->world);
+  if (rc == DG_OK) rc = ep_copy_peers(&p.peer_scale, a->peer_scale, a->world);
+  if (rc == DG_OK) rc = ep_copy_peers(&p.peer_tag, a->peer_tag, a->world);
+  if (rc != DG_OK) return rc;
+  for (int r = 0; r < a->world; ++r)
+    if (!aligned16(a->peer_a[r])) return DG_ERR_BAD_ALIGNMENT;
+  p.rows = static_cast<const uint8_t*>(a->rows);
+  p.row_scale = a->row_scale;
+  p.topk_ids = a->topk_ids;
+  p.T = a->num_tokens;
+  p.top_k = a->top_k;
+  p.row_bytes = a->row_bytes;
+  p.E = a->num_experts;
+  p.e_local = a->num_experts / a->world;
+  p.me = a->rank;
+  p.m_cap = a->m_cap;
+  p.my_base = a->my_base;
+  p.cursor = a->cursor;
+  p.pair_dest = a->pair_dest;
+  p.status = a->status;
+  const int max_blocks = dev->sm_count * 8;
+  const int grid = a->num_tokens < max_blocks ? a->num_tokens : max_blocks;
+  dg::ep_push_kernel<<<grid, dg::kEpPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
+}
+
+int dg_ep_barrier(const dg_ep_barrier_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->world < 1 || a->world > DG_EP_MAX_WORLD || a->rank < 0 || a->rank >= a->world)
+    return DG_ERR_BAD_ARGUMENT;
+  dg::EpBarrierParams p{};
+  int rc = ep_copy_peers(&p.peer_flags, a->peer_flags, a->world);
+  if (rc != DG_OK) return rc;
+  p.flags = static_cast<int32_t*>(p.peer_flags.ptr[a->rank]);
+  p.world = a->world;
+  p.me = a->rank;
+  p.epoch = a->epoch;
+  if (a->phases < 0 || a->phases > 3) return DG_ERR_BAD_ARGUMENT;
+  p.phases = a->phases == 0 ? 3 : a->phases;
+  p.status = a->status;
+  dg::ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return DG_OK;
 }
 
 int64_t dg_query(int32_t what) {

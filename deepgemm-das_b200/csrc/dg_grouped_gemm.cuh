@@ -77,6 +77,17 @@ struct KernelParams {
   int out_kind;    // 0 = bf16 output; 1 = fp16, 2 = fp32 (dense GEMM only, scalar stores)
   int split_tail;  // masked / compact: 1 = the items of a last round that is at most half full are
                    // split into two halves of BN / 2 columns
+#ifdef DG_WS_PROF
+  unsigned long long* prof;
+#endif
+  int pack_stages;  // W4A8: stages of the packed-weight ring
+  int pack_off;     // W4A8: offset of that ring in the block's shared memory
+  // Contiguous layout only: when scatter_tag is given, output row i is written to row
+  // (scatter_tag[i] & 0xFFFFFF) of the buffer scatter_base[scatter_tag[i] >> 24] (bf16 [.][N], on
+  // this or a peer GPU) instead of d[i] -- the result rows of an expert-parallel layer go straight
+  // back to the ranks their tokens came from, tile by tile, while the GEMM is still running.
+  const int32_t* scatter_tag;
+  void* scatter_base[16];
   int narrow;  // masked / compact: 0 = tiles stay BN columns wide, 1 = the kernel may narrow them
                // (down to 32 columns) when few groups have rows, 128 / 64 / 32 = forced width
 };
@@ -203,6 +214,8 @@ struct EpiWarp {
   size_t ld;              // elements between consecutive rows of D (= N)
   unsigned rv_mask;       // bit r: row r of the warp may be stored
   int lane;
+  __nv_bfloat16* lane_row = nullptr;  // scattered output: where this lane's row goes (&dst[row][n0])
+  bool scatter = false;               // warp-uniform
 };
 
 // Coalesced form of epilogue_store32: every lane converts its row's 32 columns into the warp's
@@ -220,14 +233,16 @@ __device__ __forceinline__ void epilogue_store32_staged(const uint32_t (&r)[32],
         epilogue_pack8<kIntAcc>(r, 8 * p, e, scale_mode, col);
   __syncwarp();
   const int p = w.lane & 3;
-  if (8 * p + 8 <= cols_left) {
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      const int row = (w.lane >> 2) + 8 * h;
-      if ((w.rv_mask >> row) & 1u)
-        *reinterpret_cast<uint4*>(w.d_warp + row * w.ld + col + 8 * p) =
-            *reinterpret_cast<const uint4*>(w.strip + row * 64 + ((p ^ ((row >> 1) & 3)) << 4));
-    }
+  for (int h = 0; h < 4; ++h) {
+    const int row = (w.lane >> 2) + 8 * h;
+    __nv_bfloat16* dst = w.d_warp + row * w.ld;
+    if (w.scatter)  // the row's destination is known to the lane that owns the row
+      dst = reinterpret_cast<__nv_bfloat16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(w.lane_row), row));
+    if (8 * p + 8 <= cols_left && ((w.rv_mask >> row) & 1u))
+      *reinterpret_cast<uint4*>(dst + col + 8 * p) =
+          *reinterpret_cast<const uint4*>(w.strip + row * 64 + ((p ^ ((row >> 1) & 3)) << 4));
   }
   __syncwarp();  // the strip is rewritten by the next chunk
 }
@@ -688,6 +703,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         const size_t d_off = grow * p.N + t.n0;  // in output elements
         row.d_row = p.out_kind == 2 ? reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<float*>(p.d) + d_off)
                                     : p.d + d_off;
+        const bool scatter = p.mode == MODE_CONTIG && p.scatter_tag != nullptr;
+        if (scatter && rv) {
+          const int tag = p.scatter_tag[grow];
+          row.d_row = static_cast<__nv_bfloat16*>(p.scatter_base[(tag >> 24) & 15]) +
+                      (size_t)(tag & 0xFFFFFF) * p.N + t.n0;
+        }
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const bool scalar_out = p.out_kind != 0 || (p.N & 7) != 0;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
@@ -698,6 +719,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         ew.ld = static_cast<size_t>(p.N);
         ew.rv_mask = __ballot_sync(0xffffffffu, rv);
         ew.lane = lane;
+        ew.scatter = scatter;
+        ew.lane_row = row.d_row;
         epilogue_drain<kIntAcc>(t_row, min(t.width / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
                                 cols_left0, scalar_out, p.out_kind);
       }

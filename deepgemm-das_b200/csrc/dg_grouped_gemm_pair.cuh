@@ -382,6 +382,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (warp_has_rows) {
         row.bs_row = bs_s;
         row.d_row = p.d + grow * p.N + t.n0;
+        const bool scatter = p.mode == MODE_CONTIG && p.scatter_tag != nullptr;
+        if (scatter && rv) {
+          const int tag = p.scatter_tag[grow];
+          row.d_row = static_cast<__nv_bfloat16*>(p.scatter_base[(tag >> 24) & 15]) +
+                      (size_t)(tag & 0xFFFFFF) * p.N + t.n0;
+        }
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kPairBN;
         const int cols_left0 = p.N - t.n0;
@@ -391,6 +397,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         ew.ld = static_cast<size_t>(p.N);
         ew.rv_mask = __ballot_sync(0xffffffffu, rv);
         ew.lane = lane;
+        ew.scatter = scatter;
+        ew.lane_row = row.d_row;
         epilogue_drain<kIntAcc>(t_row, min(kPairBN / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
                                 cols_left0, false, 0);
       }

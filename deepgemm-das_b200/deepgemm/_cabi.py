@@ -31,6 +31,9 @@ EXPORTED_SYMBOLS = (
     "dg_group_sorted_rows",
     "dg_silu_mul_quant_rows",
     "dg_combine_rows",
+    "dg_ep_plan",
+    "dg_ep_push",
+    "dg_ep_barrier",
     "dg_pack_weight",
     "dg_unpack_weight",
     "dg_query",
@@ -78,6 +81,10 @@ class ContigArgs(C.Structure):
         ("reserved", C.c_int32),
         ("debug_acc", C.c_void_p),
         ("status", C.c_void_p),
+        ("scatter_tag", C.c_void_p),
+        ("scatter_base", C.POINTER(C.c_void_p)),
+        ("scatter_world", C.c_int32),
+        ("reserved2", C.c_int32),
     ]
 
 
@@ -198,6 +205,70 @@ class CombineArgs(C.Structure):
     ]
 
 
+EP_MAX_WORLD = 16
+EP_PHASE_POST, EP_PHASE_WAIT = 1, 2
+
+
+class EpPlanArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("num_experts", C.c_int32),
+        ("num_pairs", C.c_int32),
+        ("align", C.c_int32),
+        ("m_cap", C.c_int32),
+        ("epoch", C.c_int32),
+        ("phases", C.c_int32),
+        ("topk_ids", C.c_void_p),
+        ("peer_counts", C.POINTER(C.c_void_p)),
+        ("peer_flags", C.POINTER(C.c_void_p)),
+        ("my_base", C.c_void_p),
+        ("cursor", C.c_void_p),
+        ("m_indices", C.c_void_p),
+        ("m_total", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
+class EpPushArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("num_experts", C.c_int32),
+        ("num_tokens", C.c_int32),
+        ("top_k", C.c_int32),
+        ("row_bytes", C.c_int32),
+        ("m_cap", C.c_int32),
+        ("reserved", C.c_int32),
+        ("rows", C.c_void_p),
+        ("row_scale", C.c_void_p),
+        ("topk_ids", C.c_void_p),
+        ("my_base", C.c_void_p),
+        ("cursor", C.c_void_p),
+        ("peer_a", C.POINTER(C.c_void_p)),
+        ("peer_scale", C.POINTER(C.c_void_p)),
+        ("peer_tag", C.POINTER(C.c_void_p)),
+        ("pair_dest", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
+class EpBarrierArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("epoch", C.c_int32),
+        ("phases", C.c_int32),
+        ("peer_flags", C.POINTER(C.c_void_p)),
+        ("status", C.c_void_p),
+    ]
+
+
+def pointer_array(ptrs):
+    """ctypes array of device pointers (a HOST array, as the dg_ep_* calls take)."""
+    return (C.c_void_p * len(ptrs))(*[int(x) for x in ptrs])
+
+
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -230,6 +301,12 @@ def _load() -> C.CDLL:
     lib.dg_silu_mul_quant_rows.restype = C.c_int
     lib.dg_combine_rows.argtypes = [C.POINTER(CombineArgs), C.c_void_p]
     lib.dg_combine_rows.restype = C.c_int
+    lib.dg_ep_plan.argtypes = [C.POINTER(EpPlanArgs), C.c_void_p]
+    lib.dg_ep_plan.restype = C.c_int
+    lib.dg_ep_push.argtypes = [C.POINTER(EpPushArgs), C.c_void_p]
+    lib.dg_ep_push.restype = C.c_int
+    lib.dg_ep_barrier.argtypes = [C.POINTER(EpBarrierArgs), C.c_void_p]
+    lib.dg_ep_barrier.restype = C.c_int
     lib.dg_query.argtypes = [C.c_int32]
     lib.dg_query.restype = C.c_int64
     lib.dg_strerror.argtypes = [C.c_int]

@@ -164,8 +164,11 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
                             d: torch.Tensor, a_scale: Optional[torch.Tensor],
                             b_scale: Optional[torch.Tensor], m_indices: torch.Tensor, *,
                             block_n: int = 0, debug_acc: Optional[torch.Tensor] = None,
-                            status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """d[i] = bf16((A[i] @ B[m_indices[i]]^T) * a_scale[i] * b_scale[m_indices[i]]) via dg_contig_gemm."""
+                            status: Optional[torch.Tensor] = None, scatter=None) -> torch.Tensor:
+    """d[i] = bf16((A[i] @ B[m_indices[i]]^T) * a_scale[i] * b_scale[m_indices[i]]) via dg_contig_gemm.
+    ``scatter`` = (tag int32 [M] CUDA tensor, ctypes array of buffer pointers, count): result row i
+    goes to row ``tag[i] & 0xFFFFFF`` of buffer ``tag[i] >> 24`` instead of ``d[i]`` (``d`` is then
+    only checked for dtype and device)."""
     what = f"contiguous {KIND_NAMES[kind]} grouped GEMM"
     if not (a.dim() == 2):
         raise RuntimeError(f"{what}: activation must be [M, K], got {tuple(a.shape)}")
@@ -176,8 +179,15 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
     _common_checks(kind, a, b, d, m_indices, what)
     if not (bk == k):
         raise RuntimeError(f"{what}: weight K={bk} does not match activation K={k}")
-    if not (tuple(d.shape) == (m_total, n)):
+    if scatter is None and not (tuple(d.shape) == (m_total, n)):
         raise RuntimeError(f"{what}: output must be {(m_total, n)}, got {tuple(d.shape)}")
+    if scatter is not None:
+        tag, bases, count = scatter
+        if not (tag.is_cuda and tag.device == a.device and tag.dtype == torch.int32 and tag.is_contiguous()
+                and tag.numel() == m_total):
+            raise RuntimeError(f"{what}: scatter tag must be contiguous CUDA int32 [{m_total}]")
+        if not (d.shape[-1] == n):
+            raise RuntimeError(f"{what}: scattered rows have {n} columns, the buffers {d.shape[-1]}")
     if not (m_indices.numel() == m_total):
         raise RuntimeError(f"{what}: m_indices must have {m_total} entries")
     if scale_mode == SCALE_NONE:
@@ -194,6 +204,8 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), m_indices=m_indices.data_ptr(), num_groups=g,
         m_total=m_total, n=n, k=k, block_n=int(block_n), reserved=0,
         debug_acc=_ptr(debug_acc), status=_ptr(status))
+    if scatter is not None:
+        args.scatter_tag, args.scatter_base, args.scatter_world = scatter[0].data_ptr(), scatter[1], int(scatter[2])
     _launch(_cabi.lib.dg_contig_gemm, args, a.device, what)
     return d
 

@@ -1,0 +1,266 @@
+"""Expert-parallel MoE layer whose token exchange runs over peer memory (NVLink / NVSwitch).
+
+The reference library is single-GPU; a serving framework that shards its experts over the GPUs
+of a box moves the routed rows itself.  ``expert_parallel.py`` does that with NCCL all-to-alls
+(host-known split sizes, hence a host synchronisation, plus a regroup pass on the receiver).
+This module is the device-side form: every rank maps one buffer of every other rank
+(``torch.distributed``'s symmetric memory) and the kernels behind ``dg_ep_plan`` /
+``dg_ep_push`` / ``dg_ep_barrier`` write each routed row straight into the owning rank's
+grouped, padded activation buffer; the second GEMM's epilogue writes every result row straight
+back into the buffer of the rank the token came from (``scatter_tag`` of ``dg_contig_gemm``), so
+the return transfer overlaps the GEMM tile by tile and the final weighted sum is a local read.
+A layer is nine launches on one stream and never synchronises with the host:
+
+    quantise rows -> plan (counts exchange) -> push -> barrier -> gate/up GEMM ->
+    SiLU*up + requantise -> down GEMM (scattering) -> barrier -> weighted top-k sum
+
+With one rank the same code runs on plain tensors.  ``make_emulated_ranks`` plays several ranks
+on one GPU for tests (every phase of all ranks is enqueued before the next phase).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _cabi, _core
+from ._core import _launch
+
+__all__ = ["EPExchange", "make_emulated_ranks", "layout_from_counts"]
+
+
+def _round_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+def layout_from_counts(counts: torch.Tensor, rank: int, align: int):
+    """What ``dg_ep_plan`` derives from the full counts table, restated with torch ops (used by
+    the tests as the expected value).  ``counts`` int [world, E].  Returns ``(my_base [E],
+    m_indices of rank's receive buffer (unpadded tail not included), m_total)``."""
+    world, e = counts.shape
+    e_local = e // world
+    c = counts.to(torch.int64)
+    tot = c.sum(dim=0)
+    padded = (tot + align - 1) // align * align
+    before = c[:rank].sum(dim=0)
+    start = torch.zeros(e, dtype=torch.int64)
+    for r in range(world):
+        seg = padded[r * e_local:(r + 1) * e_local]
+        start[r * e_local:(r + 1) * e_local] = torch.cumsum(seg, 0) - seg
+    my_base = (start + before).to(torch.int32)
+    rows = []
+    for el in range(e_local):
+        g = rank * e_local + el
+        rows.append(torch.full((int(tot[g]),), el, dtype=torch.int32))
+        rows.append(torch.full((int(padded[g] - tot[g]),), -1, dtype=torch.int32))
+    m_indices = torch.cat(rows) if rows else torch.zeros(0, dtype=torch.int32)
+    return my_base, m_indices, int(padded[rank * e_local:(rank + 1) * e_local].sum())
+
+
+class EPExchange:
+    """Buffers, peer pointers and the layer driver of one rank.
+
+    ``hidden`` / ``out_hidden``: row lengths going into the gate/up GEMM and coming out of the
+    down GEMM; ``inter2`` = columns of the gate/up GEMM (gate | up).  ``m_cap``: rows of every
+    rank's receive buffer (the same on all ranks); pairs that do not fit are dropped and
+    reported through ``check_status``.  The exchange buffers and the GEMM intermediates are
+    allocated here, once; in ``forward`` only the per-token quantisation allocates its outputs.
+    """
+
+    _ALIGN = 256
+
+    @staticmethod
+    def _sizes(world, num_experts, hidden, out_hidden, max_tokens, top_k, m_cap):
+        return {"recv_a": m_cap * hidden, "recv_scale": m_cap * 4, "recv_tag": m_cap * 4,
+                "counts": world * num_experts * 4, "flags": _cabi.EP_MAX_WORLD * 4,
+                "y_back": max_tokens * top_k * out_hidden * 2}
+
+    @classmethod
+    def shared_size(cls, world, num_experts, hidden, out_hidden, max_tokens, top_k, m_cap) -> int:
+        """Bytes of the buffer every rank maps."""
+        sizes = cls._sizes(world, num_experts, hidden, out_hidden, max_tokens, top_k,
+                           _round_up(m_cap, cls._ALIGN))
+        return sum(_round_up(v, 256) for v in sizes.values())
+
+    def __init__(self, rank: int, world: int, num_experts: int, hidden: int, inter2: int, out_hidden: int,
+                 max_tokens: int, top_k: int, m_cap: int, device: torch.device, *, kind: str = "fp8",
+                 group=None, _shared: Optional[Tuple[torch.Tensor, List[int]]] = None):
+        if num_experts % world:
+            raise ValueError("num_experts must be a multiple of the number of ranks")
+        if world > _cabi.EP_MAX_WORLD:
+            raise ValueError(f"at most {_cabi.EP_MAX_WORLD} ranks")
+        if kind not in ("fp8", "int8"):
+            raise ValueError("kind must be 'fp8' or 'int8'")
+        self.rank, self.world, self.num_experts = rank, world, num_experts
+        self.e_local = num_experts // world
+        self.hidden, self.inter2, self.out_hidden = hidden, inter2, out_hidden
+        self.max_tokens, self.top_k, self.kind = max_tokens, top_k, kind
+        self.m_cap = _round_up(m_cap, self._ALIGN)
+        self.device = device
+        self.epoch = 0
+        # ---- the one buffer every rank maps: receive side of the dispatch and of the return
+        sizes = self._sizes(world, num_experts, hidden, out_hidden, max_tokens, top_k, self.m_cap)
+        self._off, total = {}, 0
+        for name, nbytes in sizes.items():
+            self._off[name] = total
+            total += _round_up(nbytes, 256)
+        self.shared_bytes = total
+        if _shared is not None:                       # emulated ranks / one rank: plain tensors
+            self._buf, bases = _shared
+        elif world == 1:
+            self._buf = torch.zeros(total, dtype=torch.uint8, device=device)
+            bases = [self._buf.data_ptr()]
+        else:
+            import os
+            # peer loads and stores only: do not bind the buffer to an NVLink multicast object
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm
+            grp = group if group is not None else dist.group.WORLD
+            self._buf = symm.empty(total, dtype=torch.uint8, device=device)
+            self._buf.zero_()
+            self._hdl = symm.rendezvous(self._buf, grp.group_name)
+            bases = [int(p) for p in self._hdl.buffer_ptrs]
+            torch.cuda.synchronize(device)
+            dist.barrier(group=grp)                    # every rank's flags are zero before first use
+        self._bases = bases
+        self._peer = {name: _cabi.pointer_array([b + off for b in bases]) for name, off in self._off.items()}
+
+        def view(name, dtype, shape):
+            n = sizes[name]
+            return self._buf[self._off[name]:self._off[name] + n].view(dtype).view(shape)
+        qdtype = torch.float8_e4m3fn if kind == "fp8" else torch.int8
+        self.recv_a = view("recv_a", qdtype, (self.m_cap, hidden))
+        self.recv_scale = view("recv_scale", torch.float32, (self.m_cap,))
+        self.recv_tag = view("recv_tag", torch.int32, (self.m_cap,))
+        self.counts = view("counts", torch.int32, (world, num_experts))
+        self.y_back = view("y_back", torch.bfloat16, (max_tokens * top_k, out_hidden))
+        # ---- this rank's own working set
+        i32 = dict(dtype=torch.int32, device=device)
+        self.my_base = torch.zeros(num_experts, **i32)
+        self.cursor = torch.zeros(num_experts, **i32)
+        self.m_indices = torch.full((self.m_cap,), -1, **i32)
+        self.m_total = torch.zeros(1, **i32)
+        self.status = torch.zeros(_cabi.STATUS_WORDS, **i32)
+        self.pair_dest = torch.zeros(max_tokens * top_k, **i32)
+        self.pair_index = torch.arange(max_tokens * top_k, **i32)
+        self.h13 = torch.empty((self.m_cap, inter2), dtype=torch.bfloat16, device=device)
+        self.act_q = torch.empty((self.m_cap, inter2 // 2), dtype=qdtype, device=device)
+        self.act_scale = torch.empty((self.m_cap,), dtype=torch.float32, device=device)
+
+    # ------------------------------------------------------------------ the steps
+    def plan(self, topk_ids: torch.Tensor, phases: int = 0) -> None:
+        """Counts exchange + layout (``dg_ep_plan``).  ``topk_ids`` int32 [T, top_k]."""
+        if phases in (0, _cabi.EP_PHASE_POST):
+            self.epoch += 1
+        args = _cabi.EpPlanArgs(
+            world=self.world, rank=self.rank, num_experts=self.num_experts, num_pairs=topk_ids.numel(),
+            align=self._ALIGN, m_cap=self.m_cap, epoch=self.epoch, phases=phases,
+            topk_ids=topk_ids.data_ptr(), peer_counts=self._peer["counts"], peer_flags=self._peer["flags"],
+            my_base=self.my_base.data_ptr(), cursor=self.cursor.data_ptr(),
+            m_indices=self.m_indices.data_ptr(), m_total=self.m_total.data_ptr(),
+            status=self.status.data_ptr())
+        _launch(_cabi.lib.dg_ep_plan, args, self.device, "dg_ep_plan")
+
+    def push(self, q: torch.Tensor, q_scale: torch.Tensor, topk_ids: torch.Tensor) -> None:
+        """Writes every routed row into its owner's receive buffer (``dg_ep_push``)."""
+        t, k = topk_ids.shape
+        args = _cabi.EpPushArgs(
+            world=self.world, rank=self.rank, num_experts=self.num_experts, num_tokens=t, top_k=k,
+            row_bytes=self.hidden, m_cap=self.m_cap, reserved=0, rows=q.data_ptr(),
+            row_scale=q_scale.data_ptr(), topk_ids=topk_ids.data_ptr(), my_base=self.my_base.data_ptr(),
+            cursor=self.cursor.data_ptr(), peer_a=self._peer["recv_a"], peer_scale=self._peer["recv_scale"],
+            peer_tag=self._peer["recv_tag"], pair_dest=self.pair_dest.data_ptr(),
+            status=self.status.data_ptr())
+        _launch(_cabi.lib.dg_ep_push, args, self.device, "dg_ep_push")
+
+    def barrier(self, phases: int = 0) -> None:
+        if phases in (0, _cabi.EP_PHASE_POST):
+            self.epoch += 1
+        args = _cabi.EpBarrierArgs(world=self.world, rank=self.rank, epoch=self.epoch, phases=phases,
+                                   peer_flags=self._peer["flags"], status=self.status.data_ptr())
+        _launch(_cabi.lib.dg_ep_barrier, args, self.device, "dg_ep_barrier")
+
+    def experts(self, w13, w2) -> None:
+        """gate/up GEMM -> SiLU*up + requantise -> down GEMM whose result rows go home."""
+        from .moe_chain import silu_mul_quant
+        kind = _cabi.KIND_E4M3 if self.kind == "fp8" else _cabi.KIND_I8
+        _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, self.recv_a, w13[0], self.h13,
+                                      self.recv_scale, w13[1], self.m_indices)
+        silu_mul_quant(self.h13, kind=self.kind, m_indices=self.m_indices, out=(self.act_q, self.act_scale))
+        # the scattering GEMM never writes `d`; it only has to be a valid bf16 tensor
+        _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, self.act_q, w2[0], self.y_back,
+                                      self.act_scale, w2[1], self.m_indices,
+                                      scatter=(self.recv_tag, self._peer["y_back"], self.world))
+
+    def combine(self, topk_weights: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .moe_chain import combine_rows
+        t, k = topk_weights.shape
+        return combine_rows(self.y_back[:t * k], self.pair_index[:t * k].view(t, k), topk_weights, out=out)
+
+    def quantise(self, hidden: torch.Tensor):
+        from .quant_group import quantize_rows
+        return quantize_rows(hidden, kind=self.kind)
+
+    def forward(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, w13, w2,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One layer for this rank's tokens: hidden bf16 [T, hidden], topk_ids int32 [T, top_k],
+        topk_weights fp32 [T, top_k]; ``w13`` / ``w2`` = (packed weight, scale) of this rank's
+        experts.  Returns bf16 [T, out_hidden].  Enqueues only; call ``check_status`` after a
+        synchronisation to learn of dropped pairs or a peer that never arrived."""
+        if topk_ids.dtype != torch.int32 or not topk_ids.is_contiguous():
+            raise ValueError("topk_ids must be contiguous int32 [T, top_k]")
+        if topk_ids.shape[0] > self.max_tokens or topk_ids.shape[1] != self.top_k:
+            raise ValueError("more tokens than the exchange was sized for, or another top_k")
+        q, q_scale = self.quantise(hidden)
+        self.plan(topk_ids)
+        self.push(q, q_scale, topk_ids)
+        self.barrier()
+        self.experts(w13, w2)
+        self.barrier()
+        return self.combine(topk_weights.to(torch.float32), out=out)
+
+    def check_status(self) -> None:
+        """Reads the device status words (synchronises the device) and raises on a problem."""
+        st = self.status.tolist()
+        if st[0] == 1:
+            raise RuntimeError(f"expert-parallel exchange: rank {st[1]} gave up waiting for peer "
+                               f"{st[2] - 100} at epoch {st[3]}")
+        if st[0] != 0:
+            raise RuntimeError("expert-parallel exchange: routed rows did not fit the receive buffer "
+                               f"(m_cap = {self.m_cap}) and were dropped")
+
+
+def make_emulated_ranks(world: int, num_experts: int, hidden: int, inter2: int, out_hidden: int,
+                        max_tokens: int, top_k: int, m_cap: int, device: torch.device, *,
+                        kind: str = "fp8") -> List[EPExchange]:
+    """``world`` ranks on one GPU, each with its own buffers and everyone's pointers (tests)."""
+    nbytes = EPExchange.shared_size(world, num_experts, hidden, out_hidden, max_tokens, top_k, m_cap)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
+    bases = [b.data_ptr() for b in bufs]
+    return [EPExchange(r, world, num_experts, hidden, inter2, out_hidden, max_tokens, top_k, m_cap, device,
+                       kind=kind, _shared=(bufs[r], bases)) for r in range(world)]
+
+
+def emulated_forward(ranks: Sequence[EPExchange], hidden: Sequence[torch.Tensor],
+                     topk_ids: Sequence[torch.Tensor], topk_weights: Sequence[torch.Tensor],
+                     w13: Sequence, w2: Sequence) -> List[torch.Tensor]:
+    """One layer of every emulated rank, phase by phase (the posting half of each barrier for all
+    ranks before any waiting half)."""
+    qs = [r.quantise(h) for r, h in zip(ranks, hidden)]
+    for r, ids in zip(ranks, topk_ids):
+        r.plan(ids, _cabi.EP_PHASE_POST)
+    for r, ids in zip(ranks, topk_ids):
+        r.plan(ids, _cabi.EP_PHASE_WAIT)
+    for r, (q, s), ids in zip(ranks, qs, topk_ids):
+        r.push(q, s, ids)
+    for ph in (_cabi.EP_PHASE_POST, _cabi.EP_PHASE_WAIT):
+        for r in ranks:
+            r.barrier(ph)
+    for r, a, b in zip(ranks, w13, w2):
+        r.experts(a, b)
+    for ph in (_cabi.EP_PHASE_POST, _cabi.EP_PHASE_WAIT):
+        for r in ranks:
+            r.barrier(ph)
+    return [r.combine(w.to(torch.float32)) for r, w in zip(ranks, topk_weights)]

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define DG_ABI_VERSION 1
+#define DG_ABI_VERSION 2
 
 /* Exported-symbol marker: the library is built with hidden default visibility. */
 #if defined(__GNUC__)
@@ -143,6 +143,15 @@ typedef struct dg_contig_args {
   int32_t reserved;
   void*          debug_acc;   /* NULL, or [M_total][N] raw accumulators */
   int32_t*       status;
+  /* Scattered output (expert-parallel layers): when scatter_tag is not NULL, the result row i
+   * is written to row (scatter_tag[i] & 0xFFFFFF) of the bf16 [.][N] buffer
+   * scatter_base[scatter_tag[i] >> 24] instead of d[i]; the buffers may live on peer GPUs that
+   * this GPU has mapped (plain 16-byte stores; see dg_ep_push for the tag).  `d` is then unused
+   * but must still be a valid pointer.  bf16 output, N % 8 == 0. */
+  const int32_t* scatter_tag;   /* NULL, or [M_total] device array */
+  void* const*   scatter_base;  /* HOST array of scatter_world device pointers */
+  int32_t        scatter_world; /* 1..DG_EP_MAX_WORLD */
+  int32_t        reserved2;
 } dg_contig_args;
 
 /* Arguments of the compact-layout grouped GEMM: rows of all groups in one flat tensor, group g
@@ -404,6 +413,96 @@ DG_API int dg_combine_rows(const dg_combine_args* args, void* stream);
  * This function has no counterpart in the reference. */
 #define DG_NOALLOC_MAX_SCRATCH_INTS (262144 + 1024)
 DG_API int dg_quant_group_rows_noalloc(const dg_quant_group_args* args, void* stream);
+
+/*
+ * Expert-parallel exchange over peer memory.  The reference is a single-GPU library and has no
+ * counterpart for these three calls: serving frameworks shard its experts over the GPUs of a box
+ * and move the routed rows themselves (all-to-all dispatch before the first grouped GEMM, the
+ * reverse after the second).  Here the exchange is done by kernels of this library with plain
+ * peer-to-peer stores into buffers that every rank has mapped into its address space (for
+ * example with torch.distributed's symmetric memory, or CUDA IPC); no call synchronises with the
+ * host, so a whole layer is enqueued without a round trip.
+ *
+ * Ranks 0..world-1 own num_experts / world consecutive experts each.  Per layer every rank calls,
+ * on one stream: dg_ep_plan, dg_ep_push, dg_ep_barrier, its grouped GEMMs (the second with
+ * scatter_tag / scatter_base so that result rows go straight home), dg_ep_barrier,
+ * dg_combine_rows.  `epoch` must grow by one with every dg_ep_plan / dg_ep_barrier call of a
+ * rank and be the same on all ranks for the same call.  All waits on peers are bounded (2 s): on
+ * expiry status[0] = DG_DEV_WAIT_EXPIRED and the stream carries on.
+ * Every peer_* argument is a HOST array of `world` device pointers, entry r being rank r's copy
+ * of the buffer (entry `rank` is this rank's own).
+ */
+#define DG_EP_MAX_WORLD 16
+/* dg_ep_plan and dg_ep_barrier consist of a posting half (publish, signal) and a waiting half
+ * (wait for every rank's signal, then the rest).  With `phases` = 0 a call does both.  A test
+ * that plays several ranks on ONE GPU must enqueue the posting half of every rank before any
+ * waiting half (two launches per rank): kernels that wait for one another cannot be relied on to
+ * run at the same time on one GPU. */
+#define DG_EP_PHASE_POST 1
+#define DG_EP_PHASE_WAIT 2
+
+typedef struct dg_ep_plan_args {
+  int32_t world;              /* ranks, 1..DG_EP_MAX_WORLD */
+  int32_t rank;               /* this rank */
+  int32_t num_experts;        /* E, multiple of world, <= DG_MAX_GROUPS */
+  int32_t num_pairs;          /* tokens * top_k of this rank */
+  int32_t align;              /* rows each expert's block is padded to in the receive buffers (e.g. 256) */
+  int32_t m_cap;              /* rows of every rank's receive buffer */
+  int32_t epoch;
+  int32_t phases;             /* 0 = the whole call; DG_EP_PHASE_POST / DG_EP_PHASE_WAIT: one half of it */
+  const int32_t* topk_ids;    /* [num_pairs] expert of each (token, slot) pair */
+  void* const*   peer_counts; /* int32 [world][E] on every rank (scratch, written by all ranks) */
+  void* const*   peer_flags;  /* int32 [world] on every rank, zero before the first call */
+  int32_t* my_base;           /* [E] out: first row, in the owning rank's buffer, of this rank's rows of expert e */
+  int32_t* cursor;            /* [E] out: zeroed */
+  int32_t* m_indices;         /* [m_cap] out: m_indices of the buffer this rank receives into */
+  int32_t* m_total;           /* [1] out: rows in use in it */
+  int32_t* status;            /* NULL, or int32[DG_STATUS_WORDS] */
+} dg_ep_plan_args;
+
+/* Counts this rank's routed pairs per expert, exchanges the counts with every rank and derives
+ * the layout of all receive buffers (one small kernel per rank; waits for every peer's counts). */
+DG_API int dg_ep_plan(const dg_ep_plan_args* args, void* stream);
+
+typedef struct dg_ep_push_args {
+  int32_t world;              /* ranks, 1..DG_EP_MAX_WORLD */
+  int32_t rank;               /* this rank */
+  int32_t num_experts;
+  int32_t num_tokens;         /* T */
+  int32_t top_k;              /* <= 32 */
+  int32_t row_bytes;          /* bytes per quantised row, multiple of 16, <= DG_MAX_QUANT_HIDDEN */
+  int32_t m_cap;
+  int32_t reserved;
+  const void*    rows;        /* [T][row_bytes] this rank's tokens, quantised once per token */
+  const float*   row_scale;   /* [T] */
+  const int32_t* topk_ids;    /* [T][top_k] */
+  const int32_t* my_base;     /* [E] from dg_ep_plan */
+  int32_t*       cursor;      /* [E] from dg_ep_plan */
+  void* const*   peer_a;      /* [m_cap][row_bytes] receive buffer of every rank */
+  void* const*   peer_scale;  /* float [m_cap] of every rank */
+  void* const*   peer_tag;    /* int32 [m_cap] of every rank: rank << 24 | (token * top_k + slot) */
+  int32_t*       pair_dest;   /* NULL, or [T][top_k] out: row each pair was written to, -1 = dropped */
+  int32_t*       status;      /* DG_DEV_BAD_GROUP_INDEX when a pair did not fit (m_cap) and was dropped */
+} dg_ep_push_args;
+
+/* Writes every routed row of this rank into the owning rank's receive buffer (the grouped,
+ * padded A operand of that rank's dg_contig_gemm), with its scale and its return tag.  The rows
+ * of one expert from one source rank are contiguous; their order within that range is not
+ * fixed, which no result depends on (every output row is a function of its own row only). */
+DG_API int dg_ep_push(const dg_ep_push_args* args, void* stream);
+
+typedef struct dg_ep_barrier_args {
+  int32_t world;              /* ranks, 1..DG_EP_MAX_WORLD */
+  int32_t rank;               /* this rank */
+  int32_t epoch;
+  int32_t phases;             /* as in dg_ep_plan_args */
+  void* const* peer_flags;
+  int32_t*     status;
+} dg_ep_barrier_args;
+
+/* All stores this rank enqueued before the call are visible to every rank that has passed its
+ * own call with the same epoch (system-scope fence, signal, bounded wait; one tiny kernel). */
+DG_API int dg_ep_barrier(const dg_ep_barrier_args* args, void* stream);
 
 /* dg_query() selectors. */
 #define DG_QUERY_ABI_VERSION   0

@@ -4,6 +4,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 import deepgemm
 from deepgemm import _cabi
 
@@ -27,16 +29,18 @@ def test_header_functions_are_exported():
 
 def test_struct_layouts_match_header_field_order():
     text = open(HEADER).read()
-    for struct, cls in (("dg_masked_args", _cabi.MaskedArgs), ("dg_contig_args", _cabi.ContigArgs)):
+    for struct, cls in (("dg_masked_args", _cabi.MaskedArgs), ("dg_contig_args", _cabi.ContigArgs),
+                        ("dg_ep_plan_args", _cabi.EpPlanArgs), ("dg_ep_push_args", _cabi.EpPushArgs),
+                        ("dg_ep_barrier_args", _cabi.EpBarrierArgs)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = re.findall(r"(\w+)\s*;", body)
         assert fields == [f[0] for f in cls._fields_], (struct, fields)
-    assert ctypes.sizeof(_cabi.MaskedArgs) == 96 and ctypes.sizeof(_cabi.ContigArgs) == 96
+    assert ctypes.sizeof(_cabi.MaskedArgs) == 96 and ctypes.sizeof(_cabi.ContigArgs) == 120
 
 
 def test_query_and_strerror_without_a_device():
-    assert _cabi.query(_cabi.QUERY_ABI_VERSION) == 1
+    assert _cabi.query(_cabi.QUERY_ABI_VERSION) == 2
     assert _cabi.lib.dg_strerror(0) == b"ok"
     assert b"16-byte" in _cabi.lib.dg_strerror(-4)
     assert _cabi.lib.dg_strerror(12345) == b"unknown status code"
@@ -60,6 +64,18 @@ def test_calls_validate_before_touching_the_device():
     assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -1      # null pointers
     c = _cabi.ContigArgs(kind=_cabi.KIND_E4M3, scale_mode=0, num_groups=1, m_total=1 << 22, n=64, k=128)
     assert _cabi.lib.dg_contig_gemm(ctypes.byref(c), None) == -8
+    c = _cabi.ContigArgs(kind=_cabi.KIND_E4M3, scale_mode=0, num_groups=1, m_total=128, n=64, k=128,
+                         scatter_tag=16, scatter_world=2)
+    assert _cabi.lib.dg_contig_gemm(ctypes.byref(c), None) == -1      # scatter buffers missing
+    assert _cabi.lib.dg_ep_plan(None, None) == -1
+    e = _cabi.EpPlanArgs(world=4, rank=4, num_experts=16, align=256, m_cap=1024)
+    assert _cabi.lib.dg_ep_plan(ctypes.byref(e), None) == -9          # rank outside the world
+    e = _cabi.EpPlanArgs(world=4, rank=0, num_experts=18, align=256, m_cap=1024)
+    assert _cabi.lib.dg_ep_plan(ctypes.byref(e), None) == -3          # experts not a multiple of ranks
+    u = _cabi.EpPushArgs(world=2, rank=0, num_experts=16, num_tokens=8, top_k=2, row_bytes=100, m_cap=256)
+    assert _cabi.lib.dg_ep_push(ctypes.byref(u), None) == -3          # rows must be whole 16-byte chunks
+    u = _cabi.EpPushArgs(world=2, rank=0, num_experts=16, num_tokens=8, top_k=2, row_bytes=128, m_cap=256)
+    assert _cabi.lib.dg_ep_push(ctypes.byref(u), None) == -1          # null pointers
     assert _cabi.lib.dg_pack_weight(0, None, None, 1, 16, 128, 0, None) == -1
     assert _cabi.lib.dg_pack_weight(7, 16, 32, 1, 16, 128, 0, None) == -2
     assert _cabi.lib.dg_pack_weight(0, 16, 32, 1, 16, 100, 0, None) == -3
@@ -70,7 +86,6 @@ def test_calls_validate_before_touching_the_device():
 
 def test_missing_library_is_a_loud_import_error(tmp_path, monkeypatch):
     import importlib
-    import pytest
     monkeypatch.setenv("DEEP_GEMM_LIB_PATH", str(tmp_path / "nope.so"))
     spec = importlib.util.spec_from_file_location("cabi_probe", _cabi.__file__)
     mod = importlib.util.module_from_spec(spec)
@@ -89,6 +104,7 @@ def test_header_is_valid_c99_and_cxx(tmp_path):
         "int use(void) {\n"
         "  dg_masked_args m; dg_contig_args c; dg_compact_args p; dg_dense_args d; dg_quant_group_args q;\n"
         "  dg_group_sorted_args s; dg_act_quant_args a; dg_combine_args b;\n"
+        "  dg_ep_plan_args e1; dg_ep_push_args e2; dg_ep_barrier_args e3; (void)e1; (void)e2; (void)e3;\n"
         "  (void)m; (void)c; (void)p; (void)d; (void)q; (void)s; (void)a; (void)b;\n"
         "  return (int)sizeof(dg_masked_args) + DG_STATUS_WORDS + DG_ABI_VERSION;\n"
         "}\n")
