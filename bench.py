@@ -205,45 +205,84 @@ def time_launches(fn, steps: int, warmup: int, barrier=None):
 
 
 # ----------------------------------------------------------------------------- extra configurations
-def make_contig_int8_prefill(device, small=False):
-    """Contiguous INT8 prefill: 32 experts, K=7168, N=4096, 4096 tokens top-8, groups padded to
-    256 (small: 8 experts, 1024 tokens).  Returns (launch function, info)."""
+def make_contig_prefill(device, small=False, kind="int8"):
+    """Contiguous INT8 / FP8 prefill: 32 experts, K=7168, N=4096, 4096 tokens top-8, groups padded
+    to 256 (small: 8 experts, 1024 tokens).  Returns (launch function, info)."""
     import deepgemm
-    from deepgemm.quant_utils import contiguous_layout, per_token_quant_int8
+    from deepgemm.quant_utils import contiguous_layout, per_token_quant_fp8, per_token_quant_int8
+    quant = per_token_quant_int8 if kind == "int8" else per_token_quant_fp8
+    wdtype = torch.int8 if kind == "int8" else torch.float8_e4m3fn
     G, K, N, tokens = (8, 7168, 4096, 1024) if small else (32, 7168, 4096, 4096)
     cpu_gen = torch.Generator().manual_seed(3)
     picks = torch.rand(tokens, G, generator=cpu_gen).topk(8, dim=1).indices
     rows = torch.bincount(picks.flatten(), minlength=G)
     m_indices, _, m_total = contiguous_layout(rows.tolist(), 256, device)
     gen = torch.Generator(device=device).manual_seed(3)
-    a, a_s = per_token_quant_int8(torch.randn(m_total, K, device=device, generator=gen))
-    b = torch.empty(G, N, K, dtype=torch.int8, device=device)
+    a, a_s = quant(torch.randn(m_total, K, device=device, generator=gen))
+    b = torch.empty(G, N, K, dtype=wdtype, device=device)
     b_s = torch.empty(G, N, dtype=torch.float32, device=device)
     for g in range(G):
-        q, s = per_token_quant_int8(torch.randn(N, K, device=device, generator=gen))
+        q, s = quant(torch.randn(N, K, device=device, generator=gen))
         b[g], b_s[g] = q, s.reshape(N)
-    bp = deepgemm.marlin_i8_contiguous_weight(b)
     out = torch.zeros(m_total, N, dtype=torch.bfloat16, device=device)
     a_s = a_s.reshape(m_total).contiguous()
-    fn = lambda: deepgemm.m_grouped_i8_gemm_nt_contiguous((a, a_s), (bp, b_s), out, m_indices)
+    if kind == "int8":
+        bp = deepgemm.marlin_i8_contiguous_weight(b)
+        fn = lambda: deepgemm.m_grouped_i8_gemm_nt_contiguous((a, a_s), (bp, b_s), out, m_indices)
+    else:
+        bp = deepgemm.marlin_fp8_contiguous_weight(b)
+        fn = lambda: deepgemm.m_grouped_fp8_gemm_nt_contiguous((a, a_s), (bp, b_s), out, m_indices)
     v = int(rows.sum())
-    info = {"workload": "contiguous_int8_prefill G=%d K=%d N=%d V=%d M_total=%d" % (G, K, N, v, m_total),
+    info = {"workload": "contiguous_%s_prefill G=%d K=%d N=%d V=%d M_total=%d" % (kind, G, K, N, v, m_total),
             "ops": 2.0 * v * N * K,
             "bytes": algorithmic_bytes(v, int((rows > 0).sum()), G, N, K, 1, 1, index_entries=m_total)}
     return fn, info
 
 
-def bench_contig_int8_prefill(device, steps, warmup, peaks):
-    fn, info = make_contig_int8_prefill(device)
+def measure_dense_8bit_peak(device, kind="int8", size=8192, reps=10):
+    """Dense 8-bit tensor throughput of this GPU, measured with this library's own dense GEMM
+    (dg_dense_gemm, two-CTA 256x256 tiles) at size^3, best of `reps` single launches: the
+    denominator for the prefill fractions beside 2 x the measured bf16 cuBLAS figure (no 8-bit
+    figure is measured by anyone else)."""
+    from deepgemm.gemm import fp8_gemm
+    dt = torch.int8 if kind == "int8" else torch.float8_e4m3fn
+    if kind == "int8":
+        a = torch.randint(-127, 128, (size, size), dtype=torch.int8, device=device)
+        b = torch.randint(-127, 128, (size, size), dtype=torch.int8, device=device)
+    else:
+        a = torch.randn(size, size, device=device).to(dt)
+        b = torch.randn(size, size, device=device).to(dt)
+    ones = torch.ones(size, dtype=torch.float32, device=device)
+    d = torch.empty(size, size, dtype=torch.bfloat16, device=device)
+    for _ in range(3):
+        fp8_gemm((a, ones), (b, ones), d)
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fp8_gemm((a, ones), (b, ones), d)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return 2.0 * size ** 3 / (best * 1e-3) / 1e12
+
+
+def bench_contig_prefill(device, steps, warmup, peaks, kind="int8"):
+    fn, info = make_contig_prefill(device, kind=kind)
     sampler = ClockSampler(device.index or 0, period_s=0.002)
     sampler.start()
     ms, t0, t1 = time_launches(fn, steps, warmup)
     sampler.stop()
     tops = info["ops"] * steps / (ms * 1e-3) / 1e12
     peak = 2.0 * peaks["bf16_tflops"]
+    own = measure_dense_8bit_peak(device, kind)
     return {"workload": info["workload"], "ms": ms / steps, "tops": tops, "peak_tops": peak,
-            "peak_note": "2 x %s dense bf16 cuBLAS burst TFLOP/s (8-bit tcgen05 rate is twice bf16)" % peaks["source"],
-            "frac_of_tensor_peak": tops / peak, "clocks": sampler.summary(t0, t1)}
+            "peak_note": "2 x %s dense bf16 cuBLAS burst TFLOP/s (8-bit tcgen05 rate is twice bf16; "
+                         "no 8-bit peak is measured by the driver)" % peaks["source"],
+            "frac_of_tensor_peak": tops / peak,
+            "own_dense_8bit_tops": own, "own_dense_note": "this library's dense GEMM, 8192^3, best of 10 launches",
+            "frac_of_own_dense_8bit": tops / own, "clocks": sampler.summary(t0, t1)}
 
 
 def make_masked_w4a8(device, small=False):
@@ -281,11 +320,189 @@ def bench_masked_w4a8(device, steps, warmup, peaks):
             "tops": info["ops"] / sec / 1e12}
 
 
-def bench_ep_prefill(device, rank, world, steps, warmup, peaks):
-    """Expert-parallel FP8 contiguous gate/up: 256 experts sharded over the ranks, 4096 tokens
-    per rank routed top-8, NCCL all-to-all dispatch timed apart from the GEMM."""
-    from deepgemm import expert_parallel as ep
-    return ep.benchmark_ep_prefill(device, rank, world, steps=steps, warmup=warmup, peaks=peaks)
+EP = dict(experts=256, K=7168, N=4096, tokens=4096, top_k=8)
+
+
+def _ep_expert_weights(e, device, cfg=EP):
+    """Weights of global expert e, a function of e alone, so that any rank can rebuild any expert
+    for the parity check: (gate|up e4m3 [N, K], scale [N], down e4m3 [K, N/2], scale [K])."""
+    from deepgemm.quant_utils import per_token_quant_fp8
+    g = torch.Generator(device=device).manual_seed(1000 + e)
+    w13, s13 = per_token_quant_fp8(torch.randn(cfg["N"], cfg["K"], device=device, generator=g) * 0.02)
+    w2, s2 = per_token_quant_fp8(torch.randn(cfg["K"], cfg["N"] // 2, device=device, generator=g) * 0.02)
+    return w13, s13.reshape(-1), w2, s2.reshape(-1)
+
+
+def _ep_tokens(rank, device, cfg=EP):
+    gen = torch.Generator(device=device).manual_seed(100 + rank)
+    shared = torch.Generator().manual_seed(7)                     # same expert bias on every rank
+    bias = (torch.randn(cfg["experts"], generator=shared) * 0.5).to(device)
+    hidden = torch.randn(cfg["tokens"], cfg["K"], device=device, generator=gen).to(torch.bfloat16)
+    logits = torch.randn(cfg["tokens"], cfg["experts"], device=device, generator=gen) + bias
+    topk = logits.topk(cfg["top_k"], dim=1).indices.to(torch.int32).contiguous()
+    weights = torch.softmax(torch.randn(cfg["tokens"], cfg["top_k"], device=device, generator=gen), dim=1)
+    return hidden, topk, weights
+
+
+def _ep_parity(out, hidden, topk, weights, device, cfg=EP, sample=6):
+    """On-box check of the layer's result for a sample of this rank's tokens: (a) against the
+    oracle's formulas (torch fp32 dequant-matmul, calc_diff < 1e-3), (b) bit for bit against the
+    one-GPU layer of this library run on the same tokens with the experts they use."""
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import dg_oracle as O
+    import deepgemm
+    from deepgemm.moe_chain import moe_forward
+    idx = torch.linspace(0, cfg["tokens"] - 1, sample).long().to(device)
+    ids = topk[idx].long()
+    used = ids.flatten().unique()
+    remap = torch.full((cfg["experts"],), -1, dtype=torch.long, device=device)
+    remap[used] = torch.arange(used.numel(), device=device)
+    ws = [_ep_expert_weights(int(e), device, cfg) for e in used.tolist()]
+    w13 = torch.stack([w[0] for w in ws]); s13 = torch.stack([w[1] for w in ws])
+    w2 = torch.stack([w[2] for w in ws]); s2 = torch.stack([w[3] for w in ws])
+    local_ids = remap[ids].to(torch.int32).contiguous()
+    pk = deepgemm.marlin_fp8_contiguous_weight
+    one_gpu = moe_forward(hidden[idx].contiguous(), local_ids, weights[idx].contiguous(),
+                          (pk(w13.clone()), s13), (pk(w2.clone()), s2))
+    got = out[idx]
+    bit_equal = bool(torch.equal(got.view(torch.int16), one_gpu.view(torch.int16)))
+    ref = O.ref_moe_layer(hidden[idx].cpu(), local_ids.cpu().long(), weights[idx].cpu(), w13.cpu(), s13.cpu(),
+                          w2.cpu(), s2.cpu())
+    diff = float(O.calc_diff(got.cpu().double(), ref.double()))
+    return {"sample_tokens": sample, "calc_diff_vs_oracle": diff, "bit_equal_one_gpu_layer": bit_equal,
+            "ok": bool(bit_equal and diff < 1e-3)}
+
+
+def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
+    """Expert-parallel FP8 MoE layer: 256 experts sharded over the ranks, 4096 tokens per rank routed
+    top-8 (mildly skewed).  Reports the contiguous FP8 gate/up GEMM and the NCCL all-to-all dispatch
+    separately (max over ranks), then the whole layer through the peer-memory exchange
+    (deepgemm.ep_exchange) as one timed step with its phases, and a parity flag computed here."""
+    import deepgemm
+    from deepgemm import _cabi, ep_exchange as epx, expert_parallel as ep
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+    E, K, N, T, top_k = cfg["experts"], cfg["K"], cfg["N"], cfg["tokens"], cfg["top_k"]
+    e_local, inter = E // world, N // 2
+    hidden, topk, weights = _ep_tokens(rank, device, cfg)
+    w13 = torch.empty(e_local, N, K, dtype=torch.float8_e4m3fn, device=device)
+    s13 = torch.empty(e_local, N, dtype=torch.float32, device=device)
+    w2 = torch.empty(e_local, K, inter, dtype=torch.float8_e4m3fn, device=device)
+    s2 = torch.empty(e_local, K, dtype=torch.float32, device=device)
+    for el in range(e_local):
+        w13[el], s13[el], w2[el], s2[el] = _ep_expert_weights(rank * e_local + el, device, cfg)
+    w13p = (deepgemm.marlin_fp8_contiguous_weight(w13), s13)
+    w2p = (deepgemm.marlin_fp8_contiguous_weight(w2), s2)
+    m_cap = 2 * T * top_k + e_local * 256
+    x = epx.EPExchange(rank, world, E, K, N, K, T, top_k, m_cap, device)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def sync():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n=steps, w=warmup):
+        for _ in range(w):
+            fn()
+        sync()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        sync()
+        return e0.elapsed_time(e1) / n
+
+    # ---- the whole layer, one timed step (every launch of forward() between the two events)
+    out = torch.empty(T, K, dtype=torch.bfloat16, device=device)
+    layer_ms = timed(lambda: x.forward(hidden, topk, weights, w13p, w2p, out=out))
+    x.check_status()
+    parity = _ep_parity(out, hidden, topk, weights, device, cfg)
+
+    # ---- its phases, each timed on its own (a barrier closes every phase that writes to peers)
+    q, q_scale = x.quantise(hidden)
+    quant_ms = timed(lambda: x.quantise(hidden))
+    plan_ms = timed(lambda: x.plan(topk))
+
+    def push():
+        x.plan(topk)          # hands out the rows again
+        x.push(q, q_scale, topk)
+        x.barrier()
+    push_ms = timed(push) - plan_ms
+    kind = _cabi.KIND_E4M3
+    from deepgemm import _core
+    from deepgemm.moe_chain import silu_mul_quant
+    g13 = lambda: _core.grouped_gemm_contiguous(kind, 0, x.recv_a, w13p[0], x.h13, x.recv_scale, w13p[1], x.m_indices)
+    gemm_ms = timed(g13)
+    act_ms = timed(lambda: silu_mul_quant(x.h13, kind="fp8", m_indices=x.m_indices, out=(x.act_q, x.act_scale)))
+
+    def down_scatter():
+        _core.grouped_gemm_contiguous(kind, 0, x.act_q, w2p[0], x.y_back, x.act_scale, w2p[1], x.m_indices,
+                                      scatter=(x.recv_tag, x._peer["y_back"], world))
+        x.barrier()
+    down_ms = timed(down_scatter)
+    y_local = torch.empty((x.m_cap, K), dtype=torch.bfloat16, device=device)
+    down_local_ms = timed(lambda: _core.grouped_gemm_contiguous(kind, 0, x.act_q, w2p[0], y_local, x.act_scale,
+                                                                w2p[1], x.m_indices))
+    del y_local
+    combine_ms = timed(lambda: x.combine(weights, out=out))
+    x.check_status()
+
+    # ---- the NCCL all-to-all dispatch of the bf16 rows, as the configuration words it
+    plan = ep.build_dispatch_plan(topk.long(), E, world)
+    a2a_ms = timed(lambda: ep.dispatch_tokens(hidden, plan, E, rank, world)) if world > 1 else 0.0
+
+    valid = int((x.m_indices >= 0).sum())
+    m_total = int(x.m_total)
+    remote_pairs = int((torch.div(topk.long(), e_local, rounding_mode="floor") != rank).sum())
+    vals = torch.tensor([layer_ms, quant_ms, plan_ms, push_ms, gemm_ms, act_ms, down_ms, down_local_ms,
+                         combine_ms, a2a_ms], device=device, dtype=torch.float64)
+    sums = torch.tensor([2.0 * valid * N * K, 2.0 * valid * K * inter, 1.0 if parity["ok"] else 0.0],
+                        device=device, dtype=torch.float64)
+    mx = torch.tensor([float(remote_pairs)], device=device, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    (layer_ms, quant_ms, plan_ms, push_ms, gemm_ms, act_ms, down_ms, down_local_ms, combine_ms,
+     a2a_ms) = (float(v) for v in vals.tolist())
+    flops13, flops2, ok_ranks = (float(v) for v in sums.tolist())
+    tflops = flops13 / (gemm_ms * 1e-3) / 1e12
+    res = {"workload": "ep_fp8_moe_layer experts=%d K=%d N=%d tokens/rank=%d top%d" % (E, K, N, T, top_k),
+           "world": world, "all figures": "max over ranks, CUDA events",
+           "gemm_ms_max_over_ranks": gemm_ms, "gemm_tflops_aggregate": tflops,
+           "gemm_tflops_per_gpu": tflops / world,
+           "all_to_all_ms_max_over_ranks": a2a_ms,
+           "all_to_all_note": "NCCL all_to_all_single of the routed bf16 rows (counts first), as the "
+                              "configuration states; the layer below does not use it",
+           "valid_rows_this_rank": valid, "m_total_this_rank": m_total,
+           "parity": "ok" if ok_ranks == world else "FAILED", "parity_rank0": parity,
+           "layer_ms": layer_ms,
+           "layer": {"exchange": "peer-memory stores (dg_ep_plan / dg_ep_push / dg_ep_barrier), result rows "
+                                 "scattered home by the down GEMM's epilogue; no host synchronisation",
+                     "quantise_tokens_ms": quant_ms, "plan_counts_exchange_ms": plan_ms,
+                     "push_rows_and_barrier_ms": push_ms,
+                     "push_remote_gbs_max_rank": float(mx) * (K + 8) / (push_ms * 1e-3) / 1e9 if world > 1 else None,
+                     "gate_up_gemm_ms": gemm_ms, "silu_mul_quant_ms": act_ms,
+                     "down_gemm_scatter_and_barrier_ms": down_ms, "down_gemm_local_store_ms": down_local_ms,
+                     "down_gemm_tflops_aggregate": flops2 / (down_ms * 1e-3) / 1e12,
+                     "return_remote_gbs_max_rank": float(mx) * K * 2 / (down_ms * 1e-3) / 1e9 if world > 1 else None,
+                     "combine_ms": combine_ms,
+                     "exposed_exchange_ms": plan_ms + push_ms + max(0.0, down_ms - down_local_ms),
+                     "gemm_ms_sum": gemm_ms + down_local_ms,
+                     "layer_over_gemms": layer_ms / (gemm_ms + down_local_ms)}}
+    if peaks:
+        weight_bytes = e_local * N * K
+        t_hbm = (weight_bytes + valid * K + valid * N * 2) / (peaks["hbm_gbs"] * 1e9)
+        t_tc = 2.0 * valid * N * K / (2.0 * peaks["bf16_tflops"] * 1e12)
+        res["gemm_roofline_ms"] = max(t_hbm, t_tc) * 1e3
+        res["gemm_bound"] = "hbm" if t_hbm > t_tc else "tensor"
+        res["gemm_frac_of_roofline"] = max(t_hbm, t_tc) * 1e3 / gemm_ms
+    return res
 
 
 # ----------------------------------------------------------------------------- CPU arm
@@ -349,7 +566,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced problem (8 experts) for profiler captures")
     ap.add_argument("--profile", action="store_true",
                     help="profiler run: one workload's timed region only, bracketed by cudaProfilerStart/Stop")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_int8", "w4a8"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_int8", "prefill_fp8", "w4a8"],
                     help="with --profile: which configuration to run (the JSON line is always decode)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -394,8 +611,10 @@ def main():
     peaks = _peaks()
 
     if args.profile and args.workload != "decode":
-        fn, info = (make_contig_int8_prefill if args.workload == "prefill_int8" else make_masked_w4a8)(
-            device, args.small)
+        if args.workload == "w4a8":
+            fn, info = make_masked_w4a8(device, args.small)
+        else:
+            fn, info = make_contig_prefill(device, args.small, "int8" if args.workload == "prefill_int8" else "fp8")
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
@@ -581,7 +800,8 @@ def main():
                 extras["masked_fp8_decode_tensor_wise"] = {"ms": ms_t / 200, "gbs": gb,
                                                            "frac_of_hbm_peak": gb / peaks["hbm_gbs"]}
                 del wt
-                extras["contiguous_int8_prefill"] = bench_contig_int8_prefill(device, 20, 3, peaks)
+                extras["contiguous_int8_prefill"] = bench_contig_prefill(device, 20, 3, peaks, "int8")
+                extras["contiguous_fp8_prefill"] = bench_contig_prefill(device, 20, 3, peaks, "fp8")
                 extras["masked_w4a8"] = bench_masked_w4a8(device, 200, 10, peaks)
             del w
             torch.cuda.empty_cache()

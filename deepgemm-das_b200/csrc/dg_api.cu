@@ -305,6 +305,7 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.debug_acc = static_cast<uint32_t*>(pr.debug_acc);
   p.status = pr.status;
   p.b_rowmajor = pr.dense;
+  p.out_kind = pr.out_kind;
   p.scatter_tag = pr.scatter_tag;
   for (int r = 0; r < pr.scatter_world && pr.scatter_tag != nullptr; ++r) p.scatter_base[r] = pr.scatter_base[r];
 
@@ -393,6 +394,7 @@ int launch_w4(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.M = pr.M;
   p.N = pr.N;
   p.K = pr.K;
+  p.out_kind = pr.out_kind;
   p.kblocks = pr.K / 256;  // packed-weight stages per item (two 128-value K blocks each)
   p.n_tiles = (pr.N + 127) / 128;
   p.m_blocks = (pr.M + kBM - 1) / kBM;
@@ -576,8 +578,9 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
   if (pr.scale_mode != DG_SCALE_NONE && (!pr.a_scale || !pr.b_scale)) return DG_ERR_NULL_POINTER;
   if (!aligned16(pr.a) || !aligned16(pr.b) || !aligned16(pr.d)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.scale_mode == DG_SCALE_PER_CHANNEL && !aligned16(pr.b_scale)) return DG_ERR_BAD_ALIGNMENT;
-  // fp16 / fp32 output and rows of D that start unaligned exist only in the one-CTA kernel
-  const bool scalar_out = pr.out_kind != DG_OUT_BF16 || (pr.N % 8) != 0;
+  // fp32 output and rows of D that start unaligned exist only in the one-CTA kernel
+  const bool scalar_out = pr.out_kind == DG_OUT_F32 || (pr.N % 8) != 0;
+  if (!pr.dense && pr.out_kind == DG_OUT_F32) return DG_ERR_BAD_ARGUMENT;  // grouped outputs are 16-bit
   if (pr.debug_acc && !aligned16(pr.debug_acc)) return DG_ERR_BAD_ALIGNMENT;
   if (pr.block_n != 0 && pr.block_n != 32 && pr.block_n != 64 && pr.block_n != 128 &&
       pr.block_n != 256 && pr.block_n != 512)
@@ -677,6 +680,7 @@ int dg_masked_gemm(const dg_masked_args* a, void* stream) {
   pr.expected_m = a->expected_m;
   pr.debug_acc = a->debug_acc;
   pr.status = a->status;
+  pr.out_kind = a->out_kind;
   return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
 }
 
@@ -751,10 +755,12 @@ int dg_contig_gemm(const dg_contig_args* a, void* stream) {
   pr.expected_m = 0;
   pr.debug_acc = a->debug_acc;
   pr.status = a->status;
+  pr.out_kind = a->out_kind;
   if (a->scatter_tag != nullptr) {
     if (a->scatter_base == nullptr) return DG_ERR_NULL_POINTER;
     if (a->scatter_world < 1 || a->scatter_world > DG_EP_MAX_WORLD) return DG_ERR_BAD_ARGUMENT;
-    if (a->kind == DG_KIND_W4A8 || a->n % 8 != 0 || a->debug_acc != nullptr) return DG_ERR_BAD_ARGUMENT;
+    if (a->kind == DG_KIND_W4A8 || a->n % 8 != 0 || a->debug_acc != nullptr || a->out_kind != DG_OUT_BF16)
+      return DG_ERR_BAD_ARGUMENT;
     for (int r = 0; r < a->scatter_world; ++r)
       if (a->scatter_base[r] == nullptr || !aligned16(a->scatter_base[r])) return DG_ERR_BAD_ALIGNMENT;
     pr.scatter_tag = a->scatter_tag;
@@ -833,7 +839,7 @@ static int quant_group_common(const dg_quant_group_args* a, int32_t* scratch, vo
   p.kind = a->kind;
   p.hist = scratch;
   p.starts = scratch + static_cast<size_t>(p.chunks) * p.G;
-  cudaError_t e = dg::launch_quant_group(p, static_cast<cudaStream_t>(stream));
+  cudaError_t e = dg::launch_quant_group(p, dev->sm_count, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(a->num_rows > 0 ? 4 : 1, std::memory_order_relaxed);
   return DG_OK;
@@ -884,7 +890,10 @@ int dg_group_sorted_rows(const dg_group_sorted_args* a, void* stream) {
   p.kind = DG_KIND_I8;
   p.hist = static_cast<int32_t*>(a->scratch);
   p.starts = p.hist + static_cast<size_t>(p.chunks) * p.G;
-  cudaError_t e = dg::launch_quant_group(p, static_cast<cudaStream_t>(stream));
+  const DeviceInfo* dev = nullptr;
+  const int rc = device_info(&dev);
+  if (rc != DG_OK) return rc;
+  cudaError_t e = dg::launch_quant_group(p, dev->sm_count, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(a->num_sorted > 0 ? 4 : 1, std::memory_order_relaxed);
   return DG_OK;

@@ -148,6 +148,7 @@ struct EpiRow {
   const float* bs_row;   // the tile's weight scales (PER_CHANNEL), staged in shared memory
   __nv_bfloat16* d_row;  // &D[row][n0]
   uint32_t* dbg_row;     // &debug_acc[row][n0] or nullptr
+  bool f16 = false;      // 16-bit outputs are fp16 instead of bf16 (warp-uniform)
 };
 
 // Scales and converts 8 accumulator columns (j .. j+7 of the chunk that starts at column
@@ -176,6 +177,18 @@ __device__ __forceinline__ uint4 epilogue_pack8(const uint32_t (&r)[32], int j, 
     for (int i = 0; i < 8; ++i) v[i] = (v[i] * e.as) * e.bs_g;
   }
   uint4 o;
+  if (e.f16) {
+    __half2 h;
+    h = __floats2half2_rn(v[0], v[1]);
+    o.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(v[2], v[3]);
+    o.y = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(v[4], v[5]);
+    o.z = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(v[6], v[7]);
+    o.w = *reinterpret_cast<uint32_t*>(&h);
+    return o;
+  }
   __nv_bfloat162 h;
   h = __floats2bfloat162_rn(v[0], v[1]);
   o.x = *reinterpret_cast<uint32_t*>(&h);
@@ -260,7 +273,7 @@ __device__ __forceinline__ void weight_coords(const KernelParams& p, int g, int 
   }
 }
 
-// Slow twin of epilogue_store32 for what the grouped entry points never produce: fp16 / fp32
+// Slow twin of epilogue_store32 for what the grouped entry points never produce: fp32
 // output or an N that is not a multiple of 8 (rows of D then start at unaligned addresses).
 // Same arithmetic, one scalar store per element.
 template <bool kIntAcc>
@@ -696,7 +709,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (rv && p.scale_mode != DG_SCALE_NONE) row.as = p.a_scale[grow];
         if (p.scale_mode == DG_SCALE_TENSOR_WISE) row.bs_g = p.b_scale[t.g];
       }
-      if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
+      if (!mbar_wait_warp(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
       if (warp_has_rows) {
         row.bs_row = bs_s;  // PER_CHANNEL only
@@ -710,7 +723,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                       (size_t)(tag & 0xFFFFFF) * p.N + t.n0;
         }
         row.dbg_row = p.debug_acc ? p.debug_acc + grow * p.N + t.n0 : nullptr;
-        const bool scalar_out = p.out_kind != 0 || (p.N & 7) != 0;
+        row.f16 = p.out_kind == 1;
+        const bool scalar_out = p.out_kind == 2 || (p.N & 7) != 0;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
         const int cols_left0 = p.N - t.n0;
         EpiWarp ew;

@@ -377,10 +377,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (rv && p.scale_mode != DG_SCALE_NONE) row.as = p.a_scale[grow];
         if (p.scale_mode == DG_SCALE_TENSOR_WISE) row.bs_g = p.b_scale[t.g];
       }
-      if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
+      if (!mbar_wait_warp(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
       if (warp_has_rows) {
         row.bs_row = bs_s;
+        row.f16 = p.out_kind == 1;
         row.d_row = p.d + grow * p.N + t.n0;
         const bool scatter = p.mode == MODE_CONTIG && p.scatter_tag != nullptr;
         if (scatter && rv) {

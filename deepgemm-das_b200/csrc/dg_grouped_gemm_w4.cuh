@@ -390,7 +390,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
         }
         tok_mask[c] = __ballot_sync(0xffffffffu, okl);
       }
-      if (!mbar_wait_bounded(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
+      if (!mbar_wait_warp(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kW4AccCols;
       // 16 tokens per step.  A lane holds one channel of 16 tokens, but D is token-major, so the
@@ -415,7 +415,10 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
         for (int j = 0; j < 16; ++j) {
           const float as_j = __shfl_sync(0xffffffffu, as_w, (c & 1) * 16 + j);
           const float v = (__int2float_rn(static_cast<int>(r[j])) * as_j) * bs;
-          strip[j * 32 + lane] = __float2bfloat16_rn(v);
+          if (p.out_kind == 1)  // fp16 output: same 16-bit slots
+            reinterpret_cast<__half*>(strip)[j * 32 + lane] = __float2half_rn(v);
+          else
+            strip[j * 32 + lane] = __float2bfloat16_rn(v);
         }
         if (p.debug_acc != nullptr && chan_ok) {  // raw accumulators (tests only): direct stores
           uint32_t* dbg_col = p.debug_acc + (row_base + c * 16) * p.N + chan;
@@ -453,7 +456,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (it % kW4Groups != group) continue;
         const int ws = it % WS;
         const uint32_t wph = (it / WS) & 1u;
-        if (!mbar_wait_bounded(bar_wfull(ws), wph, abort_flag, SITE_UNPACK_FULL)) {
+        if (!mbar_wait_warp(bar_wfull(ws), wph, abort_flag, SITE_UNPACK_FULL)) {
           ok = false;
           break;
         }
@@ -481,7 +484,7 @@ grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (lane == 0) mbar_arrive(bar_wempty(ws));
         const int s = it % RS;
         const uint32_t ph = (it / RS) & 1u;
-        if (!mbar_wait_bounded(bar_cons(s), ph ^ 1u, abort_flag, SITE_W4_SLOT_EMPTY)) {
+        if (!mbar_wait_warp(bar_cons(s), ph ^ 1u, abort_flag, SITE_W4_SLOT_EMPTY)) {
           ok = false;
           break;
         }

@@ -95,14 +95,6 @@ struct WsSmem {
   }
 };
 
-// All lanes of a warp wait; the result is the same in every lane (a lane that gave up makes the
-// whole warp give up), so that warp-wide instructions after it never run on part of a warp.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                               int site) {
-  const bool ok = mbar_wait_bounded(bar, parity, abort_flag, site);
-  return __all_sync(0xffffffffu, ok);
-}
-
 template <int SLOTS, int TOKS, int NG>
 __global__ void __launch_bounds__(WsSmem<SLOTS, TOKS>::kThreads, 1)
 grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
@@ -477,6 +469,7 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
       tc_fence_after_sync();
       if (warp_has_rows) {
         row.bs_row = bs_s;
+        row.f16 = p.out_kind == 1;
         const size_t d_off = grow * p.N + t.n0;
         row.d_row = p.d + d_off;
         row.dbg_row = p.debug_acc ? p.debug_acc + d_off : nullptr;
@@ -489,7 +482,7 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
         ew.rv_mask = __ballot_sync(0xffffffffu, rv);
         ew.lane = lane;
         epilogue_drain<true>(t_row, min(t.width / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
-                             cols_left0, (p.N & 7) != 0 || p.out_kind != 0, p.out_kind);
+                             cols_left0, (p.N & 7) != 0, p.out_kind);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -72,6 +72,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// The same wait for a whole warp: every lane waits, and the result is made the same in all lanes
+// (a lane that gave up makes the warp give up), so that the warp-wide instructions that follow a
+// successful wait (ballots, tcgen05.ld / st, __syncwarp) never run on part of a warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int site) {
+  const bool ok = mbar_wait_bounded(bar, parity, abort_flag, site);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ----------------------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

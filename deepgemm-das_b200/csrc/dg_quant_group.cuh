@@ -282,18 +282,19 @@ __global__ void __launch_bounds__(kQgCopyThreads) qg_copy_kernel(const QuantGrou
   for (int i = threadIdx.x; i < p.H / 16; i += kQgCopyThreads) dst[i] = __ldg(src + i);
 }
 
-inline cudaError_t launch_quant_group(const QuantGroupParams& p, cudaStream_t stream) {
+// `sms`: multiprocessors of the current device (sizes the histogram grid).
+inline cudaError_t launch_quant_group(const QuantGroupParams& p, int sms, cudaStream_t stream) {
   if (p.R == 0) {
     // still mark every row unused
     QuantGroupParams q = p;
     q.chunks = 0;
-    qg_histogram_kernel<<<148, 256, 0, stream>>>(q);
+    qg_histogram_kernel<<<sms, 256, 0, stream>>>(q);
     if (p.m_total_out != nullptr) cudaMemsetAsync(p.m_total_out, 0, sizeof(int32_t), stream);
     return cudaGetLastError();
   }
   int hblocks = (p.chunks + 7) / 8;
-  if (hblocks < 148) hblocks = 148;
-  if (hblocks > 148 * 8) hblocks = 148 * 8;
+  if (hblocks < sms) hblocks = sms;
+  if (hblocks > sms * 8) hblocks = sms * 8;
   qg_histogram_kernel<<<hblocks, 256, 0, stream>>>(p);
   qg_scan_kernel<<<p.G, 256, 0, stream>>>(p);
   qg_starts_kernel<<<1, 32, 0, stream>>>(p);

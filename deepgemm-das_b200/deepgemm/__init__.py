@@ -66,6 +66,7 @@ from .quant_group import quant_group_capacity, quantize_group_rows
 from .moe_marlin_prefill import assert_moe_prefill_down_fp8_shapes, moe_w8a8_marlin_prefill_down_fp8
 from .moe_chain import combine_rows, expert_mlp_contiguous, moe_forward, silu_mul_quant
 from .print_size import install_op_size_printer
+from ._core import check_device_status
 
 install_op_size_printer(op)  # no-op unless DEEPGEMM_PRINT_OP_SIZE is set
 

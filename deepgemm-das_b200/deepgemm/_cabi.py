@@ -16,6 +16,7 @@ KIND_I8, KIND_E4M3, KIND_W4A8, KIND_BF16 = 0, 1, 2, 3
 SCALE_PER_CHANNEL, SCALE_TENSOR_WISE, SCALE_NONE = 0, 1, 2
 NIBBLE_HIGH_FIRST, NIBBLE_LOW_FIRST = 0, 1
 STATUS_WORDS = 4
+OUT_BF16, OUT_F16, OUT_F32 = 0, 1, 2
 NOALLOC_MAX_SCRATCH_INTS = 262144 + 1024
 QUERY_ABI_VERSION, QUERY_SM_COUNT, QUERY_MAX_SMEM, QUERY_CC, QUERY_LAUNCH_COUNT = 0, 1, 2, 3, 4
 ERR_CUDA = -7
@@ -60,6 +61,8 @@ class MaskedArgs(C.Structure):
         ("block_n", C.c_int32),
         ("debug_acc", C.c_void_p),
         ("status", C.c_void_p),
+        ("out_kind", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -78,7 +81,7 @@ class ContigArgs(C.Structure):
         ("n", C.c_int32),
         ("k", C.c_int32),
         ("block_n", C.c_int32),
-        ("reserved", C.c_int32),
+        ("out_kind", C.c_int32),
         ("debug_acc", C.c_void_p),
         ("status", C.c_void_p),
         ("scatter_tag", C.c_void_p),

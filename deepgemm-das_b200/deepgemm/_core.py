@@ -60,8 +60,11 @@ def _common_checks(kind, a, b, d, sched, what):
         raise RuntimeError(f"{what}: activation dtype {a.dtype} does not fit {KIND_NAMES[kind]}")
     if not (b.dtype in _B_DTYPES[kind]):
         raise RuntimeError(f"{what}: weight dtype {b.dtype} does not fit {KIND_NAMES[kind]}")
-    if not (d.dtype == torch.bfloat16):
-        raise RuntimeError(f"{what}: output must be torch.bfloat16, got {d.dtype}")
+    if not (d.dtype == torch.bfloat16 or (kind == KIND_W4A8 and d.dtype == torch.float16)):
+        # half outputs exist for the W4A8 ops only, as in the reference
+        # (csrc/arch/gfx936_gfx938_shared/m_grouped_w4a8_gemm_nt_contiguous_hipc.cu:880,909)
+        raise RuntimeError(f"{what}: output must be torch.bfloat16"
+                           f"{' or torch.float16' if kind == KIND_W4A8 else ''}, got {d.dtype}")
     if not (a.is_contiguous()):
         raise RuntimeError(f"{what}: activation must be contiguous")
     if not (b.is_contiguous()):
@@ -82,10 +85,11 @@ def _scale(t: torch.Tensor, shape: Tuple[int, ...], name: str, what: str) -> tor
     if not (tuple(t.shape) == tuple(shape)):
         raise RuntimeError(f"{what}: {name} must have shape {tuple(shape)} "
                        f"(optionally with a trailing 1), got {tuple(t.shape)}")
+    # no copy is made on the caller's behalf: the ops allocate nothing
     if not t.is_contiguous():
-        t = t.contiguous()
-    if t.data_ptr() % 16 != 0:  # a sliced view can be misaligned for the float4 loads
-        t = t.clone()
+        raise RuntimeError(f"{what}: {name} must be contiguous (got strides {tuple(t.stride())})")
+    if t.data_ptr() % 16 != 0:  # a sliced view can be misaligned for the kernels' 16-byte loads
+        raise RuntimeError(f"{what}: {name} must start on a 16-byte boundary")
     return t
 
 
@@ -108,6 +112,49 @@ def _launch(entry, args, device: torch.device, what: str) -> None:
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
+
+
+# ---- device status words ------------------------------------------------------------------
+# The kernels never trap.  A bounded wait that ran out, or an m_indices entry outside the group
+# range, is recorded in four int32 words that the launch was given.  Callers of the public entry
+# points pass none, so every launch gets the words of its device from here and the caller asks
+# for them with check_device_status() whenever it synchronises anyway.
+_status_words = {}
+_STATUS_TEXT = {1: "a bounded wait inside a kernel ran out (thread block {1}, wait site {2}, {3} work items): "
+                   "the launch left part of its output unwritten",
+                2: "an expert index was outside [0, num_groups) (m_indices entry or routed pair): "
+                   "the rows it names were skipped"}
+
+
+def device_status_words(device: torch.device) -> torch.Tensor:
+    """The int32[4] status words every launch on `device` reports into (allocated on first use)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    words = _status_words.get(index)
+    if words is None:
+        words = torch.zeros(_cabi.STATUS_WORDS, dtype=torch.int32, device=torch.device("cuda", index))
+        _status_words[index] = words
+    return words
+
+
+def check_device_status(device=None, *, clear: bool = True) -> None:
+    """Raises RuntimeError if a kernel of this library reported a problem on `device` (default:
+    the current device) since the last call.  Reads four ints from the device, i.e. waits for the
+    work enqueued so far: call it where the caller synchronises anyway.  No launch of the public
+    API fails silently: a wait that ran out or a skipped row block always shows up here."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    device = torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    words = _status_words.get(index)
+    if words is None:
+        return
+    st = words.tolist()
+    if st[0] == 0:
+        return
+    if clear:
+        words.zero_()
+    text = _STATUS_TEXT.get(st[0], "unknown device status {0}").format(*st)
+    raise RuntimeError(f"deepgemm device status on cuda:{index}: {text}")
 
 
 def _debug_and_status(debug_acc, status, rows, n, dev, what):
@@ -150,12 +197,15 @@ def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Te
         a_s = _scale(a_scale, (g, max_m), "a_scale", what)
         b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
     _debug_and_status(debug_acc, status, g * max_m, n, a.device, what)
+    if status is None:
+        status = device_status_words(a.device)
 
     args = _cabi.MaskedArgs(
         kind=kind, scale_mode=scale_mode, a=a.data_ptr(), b_packed=b.data_ptr(), d=d.data_ptr(),
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), masked_m=masked_m.data_ptr(), num_groups=g,
         max_m=max_m, n=n, k=k, expected_m=int(expected_m), block_n=int(block_n),
-        debug_acc=_ptr(debug_acc), status=_ptr(status))
+        debug_acc=_ptr(debug_acc), status=_ptr(status),
+        out_kind=_cabi.OUT_F16 if d.dtype == torch.float16 else _cabi.OUT_BF16)
     _launch(_cabi.lib.dg_masked_gemm, args, a.device, what)
     return d
 
@@ -198,11 +248,14 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
         a_s = _scale(a_scale, (m_total,), "a_scale", what)
         b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
     _debug_and_status(debug_acc, status, m_total, n, a.device, what)
+    if status is None:
+        status = device_status_words(a.device)
 
     args = _cabi.ContigArgs(
         kind=kind, scale_mode=scale_mode, a=a.data_ptr(), b_packed=b.data_ptr(), d=d.data_ptr(),
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), m_indices=m_indices.data_ptr(), num_groups=g,
-        m_total=m_total, n=n, k=k, block_n=int(block_n), reserved=0,
+        m_total=m_total, n=n, k=k, block_n=int(block_n),
+        out_kind=_cabi.OUT_F16 if d.dtype == torch.float16 else _cabi.OUT_BF16,
         debug_acc=_ptr(debug_acc), status=_ptr(status))
     if scatter is not None:
         args.scatter_tag, args.scatter_base, args.scatter_world = scatter[0].data_ptr(), scatter[1], int(scatter[2])
@@ -243,6 +296,8 @@ def grouped_gemm_compact(kind: int, scale_mode: int, a: torch.Tensor, b: torch.T
         a_s = _scale(a_scale, (cap,), "a_scale", what)
         b_s = _scale(b_scale, (g, n) if scale_mode == SCALE_PER_CHANNEL else (g,), "b_scale", what)
     _debug_and_status(debug_acc, status, cap, n, a.device, what)
+    if status is None:
+        status = device_status_words(a.device)
     args = _cabi.CompactArgs(
         kind=kind, scale_mode=scale_mode, a=a.data_ptr(), b_packed=b.data_ptr(), d=d.data_ptr(),
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), counts=counts.data_ptr(), offsets=offsets.data_ptr(),
@@ -264,6 +319,7 @@ def kind_of_activation(a: torch.Tensor) -> int:
 
 __all__ = [
     "grouped_gemm_masked", "grouped_gemm_contiguous", "grouped_gemm_compact", "packed_weight_dims", "kind_of_activation",
+    "check_device_status", "device_status_words",
     "KIND_I8", "KIND_E4M3", "KIND_W4A8", "KIND_BF16",
     "SCALE_PER_CHANNEL", "SCALE_TENSOR_WISE", "SCALE_NONE",
 ]

@@ -269,241 +269,3 @@ def ep_moe_forward(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: t
     if combine is None:
         from .moe_chain import combine_rows as combine
     return combine(back, src_row.view(t, k), topk_weights.to(torch.float32))
-
-
-def benchmark_ep_prefill(device, rank: int, world: int, steps: int = 10, warmup: int = 3,
-                         peaks: Optional[dict] = None, num_experts: int = 256, hidden_k: int = 7168,
-                         n: int = 4096, tokens: int = 4096, top_k: int = 8) -> dict:
-    """Times the all-to-all dispatch and the grouped GEMM separately (CUDA events, max over
-    ranks) for the expert-parallel prefill configuration; returns a JSON-able dict."""
-    from . import marlin_fp8_contiguous_weight
-    from .m_group_gemm_nt_contiguous import m_grouped_fp8_gemm_nt_contiguous
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-    e_local = num_experts // world
-    gen = torch.Generator(device=device).manual_seed(100 + rank)
-    shared = torch.Generator().manual_seed(7)                     # same expert bias on every rank
-    bias = (torch.randn(num_experts, generator=shared) * 0.5).to(device)
-    hidden = torch.randn(tokens, hidden_k, device=device, generator=gen).to(torch.bfloat16)
-    logits = torch.randn(tokens, num_experts, device=device, generator=gen) + bias
-    topk_ids = route_topk(logits, top_k)
-    b = torch.empty(e_local, n, hidden_k, dtype=torch.float8_e4m3fn, device=device)
-    b_scale = torch.empty(e_local, n, dtype=torch.float32, device=device)
-    for g in range(e_local):
-        q, s = per_token_quant_fp8(torch.randn(n, hidden_k, device=device, generator=gen))
-        b[g], b_scale[g] = q, s.reshape(n)
-    b_packed = marlin_fp8_contiguous_weight(b)
-
-    plan = build_dispatch_plan(topk_ids, num_experts, world)
-
-    def ev():
-        return torch.cuda.Event(enable_timing=True)
-
-    def sync():
-        if dist:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # all-to-all (counts + payload)
-    for _ in range(warmup):
-        rows, recv_expert = dispatch_tokens(hidden, plan, num_experts, rank, world)
-    sync()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        rows, recv_expert, recv_splits = dispatch_tokens(hidden, plan, num_experts, rank, world,
-                                                         return_splits=True)
-    e1.record()
-    sync()
-    a2a_ms = e0.elapsed_time(e1) / steps
-
-    # the same dispatch with rows quantised at the source: e4m3 payload + fp32 scales
-    from .quant_group import quantize_group_rows, quantize_rows
-    for _ in range(warmup):
-        q8, q8_scale = quantize_rows(hidden)
-    torch.cuda.synchronize()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        q8, q8_scale = quantize_rows(hidden)
-    e1.record()
-    torch.cuda.synchronize()
-    quant_src_ms = e0.elapsed_time(e1) / steps
-    for _ in range(warmup):
-        rows8, _, scale8 = dispatch_tokens(q8, plan, num_experts, rank, world, row_scale=q8_scale)
-    sync()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        rows8, _, scale8 = dispatch_tokens(q8, plan, num_experts, rank, world, row_scale=q8_scale)
-    e1.record()
-    sync()
-    a2a8_ms = e0.elapsed_time(e1) / steps
-    def plan_exchange():
-        return build_unique_plan(plan, tokens, num_experts, rank, world)
-    for _ in range(warmup):
-        uplan = plan_exchange()
-    sync()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        uplan = plan_exchange()
-    e1.record()
-    sync()
-    uplan_ms = e0.elapsed_time(e1) / steps    # routing metadata: counts + 8 bytes per pair
-    for _ in range(warmup):
-        urows, usrc, uexp, _, uscale = dispatch_unique(q8, plan, num_experts, rank, world,
-                                                       row_scale=q8_scale, uplan=uplan)
-    sync()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        urows, usrc, uexp, _, uscale = dispatch_unique(q8, plan, num_experts, rank, world,
-                                                       row_scale=q8_scale, uplan=uplan)
-    e1.record()
-    sync()
-    a2a_unique_ms = e0.elapsed_time(e1) / steps
-    unique_rows = int(urows.shape[0])
-    for _ in range(warmup):
-        quantize_group_rows(urows, uexp, e_local, row_scale=uscale, src_index=usrc)
-    torch.cuda.synchronize()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        quantize_group_rows(urows, uexp, e_local, row_scale=uscale, src_index=usrc)
-    e1.record()
-    torch.cuda.synchronize()
-    group_unique_ms = e0.elapsed_time(e1) / steps
-    del urows, usrc, uexp, uscale
-    for _ in range(warmup):
-        quantize_group_rows(rows8, recv_expert.to(torch.int32), e_local, row_scale=scale8)
-    torch.cuda.synchronize()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        quantize_group_rows(rows8, recv_expert.to(torch.int32), e_local, row_scale=scale8)
-    e1.record()
-    torch.cuda.synchronize()
-    group8_ms = e0.elapsed_time(e1) / steps
-    del rows8, scale8, q8, q8_scale
-
-    # quantise + group + pad (fused producer kernels; reported beside the two headline figures)
-    recv_expert = recv_expert.to(torch.int32)
-    for _ in range(warmup):
-        a, a_scale, m_indices, _, _ = quantize_group_rows(rows, recv_expert, e_local)
-    torch.cuda.synchronize()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        a, a_scale, m_indices, dest, _ = quantize_group_rows(rows, recv_expert, e_local)
-    e1.record()
-    torch.cuda.synchronize()
-    prep_ms = e0.elapsed_time(e1) / steps
-    del rows
-
-    out = torch.zeros((a.shape[0], n), dtype=torch.bfloat16, device=device)
-    gemm = lambda: m_grouped_fp8_gemm_nt_contiguous((a, a_scale), (b_packed, b_scale), out, m_indices)
-    for _ in range(warmup):
-        gemm()
-    sync()
-    e0, e1 = ev(), ev()
-    e0.record()
-    for _ in range(steps):
-        gemm()
-    e1.record()
-    sync()
-    gemm_ms = e0.elapsed_time(e1) / steps
-
-    # ---- the rest of the layer: SiLU*up + requantise, down GEMM, reverse all-to-all, combine
-    from .moe_chain import combine_rows, silu_mul_quant
-
-    def timed(fn, collective=False):
-        for _ in range(warmup):
-            fn()
-        sync() if collective else torch.cuda.synchronize()
-        t0, t1 = ev(), ev()
-        t0.record()
-        for _ in range(steps):
-            fn()
-        t1.record()
-        sync() if collective else torch.cuda.synchronize()
-        return t0.elapsed_time(t1) / steps
-
-    inter = n // 2
-    w2 = torch.empty(e_local, hidden_k, inter, dtype=torch.float8_e4m3fn, device=device)
-    w2_scale = torch.empty(e_local, hidden_k, dtype=torch.float32, device=device)
-    for g in range(e_local):
-        q, s = per_token_quant_fp8(torch.randn(hidden_k, inter, device=device, generator=gen))
-        w2[g], w2_scale[g] = q, s.reshape(hidden_k)
-    w2_packed = marlin_fp8_contiguous_weight(w2)
-    act_out = (torch.zeros((a.shape[0], inter), dtype=torch.float8_e4m3fn, device=device),
-               torch.zeros((a.shape[0],), dtype=torch.float32, device=device))
-    act_ms = timed(lambda: silu_mul_quant(out, kind="fp8", m_indices=m_indices, out=act_out))
-    y = torch.zeros((a.shape[0], hidden_k), dtype=torch.bfloat16, device=device)
-    down_ms = timed(lambda: m_grouped_fp8_gemm_nt_contiguous(act_out, (w2_packed, w2_scale), y, m_indices),
-                    collective=True)
-    y_recv = y.index_select(0, dest.long())
-    back_holder = {}
-
-    def send_back():
-        back_holder["rows"] = return_rows(y_recv, recv_splits, plan.send_splits, world)
-    back_ms = timed(send_back, collective=True)
-    src_row = torch.empty(tokens * top_k, dtype=torch.int32, device=device)
-    src_row[plan.send_pair] = torch.arange(tokens * top_k, dtype=torch.int32, device=device)
-    weights = torch.softmax(torch.randn(tokens, top_k, device=device, generator=gen), dim=1)
-    final = torch.empty((tokens, hidden_k), dtype=torch.bfloat16, device=device)
-    combine_ms = timed(lambda: combine_rows(back_holder["rows"], src_row.view(tokens, top_k), weights, out=final))
-
-    valid = int((m_indices >= 0).sum())
-    chain = torch.tensor([act_ms, down_ms, back_ms, combine_ms, quant_src_ms, a2a8_ms, group8_ms,
-                          a2a_unique_ms, group_unique_ms, uplan_ms], device=device, dtype=torch.float64)
-    if dist:
-        dist.all_reduce(chain, op=dist.ReduceOp.MAX)
-    (act_ms, down_ms, back_ms, combine_ms, quant_src_ms, a2a8_ms, group8_ms, a2a_unique_ms,
-     group_unique_ms, uplan_ms) = (float(x) for x in chain.tolist())
-    stats = torch.tensor([a2a_ms, gemm_ms, prep_ms], device=device, dtype=torch.float64)
-    flops = torch.tensor([2.0 * valid * n * hidden_k], device=device, dtype=torch.float64)
-    sent_remote = sum(s for r, s in enumerate(plan.send_splits) if r != rank) * hidden_k * 2
-    sent = torch.tensor([float(sent_remote)], device=device, dtype=torch.float64)
-    if dist:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(flops, op=dist.ReduceOp.SUM)
-        dist.all_reduce(sent, op=dist.ReduceOp.MAX)
-    a2a_ms, gemm_ms, prep_ms = (float(x) for x in stats.tolist())
-    tflops = float(flops) / (gemm_ms * 1e-3) / 1e12
-    res = {"workload": "ep_fp8_contiguous experts=%d K=%d N=%d tokens/rank=%d top%d" % (
-        num_experts, hidden_k, n, tokens, top_k), "world": world,
-        "gemm_ms_max_over_ranks": gemm_ms, "gemm_tflops_aggregate": tflops,
-        "gemm_tflops_per_gpu": tflops / world,
-        "all_to_all_ms_max_over_ranks": a2a_ms, "quantise_group_ms_max_over_ranks": prep_ms,
-        "all_to_all_remote_bytes_max_per_rank": float(sent),
-        "valid_rows_this_rank": valid, "m_total_this_rank": int(a.shape[0])}
-    down_flops = torch.tensor([2.0 * valid * hidden_k * inter], device=device, dtype=torch.float64)
-    if dist:
-        dist.all_reduce(down_flops, op=dist.ReduceOp.SUM)
-    res["fp8_dispatch"] = {   # rows quantised once per token at the source, half the bytes on the wire
-        "quantise_tokens_ms": quant_src_ms, "all_to_all_ms_max_over_ranks": a2a8_ms,
-        "group_ms_max_over_ranks": group8_ms,
-        "unique_rows": {"note": "each token once per destination rank; routing metadata (counts + 8 B per "
-                                "pair, with the one host sync) exchanged apart from the payload",
-                        "routing_exchange_ms_max_over_ranks": uplan_ms,
-                        "all_to_all_ms_max_over_ranks": a2a_unique_ms,
-                        "group_ms_max_over_ranks": group_unique_ms, "rows_received_this_rank": unique_rows},
-        "all_to_all_remote_bytes_max_per_rank": float(sent) / 2 + float(sent) / (hidden_k * 2) * 4}
-    res["down_chain"] = {
-        "silu_mul_quant_ms": act_ms,
-        "silu_mul_quant_gbs_this_rank": valid * (n * 2 + inter + 4) / (act_ms * 1e-3) / 1e9,
-        "down_gemm_ms": down_ms, "down_gemm_tflops_aggregate": float(down_flops) / (down_ms * 1e-3) / 1e12,
-        "combine_all_to_all_ms": back_ms, "combine_sum_ms": combine_ms,
-        "combine_sum_gbs_this_rank": tokens * (top_k + 1) * hidden_k * 2 / (combine_ms * 1e-3) / 1e9}
-    if float(sent) > 0:
-        res["all_to_all_gbs_per_rank"] = float(sent) / (a2a_ms * 1e-3) / 1e9
-    if peaks:
-        weight_bytes = e_local * n * hidden_k
-        t_hbm = (weight_bytes + valid * hidden_k + valid * n * 2) / (peaks["hbm_gbs"] * 1e9)
-        t_tc = 2.0 * valid * n * hidden_k / (2.0 * peaks["bf16_tflops"] * 1e12)
-        res["gemm_roofline_ms"] = max(t_hbm, t_tc) * 1e3
-        res["gemm_bound"] = "hbm" if t_hbm > t_tc else "tensor"
-        res["gemm_frac_of_roofline"] = max(t_hbm, t_tc) * 1e3 / gemm_ms
-    return res

@@ -16,7 +16,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _cabi
-from ._core import _launch
+from ._core import _launch, device_status_words
 
 _OUT_KIND = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
@@ -64,7 +64,8 @@ def _dense(a, b, d, where: str, allowed) -> torch.Tensor:
         kind=kind, out_kind=_OUT_KIND[d.dtype], a=mat_a.data_ptr(), b=mat_b.data_ptr(), d=d.data_ptr(),
         a_scale=scale_a.data_ptr() if (has_a or has_b) else None,
         b_scale=scale_b.data_ptr() if (has_a or has_b) else None,
-        batch=batch, m=m, n=n, k=k, block_n=0, reserved=0, debug_acc=None, status=None)
+        batch=batch, m=m, n=n, k=k, block_n=0, reserved=0, debug_acc=None,
+        status=device_status_words(mat_a.device).data_ptr())
     _launch(_cabi.lib.dg_dense_gemm, args, mat_a.device, where)
     return d
 

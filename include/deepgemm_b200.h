@@ -70,6 +70,11 @@ typedef enum dg_status {
   DG_ERR_BAD_ARGUMENT   = -9
 } dg_status;
 
+/* Output element types (F32: dg_dense_gemm only). */
+#define DG_OUT_BF16 0
+#define DG_OUT_F16  1
+#define DG_OUT_F32  2
+
 /* Words of the optional device-side status buffer (`status`, int32[DG_STATUS_WORDS]).
  * The kernels never trap: a wait that runs out records {code, block, role, detail} here,
  * the block leaves cleanly, and the host reads the words after synchronising the stream.
@@ -118,6 +123,9 @@ typedef struct dg_masked_args {
                                  32 / 64 = 128-wide kernel narrowed to that width (sparse routing) */
   void*          debug_acc;   /* NULL, or [G][max_m][N] of raw 32-bit accumulators (s32 / f32) */
   int32_t*       status;      /* NULL, or int32[DG_STATUS_WORDS] device status words */
+  int32_t out_kind;           /* DG_OUT_BF16 (0) or DG_OUT_F16: element type of d.  The reference's W4A8 ops
+                                 take half outputs (m_grouped_w4a8_gemm_nt_masked_hipc.cu:1148) */
+  int32_t reserved;
 } dg_masked_args;
 
 /* Arguments of the contiguous-layout grouped GEMM.
@@ -140,7 +148,7 @@ typedef struct dg_contig_args {
   int32_t n;
   int32_t k;
   int32_t block_n;            /* 0 = choose; 128 / 256 = one-CTA tile width; 512 = two-CTA 256x256 tiles */
-  int32_t reserved;
+  int32_t out_kind;           /* DG_OUT_BF16 (0) or DG_OUT_F16 (m_grouped_w4a8_gemm_nt_contiguous_hipc.cu:880,909) */
   void*          debug_acc;   /* NULL, or [M_total][N] raw accumulators */
   int32_t*       status;
   /* Scattered output (expert-parallel layers): when scatter_tag is not NULL, the result row i
@@ -207,11 +215,6 @@ DG_API int dg_contig_gemm(const dg_contig_args* args, void* stream);
  *   m_grouped_w8a8_gemm_nt_nopad_contiguous        csrc/arch/gfx936_gfx938_shared/asm_m_grouped_w8a8_gemm_nt_contiguous.cu:595-607
  *     (rows per group given as token_per_expert; the caller passes their running sum as offsets) */
 DG_API int dg_compact_gemm(const dg_compact_args* args, void* stream);
-
-/* Output element types of dg_dense_gemm. */
-#define DG_OUT_BF16 0
-#define DG_OUT_F16  1
-#define DG_OUT_F32  2
 
 /* Arguments of the plain (batched) GEMM  d[b] = (a[b] * a_scale[b][:,None]) @ (w[b] *
  * b_scale[b][:,None])^T  with weights in their natural row-major [n][k] order (no packing),

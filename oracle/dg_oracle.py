@@ -112,6 +112,32 @@ def ref_masked_w4a8(a: torch.Tensor, packed_b: torch.Tensor, a_scale: torch.Tens
     return ref_masked_scaled(a, unpack_int4_to_int8_x16(packed_b, nibble_order), a_scale, b_scale)
 
 
+def ref_masked_w4a8_hipc(a: torch.Tensor, packed_b: torch.Tensor, a_scale: torch.Tensor,
+                         w_scale: torch.Tensor, out_dtype=torch.bfloat16,
+                         nibble_order: str = "high_first") -> torch.Tensor:
+    """op_test/test_deepgemm_masked_w4a8_hipc.py:63-82: nibbles read as two's complement
+    (`where(u4 > 7, u4 - 16, u4)`), `ref = bmm(a.float(), w.float()^T) * a_scale * w_scale^T`; the
+    kernel under test receives `w_scale / 16` and multiplies by 16 x the nibble.  `packed_b` is
+    the framework layout [E, N, K/2]; a_scale [E, M, 1], w_scale [E, N, 1]."""
+    w = (unpack_int4_to_int8_x16(packed_b, nibble_order).to(torch.int16) // 16).to(torch.float32)
+    ref = torch.bmm(_f32(a), w.transpose(1, 2))
+    return (ref * a_scale * w_scale.transpose(1, 2)).to(out_dtype)
+
+
+def ref_contiguous_w4a8_hipc(a: torch.Tensor, packed_b: torch.Tensor, a_scale: torch.Tensor,
+                             w_scale: torch.Tensor, m_indices: torch.Tensor, out_dtype=torch.bfloat16,
+                             nibble_order: str = "high_first") -> torch.Tensor:
+    """op_test/test_deepgemm_contiguous_w4a8_hipc.py:70-76: per expert `acc = a[rows].float() @
+    w.float().t(); acc * a_scale[rows] * w_scale[e].t()`, rows with m_indices < 0 left zero."""
+    w = (unpack_int4_to_int8_x16(packed_b, nibble_order).to(torch.int16) // 16).to(torch.float32)
+    ref = torch.zeros((a.shape[0], w.shape[1]), dtype=torch.float32)
+    for e in range(w.shape[0]):
+        rows = m_indices == e
+        acc = _f32(a[rows]) @ w[e].t()
+        ref[rows] = acc * _f32(a_scale[rows]) * _f32(w_scale[e]).t()
+    return ref.to(out_dtype)
+
+
 # ----------------------------------------------------------------------------- contiguous references
 def ref_contiguous(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor,
                    m_indices: torch.Tensor, out_dtype=torch.bfloat16,

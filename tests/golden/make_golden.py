@@ -59,7 +59,8 @@ def _import_reference_helpers():
     for name in ("quant_utils", "masked_w8a8_int8_common", "contiguous_w8a8_int8_common",
                  "test_deepgemm_masked_w8a8_fp8", "test_deepgemm_masked_w8a8_fp8_tensor_wise",
                  "test_deepgemm_masked_w4a8", "test_deepgemm_contiguous_w8a8_fp8",
-                 "test_deepgemm_contiguous_w8a8_fp8_tensor_wise", "test_fp8_gemm"):
+                 "test_deepgemm_contiguous_w8a8_fp8_tensor_wise", "test_fp8_gemm",
+                 "test_masked_w8a8_big_tile_real6"):
         mods[name] = importlib.import_module(name)
     # The reference's int4 framework packer lives in its package; load that one file with
     # its sibling import stubbed.
@@ -179,6 +180,73 @@ def main():
     ref = m["test_fp8_gemm"].torch_fp8_gemm(ad, bd.t(), sad, sbd, out_dtype=torch.bfloat16)
     ref16 = m["test_fp8_gemm"].torch_fp8_gemm(ad, bd.t(), sad, sbd, out_dtype=torch.float16)
     _save("dense_fp8", a=ad, a_scale=sad, b=bd, b_scale=sbd, out=ref, out_f16=ref16)
+
+    # The cases below draw from a generator of their own, so that the files above stay byte for
+    # byte what they were before these were added.
+    g2 = torch.Generator().manual_seed(20251126)
+
+    # 10. masked W4A8, signed-nibble convention of the HIPC path.  The reference computes the
+    #     expectation inline (op_test/test_deepgemm_masked_w4a8_hipc.py:63-82): int8 activations in
+    #     [-8, 8), unsigned nibbles 0..14 read as two's complement, ref = bmm * a_scale * w_scale,
+    #     while the op is given w_scale / 16.  Same statements here; the framework layout comes
+    #     from the reference's own packer.
+    e4, m4, n4, k4 = 2, 48, 128, 256
+    q_a = torch.randint(-8, 8, (e4, m4, k4), generator=g2, dtype=torch.int8)
+    a_scale4 = torch.rand((e4, m4, 1), generator=g2) * 0.02 + 0.001
+    w_scale4 = torch.rand((e4, n4, 1), generator=g2) * 0.02 + 0.001
+    weight_u4 = torch.randint(0, 15, (e4, n4, k4), generator=g2, dtype=torch.int8)
+    framework4 = m["weight_pack"].pack_w4a8_weight_k_contiguous(weight_u4)
+    w_ref = torch.where(weight_u4 > 7, weight_u4 - 16, weight_u4)
+    ref = torch.bmm(q_a.float(), w_ref.float().transpose(1, 2))
+    ref = ref * a_scale4 * w_scale4.transpose(1, 2)
+    _save("masked_w4a8_hipc", a=q_a, a_scale=a_scale4, u4=weight_u4, framework=framework4, w_scale=w_scale4,
+          kernel_w_scale=w_scale4 / 16.0, out=ref.to(torch.bfloat16), out_f16=ref.to(torch.float16))
+
+    # 11. contiguous W4A8 (op_test/test_deepgemm_contiguous_w4a8_hipc.py:36-90): groups aligned to
+    #     128 rows, -1 on padding rows, same conventions
+    actual_ms, n5, k5 = [70, 128, 5], 128, 256
+    aligned = [(v + 127) // 128 * 128 for v in actual_ms]
+    size_m = sum(aligned)
+    q_a5 = torch.randint(-8, 8, (size_m, k5), generator=g2, dtype=torch.int8)
+    a_scale5 = torch.rand((size_m, 1), generator=g2) * 0.02 + 0.001
+    w_scale5 = torch.rand((len(actual_ms), n5, 1), generator=g2) * 0.02 + 0.001
+    weight_u45 = torch.randint(0, 15, (len(actual_ms), n5, k5), generator=g2, dtype=torch.int8)
+    framework5 = m["weight_pack"].pack_w4a8_weight_k_contiguous(weight_u45)
+    w_ref5 = torch.where(weight_u45 > 7, weight_u45 - 16, weight_u45)
+    m_indices5 = torch.empty((size_m,), dtype=torch.int32)
+    start = 0
+    for expert, (actual_m, aligned_m) in enumerate(zip(actual_ms, aligned)):
+        m_indices5[start:start + actual_m] = expert
+        m_indices5[start + actual_m:start + aligned_m] = -1
+        start += aligned_m
+    ref5 = torch.zeros((size_m, n5))
+    for expert in range(len(actual_ms)):
+        rows5 = m_indices5 == expert
+        acc = q_a5[rows5].float() @ w_ref5[expert].float().t()
+        ref5[rows5] = acc * a_scale5[rows5].float() * w_scale5[expert].float().t()
+    _save("contig_w4a8_hipc", a=q_a5, a_scale=a_scale5, u4=weight_u45, framework=framework5,
+          w_scale=w_scale5, kernel_w_scale=w_scale5 / 16.0, m_indices=m_indices5,
+          out=ref5.to(torch.bfloat16), out_f16=ref5.to(torch.float16))
+
+    # 12. masked BF16 (op_test/test_deepgemm_masked_w16a16_bf16.py:55-80): N(0, 0.1) operands,
+    #     ref = (a.float() @ w.float().t()).to(bf16) on the active rows, zero tail rows
+    eb, mb, nb, kb, active = 2, 64, 256, 128, 40
+    ab = (torch.randn(eb, mb, kb, generator=g2) * 0.1).to(torch.bfloat16)
+    wb = (torch.randn(eb, nb, kb, generator=g2) * 0.1).to(torch.bfloat16)
+    refb = torch.zeros(eb, mb, nb, dtype=torch.bfloat16)
+    for expert in range(eb):
+        refb[expert, :active] = (ab[expert, :active].float() @ wb[expert].float().t()).to(torch.bfloat16)
+    _save("masked_bf16", a=ab, b=wb, masked_m=torch.full((eb,), active, dtype=torch.int32), out=refb)
+
+    # 13. the six routing vectors logged from a serving run that the reference replays
+    #     (op_test/test_masked_w8a8_big_tile_real6.py:46-53): rows per expert, 36 experts, one with
+    #     16 384 rows; N and K of each case
+    real6 = m["test_masked_w8a8_big_tile_real6"]
+    names = list(real6.DEFAULT_CASES)
+    _save("skew_masked_m", names=np.array(names),
+          masked_m=np.array([real6.CASES[n].masked_m for n in names], dtype=np.int32),
+          n=np.array([getattr(real6.CASES[n], "n", 0) for n in names], dtype=np.int32),
+          k=np.array([getattr(real6.CASES[n], "k", 0) for n in names], dtype=np.int32))
 
 
 if __name__ == "__main__":

@@ -21,7 +21,9 @@ def load_golden(name: str) -> dict:
     out = {}
     for k in raw.files:
         arr = raw[k]
-        if arr.dtype == np.uint16:  # bf16 bit patterns
+        if arr.dtype.kind in "US":  # names
+            out[k] = [str(v) for v in arr.tolist()]
+        elif arr.dtype == np.uint16:  # bf16 bit patterns
             out[k] = torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16)
         elif arr.dtype == np.uint8 and name in _FP8_CASES and k in ("a", "b"):
             out[k] = torch.from_numpy(arr.copy()).view(FP8)

@@ -107,6 +107,19 @@ def test_rows_that_do_not_fit_are_dropped_and_reported():
             r.check_status()
 
 
+def test_a_peer_that_never_arrives_is_reported_not_waited_for_ever():
+    """The waiting half of a barrier whose signal nobody posts gives up after its limit (2 s),
+    records which peer was missing and returns; the device stays usable."""
+    dev = torch.device("cuda", 0)
+    ranks = epx.make_emulated_ranks(2, E, H, 2 * INTER, H, T, TOPK, 1024, dev)
+    ranks[0].barrier(_cabi.EP_PHASE_POST)               # rank 0 posts its own arrival ...
+    ranks[0].barrier(_cabi.EP_PHASE_WAIT)               # ... rank 1 never posts this epoch
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="gave up waiting for peer 1"):
+        ranks[0].check_status()
+    assert int(torch.ones(4, device=dev).sum()) == 4     # the context still works
+
+
 def test_argument_errors():
     dev = torch.device("cuda", 0)
     x = epx.EPExchange(0, 1, E, H, 2 * INTER, H, T, TOPK, 4096, dev)

@@ -144,3 +144,37 @@ def test_sorted_routing_oracle_equals_the_per_pair_formula():
             want = ((inp[r].double() @ w[ee].double().t()).float() * (tw[tok, s] * a_s[r])) * b_s[ee]
             want = torch.zeros(n) if ee == 3 else want
             assert torch.equal(out[r], want.bfloat16()), (tok, s)
+
+
+def test_w4a8_signed_nibble_convention_matches_reference():
+    """The expectation the reference's HIPC W4A8 tests compute inline (signed nibbles, the op
+    gets w_scale / 16), masked and contiguous, bf16 and fp16 outputs."""
+    g = load_golden("masked_w4a8_hipc")
+    assert torch.equal(O.signed_int4(g["u4"]).to(torch.int16) * 16,
+                       O.unpack_int4_to_int8_x16(g["framework"]).to(torch.int16))
+    _same_bits(O.ref_masked_w4a8_hipc(g["a"], g["framework"], g["a_scale"], g["w_scale"]), g["out"])
+    got16 = O.ref_masked_w4a8_hipc(g["a"], g["framework"], g["a_scale"], g["w_scale"], torch.float16)
+    assert torch.equal(got16.view(torch.int16), g["out_f16"].view(torch.int16))
+    # what the kernel computes, 16 x nibble with w_scale / 16, is the same number bit for bit
+    _same_bits(O.ref_masked_w4a8(g["a"], g["framework"], g["a_scale"], g["kernel_w_scale"]), g["out"])
+    c = load_golden("contig_w4a8_hipc")
+    _same_bits(O.ref_contiguous_w4a8_hipc(c["a"], c["framework"], c["a_scale"], c["w_scale"], c["m_indices"]),
+               c["out"])
+    got16 = O.ref_contiguous_w4a8_hipc(c["a"], c["framework"], c["a_scale"], c["w_scale"], c["m_indices"],
+                                       torch.float16)
+    assert torch.equal(got16.view(torch.int16), c["out_f16"].view(torch.int16))
+
+
+def test_masked_bf16_matches_reference():
+    g = load_golden("masked_bf16")
+    m = int(g["masked_m"][0])
+    got = O.ref_masked_bf16(g["a"], g["b"])
+    _same_bits(got[:, :m].contiguous(), g["out"][:, :m].contiguous())
+    assert bool((g["out"][:, m:] == 0).all())
+
+
+def test_logged_routing_vectors_fixture():
+    g = load_golden("skew_masked_m")
+    mm = g["masked_m"]
+    assert tuple(mm.shape) == (6, 36) and int(mm.max()) == 16384
+    assert int((mm == 0).sum()) > 20          # many experts without a row, a few with thousands
