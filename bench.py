@@ -285,9 +285,11 @@ def bench_contig_prefill(device, steps, warmup, peaks, kind="int8"):
             "frac_of_own_dense_8bit": tops / own, "clocks": sampler.summary(t0, t1)}
 
 
-def make_masked_w4a8(device, small=False):
+def make_masked_w4a8(device, small=False, smem_unpack=False):
     """Masked W4A8 down projection: 32 experts, N=7168, K=2048, max_m=256, masked_m uniform in
-    [0,256]; int4 source bytes low-nibble-first.  Returns (launch function, info)."""
+    [0,256]; int4 source bytes low-nibble-first.  Returns (launch function, info).  With
+    `smem_unpack` the launch goes to the kernel that unpacks into shared memory (block_n = 512)
+    instead of the default one (unpacked weights through tensor memory)."""
     import deepgemm
     from deepgemm.quant_utils import pack_int4_pairs, per_channel_quant_int4, per_token_quant_int8
     G, N, K, max_m = 32, 7168, 2048, 256
@@ -304,7 +306,11 @@ def make_masked_w4a8(device, small=False):
     d = torch.zeros(G, max_m, N, dtype=torch.bfloat16, device=device)
     a_s = a_s.reshape(G, max_m).contiguous()
     mmd = mm.to(device)
-    fn = lambda: deepgemm.m_grouped_w4a8_gemm_nt_masked((a, a_s), (bp, b_s), d, mmd, max_m)
+    if smem_unpack:
+        from deepgemm import _cabi, _core
+        fn = lambda: _core.grouped_gemm_masked(_cabi.KIND_W4A8, 0, a, bp, d, a_s, b_s, mmd, max_m, block_n=512)
+    else:
+        fn = lambda: deepgemm.m_grouped_w4a8_gemm_nt_masked((a, a_s), (bp, b_s), d, mmd, max_m)
     v = int(mm.sum())
     info = {"workload": "masked_w4a8 G=32 N=7168 K=2048 max_m=256 V=%d" % v,
             "ops": 2.0 * v * N * K, "bytes": algorithmic_bytes(v, int((mm > 0).sum()), G, N, K, 1, 0.5)}
@@ -313,11 +319,59 @@ def make_masked_w4a8(device, small=False):
 
 def bench_masked_w4a8(device, steps, warmup, peaks):
     fn, info = make_masked_w4a8(device)
-    ms, _, _ = time_launches(fn, steps, warmup)
+    sampler = ClockSampler(device.index or 0, period_s=0.002)
+    sampler.start()
+    ms, t0, t1 = time_launches(fn, steps, warmup)
+    sampler.stop()
     sec = ms * 1e-3 / steps
-    return {"workload": info["workload"], "ms": ms / steps, "gbs": info["bytes"] / sec / 1e9,
-            "frac_of_hbm_peak": info["bytes"] / sec / 1e9 / peaks["hbm_gbs"],
-            "tops": info["ops"] / sec / 1e12}
+    res = {"workload": info["workload"], "ms": ms / steps, "gbs": info["bytes"] / sec / 1e9,
+           "frac_of_hbm_peak": info["bytes"] / sec / 1e9 / peaks["hbm_gbs"],
+           "tops": info["ops"] / sec / 1e12, "kernel": "grouped_gemm_w4_kernel (unpacked weights through TMEM)",
+           "clocks": sampler.summary(t0, t1)}
+    fn2, _ = make_masked_w4a8(device, smem_unpack=True)
+    ms2, _, _ = time_launches(fn2, steps, warmup)
+    res["smem_unpack_kernel_ms"] = ms2 / steps     # the other W4A8 kernel on the same inputs, same box
+    return res
+
+
+def profile_chain(device, steps, warmup):
+    """Profiler driver for the memory-bound kernels around the GEMMs, on a small case (8192 rows of
+    7168; a few hundred MB): quantise + group, SiLU*up + requantise, weighted top-k sum, and the
+    expert-parallel push with one rank."""
+    import deepgemm
+    from deepgemm import ep_exchange as epx
+    from deepgemm.moe_chain import combine_rows, silu_mul_quant
+    rows, hidden, experts, top_k = 8192, 7168, 32, 8
+    gen = torch.Generator(device=device).manual_seed(9)
+    x = torch.randn(rows, hidden, device=device, generator=gen).bfloat16()
+    expert = torch.randint(0, experts, (rows,), device=device, generator=gen, dtype=torch.int32)
+    h13 = torch.randn(rows, 4096, device=device, generator=gen).bfloat16()
+    m_idx = torch.zeros(rows, dtype=torch.int32, device=device)
+    tokens = rows // top_k
+    y = torch.randn(rows, hidden, device=device, generator=gen).bfloat16()
+    src = torch.arange(rows, dtype=torch.int32, device=device).view(tokens, top_k)
+    w = torch.softmax(torch.randn(tokens, top_k, device=device, generator=gen), dim=1)
+    ex = epx.EPExchange(0, 1, experts, hidden, 4096, hidden, tokens, top_k, 2 * rows, device)
+    ids = torch.rand(tokens, experts, device=device, generator=gen).topk(top_k, dim=1).indices.to(torch.int32)
+    q, qs = ex.quantise(x[:tokens].contiguous())
+    ex.plan(ids)
+
+    def step():
+        deepgemm.quantize_group_rows(x, expert, experts)
+        silu_mul_quant(h13, kind="fp8", m_indices=m_idx)
+        combine_rows(y, src, w)
+        ex.plan(ids)
+        ex.push(q, qs, ids)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(json.dumps({"profile_run": True, "workload": "chain kernels rows=%d hidden=%d" % (rows, hidden),
+                      "steps": steps}))
 
 
 EP = dict(experts=256, K=7168, N=4096, tokens=4096, top_k=8)
@@ -566,7 +620,8 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced problem (8 experts) for profiler captures")
     ap.add_argument("--profile", action="store_true",
                     help="profiler run: one workload's timed region only, bracketed by cudaProfilerStart/Stop")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_int8", "prefill_fp8", "w4a8"],
+    ap.add_argument("--workload", default="decode",
+                    choices=["decode", "prefill_int8", "prefill_fp8", "w4a8", "w4a8_smem", "chain"],
                     help="with --profile: which configuration to run (the JSON line is always decode)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -610,9 +665,12 @@ def main():
     barrier = (lambda: dist.barrier()) if dist else None
     peaks = _peaks()
 
+    if args.profile and args.workload == "chain":
+        profile_chain(device, args.steps, warmup)
+        return
     if args.profile and args.workload != "decode":
-        if args.workload == "w4a8":
-            fn, info = make_masked_w4a8(device, args.small)
+        if args.workload in ("w4a8", "w4a8_smem"):
+            fn, info = make_masked_w4a8(device, args.small, smem_unpack=args.workload == "w4a8_smem")
         else:
             fn, info = make_contig_prefill(device, args.small, "int8" if args.workload == "prefill_int8" else "fp8")
         for _ in range(warmup):

@@ -151,6 +151,7 @@ struct Problem {
   const int32_t* scatter_tag;
   void* const* scatter_base;  // host array
   int scatter_world;
+  int32_t* signal;
 };
 
 template <int KIND, int BN>
@@ -181,6 +182,7 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.status = pr.status;
   p.b_rowmajor = pr.dense;
   p.out_kind = pr.out_kind;
+  p.signal = pr.signal;
   p.scatter_tag = pr.scatter_tag;
   for (int r = 0; r < pr.scatter_world && pr.scatter_tag != nullptr; ++r) p.scatter_base[r] = pr.scatter_base[r];
 
@@ -626,6 +628,7 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
     }
   }
   if (bn == 512 && (pr.N < 256 || pr.mode == MODE_COMPACT)) bn = 128;
+  if (bn == 512 && pr.signal != nullptr) bn = 256;  // completion counters live in the one-CTA kernel
   if (bn == 512 && scalar_out) bn = 256;
   if (pr.kind == DG_KIND_W4A8) {
     if (pr.block_n == 512) return launch_w4_smem<3, 3, 4>(pr, *dev, stream);
@@ -681,6 +684,11 @@ int dg_masked_gemm(const dg_masked_args* a, void* stream) {
   pr.debug_acc = a->debug_acc;
   pr.status = a->status;
   pr.out_kind = a->out_kind;
+  if (a->signal != nullptr) {
+    // a tile's columns are credited in four equal parts: N % 32 == 0 keeps them whole numbers
+    if (a->kind == DG_KIND_W4A8 || a->n % 32 != 0) return DG_ERR_BAD_ARGUMENT;
+    pr.signal = a->signal;
+  }
   return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
 }
 
@@ -880,6 +888,11 @@ int dg_group_sorted_rows(const dg_group_sorted_args* a, void* stream) {
   p.a_scale_out = a->a_scale_out;
   p.m_indices_out = a->m_indices_out;
   p.dest_out = a->dest_out;
+  p.src_out = a->src_out;
+  if (a->zero_rows != nullptr && (a->zero_row_bytes < 16 || a->zero_row_bytes % 16 != 0 || !aligned16(a->zero_rows)))
+    return DG_ERR_BAD_ARGUMENT;
+  p.zero_rows = a->zero_rows;
+  p.zero_row_bytes = a->zero_row_bytes;
   p.m_total_out = a->m_total_out;
   p.R = a->num_sorted;
   p.H = a->hidden;

@@ -88,6 +88,9 @@ struct KernelParams {
   // back to the ranks their tokens came from, tile by tile, while the GEMM is still running.
   const int32_t* scatter_tag;
   void* scatter_base[16];
+  // Masked layout only: per (group, 128-row block) completion counters; a finished tile adds the
+  // number of columns it covers, a quarter per epilogue warp (the block is done at N).
+  int32_t* signal;
   int narrow;  // masked / compact: 0 = tiles stay BN columns wide, 1 = the kernel may narrow them
                // (down to 32 columns) when few groups have rows, 128 / 64 / 32 = forced width
 };
@@ -741,7 +744,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       // hand the accumulator back to the UMMA issuer
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+      if (lane == 0) {
+        mbar_arrive(bar_acc_empty(buf));
+        if (p.signal != nullptr && p.mode == MODE_MASKED) {
+          __threadfence();  // this warp's stores (ordered before by __syncwarp) before the count
+          atomicAdd(p.signal + (size_t)t.g * p.m_blocks + t.row0 / kBM, min(t.width, p.N - t.n0) / 4);
+        }
+      }
     }
   }
 

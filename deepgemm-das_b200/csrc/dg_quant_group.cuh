@@ -59,6 +59,9 @@ struct QuantGroupParams {
   float* a_scale_out;
   int32_t* m_indices_out;
   int32_t* dest_out;     // nullable
+  int32_t* src_out;      // nullable, sorted-ids input: src_out[dest] = row of `rows` stored at dest
+  void* zero_rows;       // nullable, sorted-ids input: rows named by blocks whose expert is -1 are
+  int zero_row_bytes;    //   zeroed in this [size_m][zero_row_bytes] buffer (multiple of 16 bytes)
   int32_t* m_total_out;  // nullable
   int32_t* hist;         // scratch: [G][chunks] rows per (expert, chunk); exclusive-scanned in place
   int32_t* starts;       // scratch: [G] totals, then first output row of each expert
@@ -261,20 +264,35 @@ __global__ void __launch_bounds__(kQgThreads) qg_quantise_kernel(const QuantGrou
 // bytes and the (weighted) scale.
 constexpr int kQgCopyThreads = 64;
 __global__ void __launch_bounds__(kQgCopyThreads) qg_copy_kernel(const QuantGroupParams p) {
-  __shared__ int s_dest, s_src, s_expert;
+  __shared__ int s_dest, s_src, s_expert, s_zero;
   const int r = blockIdx.x;
   if (threadIdx.x == 0) {
     s_dest = qg_dest_of(p, r, &s_expert, &s_src);
+    s_zero = -1;
     if (p.dest_out != nullptr && p.sorted_ids == nullptr) p.dest_out[r] = s_dest;
+    if (p.sorted_ids != nullptr && p.zero_rows != nullptr && r < *p.num_post_pad &&
+        p.expert_ids[r / p.block_m] < 0) {
+      // a row of an expert that does not live here: the reference's kernel stores zeros for it
+      const uint32_t id = static_cast<uint32_t>(p.sorted_ids[r]);
+      const int slot = static_cast<int>(id >> 24);
+      const long long row = static_cast<long long>(id & 0x00FFFFFFu) * p.real_topk + slot;
+      if (slot < p.real_topk && row < p.size_m) s_zero = static_cast<int>(row);
+    }
     if (s_dest >= 0) {
       // sorted-ids input: dest is indexed by the source row (one entry per row of `rows`)
       if (p.dest_out != nullptr && p.sorted_ids != nullptr) p.dest_out[s_src] = s_dest;
+      if (p.src_out != nullptr) p.src_out[s_dest] = s_src;
       const float w = p.row_weight ? p.row_weight[s_src] : 1.0f;
       p.a_scale_out[s_dest] = p.row_weight ? __fmul_rn(w, p.row_scale[s_src]) : p.row_scale[s_src];
       p.m_indices_out[s_dest] = s_expert;
     }
   }
   __syncthreads();
+  if (s_zero >= 0) {
+    uint4* z = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.zero_rows) +
+                                        static_cast<size_t>(s_zero) * p.zero_row_bytes);
+    for (int i = threadIdx.x; i < p.zero_row_bytes / 16; i += kQgCopyThreads) z[i] = make_uint4(0, 0, 0, 0);
+  }
   if (s_dest < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.rows) +
                                                     static_cast<size_t>(s_src) * p.H);

@@ -63,6 +63,7 @@ class MaskedArgs(C.Structure):
         ("status", C.c_void_p),
         ("out_kind", C.c_int32),
         ("reserved", C.c_int32),
+        ("signal", C.c_void_p),
     ]
 
 
@@ -178,6 +179,10 @@ class GroupSortedArgs(C.Structure):
         ("m_total_out", C.c_void_p),
         ("scratch", C.c_void_p),
         ("scratch_bytes", C.c_size_t),
+        ("src_out", C.c_void_p),
+        ("zero_rows", C.c_void_p),
+        ("zero_row_bytes", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

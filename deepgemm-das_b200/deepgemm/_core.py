@@ -9,6 +9,7 @@ raise RuntimeError like they do; nothing here computes on the CPU.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -18,6 +19,9 @@ from ._cabi import (KIND_BF16, KIND_E4M3, KIND_I8, KIND_W4A8, SCALE_NONE, SCALE_
                     SCALE_TENSOR_WISE)
 
 _FP8 = torch.float8_e4m3fn
+# (device type, index, data pointer) of every [E, N, K/2] int4 tensor a packer of this package has
+# put into the kernel layout: that shape is shared with the unpacked framework layout
+PACKED_W4A8_STORAGES = set()
 
 # bytes of K per packed row, and elements per row, by kind
 _ROW_ELEMS = {KIND_I8: 128, KIND_E4M3: 128, KIND_BF16: 64, KIND_W4A8: 128}
@@ -35,10 +39,16 @@ def packed_weight_dims(b: torch.Tensor, kind: int, k_hint: Optional[int] = None
 
     Packed weights are 4-D ``[G, K/BK, N, row]`` with row = 128 (8-bit elements, or int4 bytes
     holding 256 values) or 64 (bf16 elements).  W4A8 weights may also be the 3-D ``[G, N, K/2]`` tensor that the reference's
-    in-place packer returns (deepgemm/group_gemm_weight_pack.py:691-714) -- that shape cannot
-    be told apart from an unpacked one, exactly as in the reference.
+    in-place packer returns (deepgemm/group_gemm_weight_pack.py:691-714); since that shape is also
+    the unpacked one, such a tensor is accepted only if a packer of this package marked its storage.
     """
     if kind == KIND_W4A8 and b.dim() == 3:
+        if (b.device.type, b.device.index, b.data_ptr()) not in PACKED_W4A8_STORAGES \
+                and not os.environ.get("DEEPGEMM_TRUST_W4A8_LAYOUT"):
+            raise ValueError(
+                "w4a8 grouped GEMM: this [E, N, K/2] weight has not been through pack_w4a8_moe_hipc_weight "
+                "(the framework layout would be silently mis-read); pack it, or mark a weight packed "
+                "elsewhere with group_gemm_weight_pack.register_packed_w4a8_weight")
         g, n, kh = b.shape
         return int(g), int(n), int(kh) * 2
     if b.dim() != 4 or int(b.shape[3]) != _ROW_ELEMS[kind]:
@@ -171,8 +181,11 @@ def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Te
                         b_scale: Optional[torch.Tensor], masked_m: torch.Tensor,
                         expected_m: int, *, block_n: int = 0,
                         debug_acc: Optional[torch.Tensor] = None,
-                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """d[g, :masked_m[g]] = bf16((A[g] @ B[g]^T) * a_scale[g] * b_scale[g]) via dg_masked_gemm."""
+                        status: Optional[torch.Tensor] = None,
+                        signal: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """d[g, :masked_m[g]] = bf16((A[g] @ B[g]^T) * a_scale[g] * b_scale[g]) via dg_masked_gemm.
+    ``signal``: int32 [G, ceil(max_m / 128)] completion counters (zeroed by the caller); entry
+    (g, mb) reaches N when rows [128 mb, 128 mb + 128) of group g are complete."""
     what = f"masked {KIND_NAMES[kind]} grouped GEMM"
     if not (a.dim() == 3):
         raise RuntimeError(f"{what}: activation must be [G, max_m, K], got {tuple(a.shape)}")
@@ -199,13 +212,19 @@ def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Te
     _debug_and_status(debug_acc, status, g * max_m, n, a.device, what)
     if status is None:
         status = device_status_words(a.device)
+    if signal is not None:
+        if not (signal.is_cuda and signal.device == a.device and signal.dtype == torch.int32
+                and signal.is_contiguous() and signal.numel() == g * ((max_m + 127) // 128)):
+            raise RuntimeError(f"{what}: signal must be contiguous CUDA int32 [{g}, {(max_m + 127) // 128}]")
+        if kind == KIND_W4A8 or n % 32 != 0:
+            raise RuntimeError(f"{what}: completion counters need an INT8 / FP8 / BF16 kind and N % 32 == 0")
 
     args = _cabi.MaskedArgs(
         kind=kind, scale_mode=scale_mode, a=a.data_ptr(), b_packed=b.data_ptr(), d=d.data_ptr(),
         a_scale=_ptr(a_s), b_scale=_ptr(b_s), masked_m=masked_m.data_ptr(), num_groups=g,
         max_m=max_m, n=n, k=k, expected_m=int(expected_m), block_n=int(block_n),
         debug_acc=_ptr(debug_acc), status=_ptr(status),
-        out_kind=_cabi.OUT_F16 if d.dtype == torch.float16 else _cabi.OUT_BF16)
+        out_kind=_cabi.OUT_F16 if d.dtype == torch.float16 else _cabi.OUT_BF16, signal=_ptr(signal))
     _launch(_cabi.lib.dg_masked_gemm, args, a.device, what)
     return d
 

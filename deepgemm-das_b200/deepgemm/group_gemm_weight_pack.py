@@ -26,7 +26,7 @@ from typing import Any, Optional
 
 import torch
 
-from . import _cabi
+from . import _cabi, _core
 from ._cabi import KIND_BF16, KIND_E4M3, KIND_I8, KIND_W4A8, NIBBLE_HIGH_FIRST, NIBBLE_LOW_FIRST
 
 # Layout-mode constants kept for API compatibility (reference :12-33).
@@ -288,6 +288,16 @@ def pack_w4a8_weight_k_contiguous(weight_u4: torch.Tensor) -> torch.Tensor:
     return ((nib[..., 0] << 4) | nib[..., 1]).to(torch.int8)
 
 
+def register_packed_w4a8_weight(weight: torch.Tensor) -> torch.Tensor:
+    """Marks an ``[E,N,K/2]`` int4 tensor as being in the kernel layout.  The packed tensor keeps the
+    framework shape (as the reference's does), so the shape cannot tell the two apart; the W4A8 ops
+    accept a 3-D weight only if its storage was marked here -- the packers do it themselves.  Call
+    it for weights that were packed elsewhere (for example loaded from a file that already holds
+    the kernel layout)."""
+    _core.PACKED_W4A8_STORAGES.add((weight.device.type, weight.device.index, weight.data_ptr()))
+    return weight
+
+
 def pack_w4a8_moe_hipc_weight_inplace(packed_k_contiguous: torch.Tensor, *,
                                       nibble_order="high_first") -> torch.Tensor:
     """Framework int4 bytes ``[E,N,K/2]`` -> kernel layout, in place; the returned tensor keeps
@@ -307,6 +317,7 @@ def pack_w4a8_moe_hipc_weight_inplace(packed_k_contiguous: torch.Tensor, *,
     if n % 16 != 0:
         raise ValueError(f"N must be divisible by 16 for the W4A8 tile layout, got {n}")
     _pack_inplace(packed_k_contiguous, KIND_W4A8, _nibble_order(nibble_order))
+    register_packed_w4a8_weight(packed_k_contiguous)
     return packed_k_contiguous.view(original_shape)
 
 

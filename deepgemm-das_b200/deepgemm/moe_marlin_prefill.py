@@ -7,12 +7,16 @@ Same name, argument order and checks as the reference's ``deepgemm/moe_marlin_pr
 
 for every ``row = token * real_topk + slot`` named by ``sorted_token_ids`` (``slot << 24 | token``,
 blocks of ``len(sorted_token_ids) / len(expert_ids)`` entries per expert), zeros for rows whose
-block has ``expert_ids == -1``.  The reference's kernel gathers 32-row blocks itself; here the
-rows are regrouped into 128-row blocks per expert (``dg_group_sorted_rows``), multiplied by the
-contiguous grouped GEMM and scattered back (``dg_combine_rows``) -- three device steps, with
-temporaries from torch's allocator.  ``b_qweight`` must come from ``marlin_fp8_contiguous_weight``
-/ ``marlin_i8_contiguous_weight`` of this package.  Rows of ``output`` that the list never names
-are written as zeros (the reference leaves them untouched).
+block has ``expert_ids == -1``; rows the list never names are left untouched, as in the
+reference.  The reference's kernel gathers 32-row blocks itself; a tcgen05 tile wants 128 rows of
+one expert, so the rows are first regrouped into 128-row blocks per expert
+(``dg_group_sorted_rows``, which also zeroes the rows of absent experts) and the contiguous
+grouped GEMM then writes every result row straight to its place in ``output`` from its epilogue
+(``scatter_tag``): two device steps, five launches, no pass over the result afterwards.  The
+regrouped operand lives in a workspace kept per problem size, so steady-state calls allocate
+nothing.  ``b_qweight`` must come from ``marlin_fp8_contiguous_weight`` /
+``marlin_i8_contiguous_weight`` of this package; K must be a multiple of 128 (the reference:
+64).
 """
 from __future__ import annotations
 
@@ -65,12 +69,8 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
     dev = input.device
     kind = _cabi.KIND_E4M3 if input.dtype == torch.float8_e4m3fn else _cabi.KIND_I8
     m_cap = quant_group_capacity(em, experts, 128)
-    a = torch.empty((m_cap, size_k), dtype=input.dtype, device=dev)
-    a_s = torch.empty((m_cap,), dtype=torch.float32, device=dev)
-    m_idx = torch.empty((m_cap,), dtype=torch.int32, device=dev)
-    dest = torch.empty((size_m,), dtype=torch.int32, device=dev)
-    need = int(_cabi.lib.dg_quant_group_scratch_bytes(em, experts))
-    scratch = torch.empty((max(need, 16),), dtype=torch.uint8, device=dev)
+    ws = _workspace(dev, m_cap, size_k, em, experts, input.dtype)
+    out2d = output.view(size_m, size_n)
     args = _cabi.GroupSortedArgs(
         num_sorted=em, block_m=em // blocks, size_m=size_m, hidden=size_k, num_groups=experts, align=128,
         m_cap=m_cap, real_topk=int(real_topk), rows=input.data_ptr(),
@@ -78,16 +78,37 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
         sorted_token_ids=sorted_token_ids.contiguous().data_ptr(),
         expert_ids=expert_ids.contiguous().data_ptr(),
         num_tokens_post_pad=num_tokens_post_pad.contiguous().data_ptr(),
-        a_out=a.data_ptr(), a_scale_out=a_s.data_ptr(), m_indices_out=m_idx.data_ptr(),
-        dest_out=dest.data_ptr(), m_total_out=None, scratch=scratch.data_ptr(),
-        scratch_bytes=scratch.numel())
+        a_out=ws["a"].data_ptr(), a_scale_out=ws["a_s"].data_ptr(), m_indices_out=ws["m_idx"].data_ptr(),
+        dest_out=None, m_total_out=None, scratch=ws["scratch"].data_ptr(),
+        scratch_bytes=ws["scratch"].numel(), src_out=ws["src"].data_ptr(),
+        zero_rows=out2d.data_ptr(), zero_row_bytes=size_n * 2, reserved=0)
     _core._launch(_cabi.lib.dg_group_sorted_rows, args, dev, "dg_group_sorted_rows")
-    y = torch.empty((m_cap, size_n), dtype=torch.bfloat16, device=dev)
-    _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, a, b_qweight, y, a_s,
-                                  b_scale.reshape(experts, size_n).contiguous(), m_idx)
-    from .moe_chain import combine_rows
-    combine_rows(y, dest.view(size_m, 1), None, out=output.view(size_m, size_n))
+    # the GEMM's epilogue writes result row i straight to output[src[i]] (tag = buffer 0, row src[i])
+    _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, ws["a"], b_qweight, out2d, ws["a_s"],
+                                  b_scale.reshape(experts, size_n), ws["m_idx"],
+                                  scatter=(ws["src"], _cabi.pointer_array([out2d.data_ptr()]), 1))
     return output
+
+
+_WORKSPACES = {}
+
+
+def _workspace(dev, m_cap, size_k, em, experts, dtype):
+    """The regrouped operand, its scales and index arrays: allocated on the first call for a
+    problem size and kept, so that steady-state calls allocate nothing."""
+    key = (dev.index, m_cap, size_k, em, experts, dtype)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        need = int(_cabi.lib.dg_quant_group_scratch_bytes(em, experts))
+        ws = {"a": torch.empty((m_cap, size_k), dtype=dtype, device=dev),
+              "a_s": torch.empty((m_cap,), dtype=torch.float32, device=dev),
+              "m_idx": torch.empty((m_cap,), dtype=torch.int32, device=dev),
+              "src": torch.zeros((m_cap,), dtype=torch.int32, device=dev),
+              "scratch": torch.empty((max(need, 16),), dtype=torch.uint8, device=dev)}
+        if len(_WORKSPACES) >= 8:          # a handful of layer shapes at most; drop the oldest
+            _WORKSPACES.pop(next(iter(_WORKSPACES)))
+        _WORKSPACES[key] = ws
+    return ws
 
 
 _lib = torch.library.Library("deep_gemm", "FRAGMENT")

@@ -29,28 +29,39 @@ def _define(name: str, schema: str, fn) -> None:
 
 
 # --------------------------------------------------------------------------- masked
+def _check_overlap(b_overlap, signal) -> None:
+    """The reference declares the overlap mode (per row-block completion counters in `signal`,
+    m_grouped_fp8_gemm_nt_maksed_low_latency.cu:1022-1029) and then refuses it at run time
+    (:1148).  Here it works: with b_overlap the counters are maintained (see
+    _core.grouped_gemm_masked); a signal tensor without b_overlap is still an error."""
+    if b_overlap and signal is None:
+        raise RuntimeError("tensor signal empty")                  # the reference's message (:1137)
+    if signal is not None and not b_overlap:
+        raise RuntimeError("signal is only valid together with enable_overlap / b_overlap")
+
+
 def _ll_impl(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
              max_tokens, experts, cu_s, block_wise, b_overlap, signal):
     if block_wise:
         raise RuntimeError("block-wise scales are not supported")
-    if b_overlap or signal is not None:
-        raise RuntimeError("overlap mode / signal is not supported")
+    _check_overlap(b_overlap, signal)
     if int(experts) != int(matrix_a.shape[0]):
         raise RuntimeError(f"experts={experts} does not match matrix_a.shape[0]={matrix_a.shape[0]}")
     kind = _core.kind_of_activation(matrix_a)
     return _core.grouped_gemm_masked(kind, SCALE_PER_CHANNEL, matrix_a, matrix_b, matrix_c,
-                                     matrix_a_scale, matrix_b_scale, actual_tokens, max_tokens)
+                                     matrix_a_scale, matrix_b_scale, actual_tokens, max_tokens,
+                                     signal=signal if b_overlap else None)
 
 
 def _ll_tw_impl(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
                 max_tokens, experts, cu_s, b_overlap, signal):
-    if b_overlap or signal is not None:
-        raise RuntimeError("overlap mode / signal is not supported")
+    _check_overlap(b_overlap, signal)
     if int(experts) != int(matrix_a.shape[0]):
         raise RuntimeError(f"experts={experts} does not match matrix_a.shape[0]={matrix_a.shape[0]}")
     kind = _core.kind_of_activation(matrix_a)
     return _core.grouped_gemm_masked(kind, SCALE_TENSOR_WISE, matrix_a, matrix_b, matrix_c,
-                                     matrix_a_scale, matrix_b_scale, actual_tokens, max_tokens)
+                                     matrix_a_scale, matrix_b_scale, actual_tokens, max_tokens,
+                                     signal=signal if b_overlap else None)
 
 
 _LL_SCHEMA = ("(Tensor matrix_a, Tensor matrix_b, Tensor matrix_a_scale, Tensor matrix_b_scale, "

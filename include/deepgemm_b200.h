@@ -126,6 +126,13 @@ typedef struct dg_masked_args {
   int32_t out_kind;           /* DG_OUT_BF16 (0) or DG_OUT_F16: element type of d.  The reference's W4A8 ops
                                  take half outputs (m_grouped_w4a8_gemm_nt_masked_hipc.cu:1148) */
   int32_t reserved;
+  int32_t*       signal;      /* NULL, or int32 [G][ceil(max_m / 128)] completion counters, zeroed by the
+                                 caller: when a tile of row block mb of group g has been stored,
+                                 signal[g][mb] grows by the number of output columns the tile covers, so
+                                 the rows of that block are complete once it reads N (release ordering:
+                                 a consumer that acquires the value sees the rows).  The overlap hook of
+                                 m_grouped_fp8_gemm_nt_maksed_low_latency.cu:1022-1029 (there +1 per tile,
+                                 and switched off at run time, :1148).  INT8 / FP8 / BF16 kinds. */
 } dg_masked_args;
 
 /* Arguments of the contiguous-layout grouped GEMM.
@@ -340,6 +347,13 @@ typedef struct dg_group_sorted_args {
   int32_t*       m_total_out;         /* NULL, or one int */
   void*          scratch;             /* dg_quant_group_scratch_bytes(num_sorted, num_groups) bytes */
   size_t         scratch_bytes;
+  int32_t*       src_out;             /* NULL, or [m_cap]: src_out[dest] = the row of `rows` stored at dest
+                                         (the scatter_tag of dg_contig_gemm with one output buffer) */
+  void*          zero_rows;           /* NULL, or a [size_m][zero_row_bytes] buffer: every row named by a
+                                         block whose expert_ids entry is -1 is set to zero in it, as the
+                                         reference's kernel stores zeros for such rows */
+  int32_t        zero_row_bytes;      /* multiple of 16 */
+  int32_t        reserved;
 } dg_group_sorted_args;
 
 /* Regroups the rows named by a sorted routing list into the contiguous layout of

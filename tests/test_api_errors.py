@@ -149,3 +149,17 @@ def test_op_size_printer_reports_operands_without_touching_the_call(capsys, monk
     mod.m_grouped_fake_masked(a, w, d, None, None, mm, 64, mode=1)
     assert capsys.readouterr().out == ""
     assert seen == [((4, 64, 256), 1002), ((4, 64, 256), 1)]
+
+
+def test_w4a8_weight_that_was_never_packed_is_rejected():
+    """The packed int4 tensor keeps the framework shape [E, N, K/2]: a tensor that did not go
+    through the packer must not be read as if it had."""
+    from deepgemm import _core, _cabi
+    from deepgemm import group_gemm_weight_pack as P
+    fw = torch.zeros(2, 16, 128, dtype=torch.int8)
+    with pytest.raises(ValueError, match="has not been through"):
+        _core.packed_weight_dims(fw, _cabi.KIND_W4A8)
+    packed = P.pack_w4a8_moe_hipc_weight(fw)
+    assert _core.packed_weight_dims(packed, _cabi.KIND_W4A8) == (2, 16, 256)
+    other = P.register_packed_w4a8_weight(torch.zeros(2, 16, 128, dtype=torch.int8))
+    assert _core.packed_weight_dims(other, _cabi.KIND_W4A8) == (2, 16, 256)

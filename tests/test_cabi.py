@@ -36,7 +36,7 @@ def test_struct_layouts_match_header_field_order():
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = re.findall(r"(\w+)\s*;", body)
         assert fields == [f[0] for f in cls._fields_], (struct, fields)
-    assert ctypes.sizeof(_cabi.MaskedArgs) == 104 and ctypes.sizeof(_cabi.ContigArgs) == 120
+    assert ctypes.sizeof(_cabi.MaskedArgs) == 112 and ctypes.sizeof(_cabi.ContigArgs) == 120
 
 
 def test_query_and_strerror_without_a_device():

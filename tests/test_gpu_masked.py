@@ -210,7 +210,7 @@ def test_fp8_nan_rows_above_masked_m_do_not_leak():
 def test_masked_w4a8_bit_exact(order):
     mm = [0, 256, 17, 130]
     c = gen_masked_w4a8(4, 256, 384, 512, mm, seed=9, nibble_order=order)
-    bp = P.pack_w4a8_moe_hipc_weight(c["b_framework"].clone().to(DEV), nibble_order=order).cpu()
+    bp = P.pack_w4a8_moe_hipc_weight(c["b_framework"].clone().to(DEV), nibble_order=order)
     w_x16 = (c["w4"].to(torch.int16) * 16).to(torch.int8)     # what the kernel multiplies by
     assert torch.equal(w_x16, O.unpack_int4_to_int8_x16(c["b_framework"], order))
     _check_int_case(c, _cabi.KIND_W4A8, w_x16, bp, c["b_scale"] / 16.0, what=f"w4a8 {order}")
@@ -362,7 +362,37 @@ def test_w4a8_random_shapes_bit_exact(seed):
     mm[torch.rand(G, generator=gen) < 0.25] = 0
     order = ("high_first", "low_first")[seed % 2]
     c = gen_masked_w4a8(G, max_m, n, k, mm, seed=6000 + seed, nibble_order=order)
-    bp = P.pack_w4a8_moe_hipc_weight(c["b_framework"].clone().to(DEV), nibble_order=order).cpu()
+    bp = P.pack_w4a8_moe_hipc_weight(c["b_framework"].clone().to(DEV), nibble_order=order)
     w_x16 = (c["w4"].to(torch.int16) * 16).to(torch.int8)
     _check_int_case(c, _cabi.KIND_W4A8, w_x16, bp, c["b_scale"] / 16.0,
                     what=f"seed {seed}: G={G} max_m={max_m} N={n} K={k} masked_m={mm.tolist()} {order}")
+
+
+@pytest.mark.parametrize("tensor_wise", [False, True])
+def test_overlap_mode_completion_counters(tensor_wise):
+    """enable_overlap with a signal tensor: every 128-row block of every expert that has rows ends
+    with N credited (a finished tile adds the columns it covers), blocks without rows stay 0, and
+    the result is the one the plain call gives.  (The reference declares this mode and refuses it at
+    run time: m_grouped_fp8_gemm_nt_maksed_low_latency.cu:1022-1029,1148.)"""
+    G, max_m, N, K = 6, 300, 640, 256
+    mm = [0, 1, 128, 129, 300, 64]
+    c = gen_masked_fp8(G, max_m, N, K, mm, seed=77, tensor_wise=tensor_wise)
+    bp = P.marlin_fp8_masked_weight(c["b"].clone().to(DEV))
+    fn = deepgemm.m_grouped_fp8_gemm_nt_masked_ll_tensor_wise if tensor_wise else deepgemm.m_grouped_fp8_gemm_nt_masked_ll
+    plain = torch.zeros(G, max_m, N, dtype=torch.bfloat16, device=DEV)
+    fn((c["a"].to(DEV), c["a_scale"].to(DEV)), (bp, c["b_scale"].to(DEV)), plain, c["masked_m"].to(DEV), 300)
+    blocks = (max_m + 127) // 128
+    signal = torch.zeros(G, blocks, dtype=torch.int32, device=DEV)
+    d = torch.zeros(G, max_m, N, dtype=torch.bfloat16, device=DEV)
+    fn((c["a"].to(DEV), c["a_scale"].to(DEV)), (bp, c["b_scale"].to(DEV)), d, c["masked_m"].to(DEV), 300,
+       enable_overlap=True, signal=signal)
+    torch.cuda.synchronize()
+    want = torch.tensor([[N if 128 * b < m else 0 for b in range(blocks)] for m in mm], dtype=torch.int32)
+    assert torch.equal(signal.cpu(), want)
+    assert torch.equal(d.view(torch.int16), plain.view(torch.int16))
+    with pytest.raises(RuntimeError, match="signal"):
+        fn((c["a"].to(DEV), c["a_scale"].to(DEV)), (bp, c["b_scale"].to(DEV)), d, c["masked_m"].to(DEV), 300,
+           enable_overlap=True)
+    with pytest.raises(RuntimeError, match="signal"):
+        fn((c["a"].to(DEV), c["a_scale"].to(DEV)), (bp, c["b_scale"].to(DEV)), d, c["masked_m"].to(DEV), 300,
+           signal=signal)

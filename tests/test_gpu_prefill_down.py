@@ -41,7 +41,8 @@ def _run(c, kind, sentinel=3.0):
         c["topk_w"].to(DEV), c["ids"].to(DEV), c["experts"].to(DEV), c["used"].to(DEV), c["k"], c["k"])
     assert r is out
     want = O.ref_prefill_down(c["inp"], c["w"], c["a_scale"], c["b_scale"], c["topk_w"], c["ids"],
-                              c["experts"], c["used"], c["k"], torch.zeros(size_m, n, dtype=torch.bfloat16))
+                              c["experts"], c["used"], c["k"],
+                              torch.full((size_m, n), sentinel, dtype=torch.bfloat16))
     return out.cpu(), want
 
 
@@ -52,6 +53,24 @@ def test_matches_the_block_by_block_oracle(kind, t, k, e, hid, n, block_m):
     c = _case(kind, t, k, e, hid, n, block_m, seed=t + e, extra_blocks=2)
     out, want = _run(c, kind)
     assert_bf16_within_ulp(out, want, 1, f"prefill-down {kind} T={t} top{k} E={e}")
+
+
+def test_rows_the_list_never_names_stay_untouched():
+    """Only the rows named by sorted_token_ids are written (the reference's kernel touches nothing
+    else), so several calls can fill disjoint rows of one output tensor."""
+    c = _case("int8", 96, 4, 6, 256, 512, 32, seed=9)
+    keep = c["ids"].clone()
+    blocks = keep.numel() // 32
+    dropped = keep.view(blocks, 32)[::2].clone()
+    keep.view(blocks, 32)[::2] = (4 << 24)                    # every other block becomes padding (slot >= top-k)
+    c2 = dict(c, ids=keep)
+    out, want = _run(c2, "int8", sentinel=5.0)
+    assert_bf16_within_ulp(out, want, 1, "prefill-down with half of the blocks masked out")
+    rows = ((dropped.long() & 0xFFFFFF) * 4 + (dropped.long() >> 24)).flatten()
+    rows = rows[(dropped.flatten().long() >> 24) < 4]
+    named = ((keep.long() & 0xFFFFFF) * 4 + (keep.long() >> 24))[(keep.long() >> 24) < 4]
+    only_dropped = rows[~torch.isin(rows, named)]
+    assert only_dropped.numel() > 0 and bool((out[only_dropped].float() == 5.0).all())
 
 
 def test_experts_of_other_ranks_give_zero_rows():
