@@ -133,6 +133,11 @@ struct StagesFor {
   static constexpr int value = (200 * 1024) / per_stage;
 };
 
+#ifndef DG_WIDE_STRIPS_ALWAYS
+#define DG_WIDE_STRIPS_ALWAYS 0
+#endif
+constexpr bool kWideStripsAlways = DG_WIDE_STRIPS_ALWAYS != 0;
+
 struct Problem {
   int kind, scale_mode, mode;
   const void* a;
@@ -194,8 +199,16 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   const int table_bytes = pr.mode == MODE_MASKED    ? (2 * pr.G + 1) * 4
                           : pr.mode == MODE_COMPACT ? (3 * pr.G + 1) * 4
                                                     : p.m_blocks * 4;
-  const int smem_bytes = L::total(table_bytes);
+  int smem_bytes = L::total(table_bytes);
   if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
+  // scattered output: wider store strips behind the table when they fit
+  if (pr.scatter_tag != nullptr || kWideStripsAlways) {
+    const int off = (L::off_table + table_bytes + 15) & ~15;
+    if (off + 4 * 4096 + 1024 <= dev.max_smem && off + 4 * 4096 + 1024 <= kMaxSmem) {
+      p.wide_off = off;
+      smem_bytes = off + 4 * 4096 + 1024;
+    }
+  }
 
   // A: rows of K elements.  Masked: (K, max_m, G) so a box never crosses into the next
   // group; contiguous: (K, M_total).  Rows past the extent read as zero.
@@ -315,8 +328,15 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
       (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : 2LL * p.m_blocks) * p.n_tiles;
   if (max_items <= 0) return DG_OK;
   const int table_bytes = (pr.mode == MODE_MASKED) ? (2 * pr.G + 1) * 4 : 2 * p.m_blocks * 4;
-  const int smem_bytes = L::total(table_bytes);
+  int smem_bytes = L::total(table_bytes);
   if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
+  if (pr.scatter_tag != nullptr || kWideStripsAlways) {
+    const int off = (L::off_table + table_bytes + 15) & ~15;
+    if (off + 4 * 4096 + 1024 <= dev.max_smem && off + 4 * 4096 + 1024 <= kMaxSmem) {
+      p.wide_off = off;
+      smem_bytes = off + 4 * 4096 + 1024;
+    }
+  }
 
   const CUtensorMapDataType dt_a =
       (KIND == DG_KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;

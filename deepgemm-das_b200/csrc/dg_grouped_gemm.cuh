@@ -91,6 +91,7 @@ struct KernelParams {
   // Masked layout only: per (group, 128-row block) completion counters; a finished tile adds the
   // number of columns it covers, a quarter per epilogue warp (the block is done at N).
   int32_t* signal;
+  int wide_off;  // 0, or offset in shared memory of four 32-row x 128-byte store strips (scattered output)
   int narrow;  // masked / compact: 0 = tiles stay BN columns wide, 1 = the kernel may narrow them
                // (down to 32 columns) when few groups have rows, 128 / 64 / 32 = forced width
 };
@@ -232,6 +233,7 @@ struct EpiWarp {
   int lane;
   __nv_bfloat16* lane_row = nullptr;  // scattered output: where this lane's row goes (&dst[row][n0])
   bool scatter = false;               // warp-uniform
+  uint8_t* wide_strip = nullptr;      // optional 32 rows x 128 bytes: 64 columns per pass (see epilogue_store64_staged)
 };
 
 // Coalesced form of epilogue_store32: every lane converts its row's 32 columns into the warp's
@@ -261,6 +263,38 @@ __device__ __forceinline__ void epilogue_store32_staged(const uint32_t (&r)[32],
           *reinterpret_cast<const uint4*>(w.strip + row * 64 + ((p ^ ((row >> 1) & 3)) << 4));
   }
   __syncwarp();  // the strip is rewritten by the next chunk
+}
+
+// Two chunks (64 columns) at once through a 32-row x 128-byte strip: a store instruction then
+// covers 4 rows x 128 contiguous bytes.  Used when the rows go to peer GPUs (scattered output):
+// a 128-byte write carries half the per-packet overhead of a 64-byte one over NVLink.  Piece
+// index XOR row % 8 keeps writes and reads free of bank conflicts.
+template <bool kIntAcc>
+__device__ __forceinline__ void epilogue_store64_staged(const uint32_t (&ra)[32], const uint32_t (&rb)[32],
+                                                        const EpiRow& e, const EpiWarp& w, int scale_mode,
+                                                        int col, int cols_left) {
+  const int swz = w.lane & 7;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    *reinterpret_cast<uint4*>(w.wide_strip + w.lane * 128 + ((p ^ swz) << 4)) =
+        epilogue_pack8<kIntAcc>(ra, 8 * p, e, scale_mode, col);
+    *reinterpret_cast<uint4*>(w.wide_strip + w.lane * 128 + (((4 + p) ^ swz) << 4)) =
+        epilogue_pack8<kIntAcc>(rb, 8 * p, e, scale_mode, col + 32);
+  }
+  __syncwarp();
+  const int p = w.lane & 7;
+#pragma unroll
+  for (int h = 0; h < 8; ++h) {
+    const int row = (w.lane >> 3) + 4 * h;
+    __nv_bfloat16* dst = w.d_warp + row * w.ld;
+    if (w.scatter)
+      dst = reinterpret_cast<__nv_bfloat16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(w.lane_row), row));
+    if (8 * p + 8 <= cols_left && ((w.rv_mask >> row) & 1u))
+      *reinterpret_cast<uint4*>(dst + col + 8 * p) =
+          *reinterpret_cast<const uint4*>(w.wide_strip + row * 128 + ((p ^ (row & 7)) << 4));
+  }
+  __syncwarp();  // the strip is rewritten by the next pass
 }
 
 // TMA coordinates of the weight tile of K block kb: packed layout = flat list of 128-byte rows
@@ -338,6 +372,22 @@ __device__ __forceinline__ void epilogue_drain(uint32_t t_row, int nchunks, bool
       epilogue_store32_scalar<kIntAcc>(r, row, scale_mode, c * 32, cols_left0 - c * 32, out_kind);
   };
   uint32_t ra[32], rb[32];
+  if (staged && ew.wide_strip != nullptr) {  // warp-uniform: 64 columns per pass
+    int c = 0;
+#pragma unroll 1
+    for (; c + 1 < nchunks; c += 2) {
+      tmem_ld_32x32(t_row + c * 32, ra);
+      tmem_ld_32x32(t_row + (c + 1) * 32, rb);
+      tmem_ld_wait();
+      epilogue_store64_staged<kIntAcc>(ra, rb, row, ew, scale_mode, c * 32, cols_left0 - c * 32);
+    }
+    if (c < nchunks) {
+      tmem_ld_32x32(t_row + c * 32, ra);
+      tmem_ld_wait();
+      store(ra, c);
+    }
+    return;
+  }
   if (nchunks > 0) tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
   for (int c = 0; c < nchunks; c += 2) {
@@ -738,6 +788,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         ew.lane = lane;
         ew.scatter = scatter;
         ew.lane_row = row.d_row;
+        if (p.wide_off) ew.wide_strip = smem + p.wide_off + q * 4096;
         epilogue_drain<kIntAcc>(t_row, min(t.width / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
                                 cols_left0, scalar_out, p.out_kind);
       }

@@ -400,6 +400,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         ew.lane = lane;
         ew.scatter = scatter;
         ew.lane_row = row.d_row;
+        if (p.wide_off) ew.wide_strip = smem + p.wide_off + q * 4096;
         epilogue_drain<kIntAcc>(t_row, min(kPairBN / 32, (cols_left0 + 31) / 32), rv, row, ew, p.scale_mode,
                                 cols_left0, false, 0);
       }
