@@ -478,13 +478,12 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
     parity = _ep_parity(out, hidden, topk, weights, device, cfg)
 
     # ---- its phases, each timed on its own (a barrier closes every phase that writes to peers)
-    q, q_scale = x.quantise(hidden)
-    quant_ms = timed(lambda: x.quantise(hidden))
+    quant_ms = 0.0            # fused into the push
     plan_ms = timed(lambda: x.plan(topk))
 
     def push():
         x.plan(topk)          # hands out the rows again
-        x.push(q, q_scale, topk)
+        x.push(hidden, None, topk)
         x.barrier()
     push_ms = timed(push) - plan_ms
     kind = _cabi.KIND_E4M3
@@ -536,10 +535,11 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
            "valid_rows_this_rank": valid, "m_total_this_rank": m_total,
            "parity": "ok" if ok_ranks == world else "FAILED", "parity_rank0": parity,
            "layer_ms": layer_ms,
-           "layer": {"exchange": "peer-memory stores (dg_ep_plan / dg_ep_push / dg_ep_barrier), result rows "
-                                 "scattered home by the down GEMM's epilogue; no host synchronisation",
-                     "quantise_tokens_ms": quant_ms, "plan_counts_exchange_ms": plan_ms,
-                     "push_rows_and_barrier_ms": push_ms,
+           "layer": {"exchange": "peer-memory stores (dg_ep_plan / dg_ep_push with the per-token quantisation "
+                                 "fused in / dg_ep_barrier), result rows scattered home by the down GEMM's "
+                                 "epilogue; no host synchronisation",
+                     "plan_counts_exchange_ms": plan_ms,
+                     "quantise_push_rows_and_barrier_ms": push_ms,
                      "push_remote_gbs_max_rank": float(mx) * (K + 8) / (push_ms * 1e-3) / 1e9 if world > 1 else None,
                      "gate_up_gemm_ms": gemm_ms, "silu_mul_quant_ms": act_ms,
                      "down_gemm_scatter_and_barrier_ms": down_ms, "down_gemm_local_store_ms": down_local_ms,

@@ -1076,8 +1076,12 @@ int dg_ep_push(const dg_ep_push_args* a, void* stream) {
   if (a->row_bytes > 16 * dg::kEpPushThreads * dg::kEpMaxChunksPerThread || a->num_experts > DG_MAX_GROUPS ||
       (long long)a->num_tokens * a->top_k >= (1 << 24))
     return DG_ERR_TOO_LARGE;
+  if (a->quantise < 0 || a->quantise > DG_EP_QUANT_I8) return DG_ERR_BAD_ARGUMENT;
+  if (a->quantise != 0 && (a->row_bytes % 8 != 0 || a->row_bytes > 8 * dg::kEpPushThreads * dg::kEpMaxVec))
+    return DG_ERR_BAD_SHAPE;
   if (a->num_tokens == 0) return DG_OK;
-  if (!a->rows || !a->row_scale || !a->topk_ids || !a->my_base || !a->cursor) return DG_ERR_NULL_POINTER;
+  if (!a->rows || (!a->row_scale && a->quantise == 0) || !a->topk_ids || !a->my_base || !a->cursor)
+    return DG_ERR_NULL_POINTER;
   if (!aligned16(a->rows)) return DG_ERR_BAD_ALIGNMENT;
   const DeviceInfo* dev = nullptr;
   int rc = device_info(&dev);
@@ -1105,7 +1109,12 @@ int dg_ep_push(const dg_ep_push_args* a, void* stream) {
   p.status = a->status;
   const int max_blocks = dev->sm_count * 8;
   const int grid = a->num_tokens < max_blocks ? a->num_tokens : max_blocks;
-  dg::ep_push_kernel<<<grid, dg::kEpPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (a->quantise == DG_EP_QUANT_E4M3)
+    dg::ep_push_quant_kernel<DG_KIND_E4M3><<<grid, dg::kEpPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else if (a->quantise == DG_EP_QUANT_I8)
+    dg::ep_push_quant_kernel<DG_KIND_I8><<<grid, dg::kEpPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    dg::ep_push_kernel<<<grid, dg::kEpPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);

@@ -16,6 +16,9 @@
 //                      the destination row of each of its top-k experts (16-byte stores to peer
 //                      memory), with its scale and a tag (source rank << 24 | pair index) that
 //                      the second GEMM's epilogue uses to send the result row home.
+//   ep_push_quant_kernel  the same with the per-token quantisation fused in: the token's bf16 row
+//                      is read once, quantised in registers (the arithmetic of qg_quantise_kernel)
+//                      and its e4m3 / int8 bytes go to the top-k destinations.
 //   ep_barrier_kernel  fence + signal + wait: every rank's earlier stores have landed.
 //
 // Signals are monotonically increasing epoch numbers in one int per (rank, peer), so a signal
@@ -28,6 +31,7 @@
 #include <stdint.h>
 
 #include "deepgemm_b200.h"
+#include "dg_moe_chain.cuh"
 #include "dg_ptx.cuh"
 
 namespace dg {
@@ -219,6 +223,85 @@ __global__ void __launch_bounds__(kEpPushThreads) ep_push_kernel(const EpPushPar
         if (tid + c * kEpPushThreads < chunks) dst[tid + c * kEpPushThreads] = v[c];
     }
     __syncthreads();  // dest_s is rewritten for the next token
+  }
+}
+
+// bf16 rows in, quantised rows out.  p.rows holds bf16 [T][row_bytes] (row_bytes = elements per
+// row = bytes per quantised row, a multiple of 8, at most 8 * 256 * kEpMaxVec); p.row_scale is
+// not read.
+constexpr int kEpMaxVec = 4;
+template <int KIND>
+__global__ void __launch_bounds__(kEpPushThreads) ep_push_quant_kernel(const EpPushParams p) {
+  static_assert(kEpPushThreads == kQgThreads, "qg_block_max reduces over kQgThreads threads");
+  __shared__ float red[kEpPushThreads / 32];
+  __shared__ int32_t dest_s[kEpMaxTopK];
+  const int tid = threadIdx.x;
+  const int nvec = p.row_bytes >> 3;  // 16-byte vectors of 8 bf16
+  constexpr float kQmax = (KIND == DG_KIND_E4M3) ? 448.0f : 127.0f;
+  for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.rows) +
+                                                      (size_t)t * p.row_bytes);
+    uint4 v[kEpMaxVec];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kEpMaxVec; ++i) {
+      const int idx = tid + i * kEpPushThreads;
+      if (idx < nvec) {
+        v[i] = __ldg(src + idx);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(h[k]);
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+      }
+    }
+    amax = fmaxf(qg_block_max(amax, red), 1e-10f);
+    const float inv = __fmul_rn(__frcp_rn(amax), kQmax);  // as torch evaluates qmax / absmax
+    if (tid < p.top_k) {
+      const int e = p.topk_ids[(size_t)t * p.top_k + tid];
+      int dest = -1;
+      if (e >= 0 && e < p.E) {
+        dest = p.my_base[e] + atomicAdd(&p.cursor[e], 1);
+        if (dest >= p.m_cap) {
+          dest = -1;
+          if (p.status != nullptr) atomicCAS(p.status, DG_DEV_OK, DG_DEV_BAD_GROUP_INDEX);
+        }
+      }
+      dest_s[tid] = dest;
+      if (p.pair_dest != nullptr) p.pair_dest[(size_t)t * p.top_k + tid] = dest;
+      if (dest >= 0) {
+        const int r = e / p.e_local;
+        static_cast<float*>(p.peer_scale.ptr[r])[dest] = __fdiv_rn(amax, kQmax);
+        static_cast<int32_t*>(p.peer_tag.ptr[r])[dest] = (p.me << 24) | (t * p.top_k + tid);
+      }
+    }
+    uint2 q[kEpMaxVec];
+#pragma unroll
+    for (int i = 0; i < kEpMaxVec; ++i) {
+      if (tid + i * kEpPushThreads < nvec) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+        float x[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(h[k]);
+          x[2 * k] = f.x * inv;
+          x[2 * k + 1] = f.y * inv;
+        }
+        q[i] = quantise8<KIND>(x);
+      }
+    }
+    __syncthreads();
+    for (int j = 0; j < p.top_k; ++j) {
+      const int dest = dest_s[j];
+      if (dest < 0) continue;
+      const int r = p.topk_ids[(size_t)t * p.top_k + j] / p.e_local;
+      uint2* dst = reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.peer_a.ptr[r]) + (size_t)dest * p.row_bytes);
+#pragma unroll
+      for (int i = 0; i < kEpMaxVec; ++i)
+        if (tid + i * kEpPushThreads < nvec) dst[tid + i * kEpPushThreads] = q[i];
+    }
+    __syncthreads();  // dest_s and red are rewritten for the next token
   }
 }
 

@@ -215,6 +215,7 @@ class CombineArgs(C.Structure):
 
 EP_MAX_WORLD = 16
 EP_PHASE_POST, EP_PHASE_WAIT = 1, 2
+EP_QUANT_NONE, EP_QUANT_E4M3, EP_QUANT_I8 = 0, 1, 2
 
 
 class EpPlanArgs(C.Structure):
@@ -247,7 +248,7 @@ class EpPushArgs(C.Structure):
         ("top_k", C.c_int32),
         ("row_bytes", C.c_int32),
         ("m_cap", C.c_int32),
-        ("reserved", C.c_int32),
+        ("quantise", C.c_int32),
         ("rows", C.c_void_p),
         ("row_scale", C.c_void_p),
         ("topk_ids", C.c_void_p),

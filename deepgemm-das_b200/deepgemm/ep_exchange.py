@@ -9,10 +9,10 @@ This module is the device-side form: every rank maps one buffer of every other r
 grouped, padded activation buffer; the second GEMM's epilogue writes every result row straight
 back into the buffer of the rank the token came from (``scatter_tag`` of ``dg_contig_gemm``), so
 the return transfer overlaps the GEMM tile by tile and the final weighted sum is a local read.
-A layer is nine launches on one stream and never synchronises with the host:
+A layer is eight launches on one stream and never synchronises with the host:
 
-    quantise rows -> plan (counts exchange) -> push -> barrier -> gate/up GEMM ->
-    SiLU*up + requantise -> down GEMM (scattering) -> barrier -> weighted top-k sum
+    plan (counts exchange) -> push (quantising each token on the way out) -> barrier ->
+    gate/up GEMM -> SiLU*up + requantise -> down GEMM (scattering) -> barrier -> weighted top-k sum
 
 With one rank the same code runs on plain tensors.  ``make_emulated_ranks`` plays several ranks
 on one GPU for tests (every phase of all ranks is enqueued before the next phase).
@@ -65,7 +65,8 @@ class EPExchange:
     down GEMM; ``inter2`` = columns of the gate/up GEMM (gate | up).  ``m_cap``: rows of every
     rank's receive buffer (the same on all ranks); pairs that do not fit are dropped and
     reported through ``check_status``.  The exchange buffers and the GEMM intermediates are
-    allocated here, once; in ``forward`` only the per-token quantisation allocates its outputs.
+    allocated here, once; ``forward`` allocates nothing (rows longer than 8192 elements take a
+    separate quantisation step that allocates its outputs).
     """
 
     _ALIGN = 256
@@ -163,13 +164,22 @@ class EPExchange:
             status=self.status.data_ptr())
         _launch(_cabi.lib.dg_ep_plan, args, self.device, "dg_ep_plan")
 
-    def push(self, q: torch.Tensor, q_scale: torch.Tensor, topk_ids: torch.Tensor) -> None:
-        """Writes every routed row into its owner's receive buffer (``dg_ep_push``)."""
+    def push(self, q: torch.Tensor, q_scale: Optional[torch.Tensor], topk_ids: torch.Tensor) -> None:
+        """Writes every routed row into its owner's receive buffer (``dg_ep_push``).  ``q`` holds the
+        quantised rows and ``q_scale`` their scales, or ``q`` holds the bf16 rows and ``q_scale`` is
+        None: the kernel then quantises each token on the way out."""
         t, k = topk_ids.shape
+        if q_scale is None:
+            if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[1] != self.hidden:
+                raise ValueError("rows to quantise must be a contiguous bf16 [T, hidden] tensor")
+            quantise = _cabi.EP_QUANT_E4M3 if self.kind == "fp8" else _cabi.EP_QUANT_I8
+        else:
+            quantise = _cabi.EP_QUANT_NONE
         args = _cabi.EpPushArgs(
             world=self.world, rank=self.rank, num_experts=self.num_experts, num_tokens=t, top_k=k,
-            row_bytes=self.hidden, m_cap=self.m_cap, reserved=0, rows=q.data_ptr(),
-            row_scale=q_scale.data_ptr(), topk_ids=topk_ids.data_ptr(), my_base=self.my_base.data_ptr(),
+            row_bytes=self.hidden, m_cap=self.m_cap, quantise=quantise, rows=q.data_ptr(),
+            row_scale=q_scale.data_ptr() if q_scale is not None else None,
+            topk_ids=topk_ids.data_ptr(), my_base=self.my_base.data_ptr(),
             cursor=self.cursor.data_ptr(), peer_a=self._peer["recv_a"], peer_scale=self._peer["recv_scale"],
             peer_tag=self._peer["recv_tag"], pair_dest=self.pair_dest.data_ptr(),
             status=self.status.data_ptr())
@@ -213,9 +223,11 @@ class EPExchange:
             raise ValueError("topk_ids must be contiguous int32 [T, top_k]")
         if topk_ids.shape[0] > self.max_tokens or topk_ids.shape[1] != self.top_k:
             raise ValueError("more tokens than the exchange was sized for, or another top_k")
-        q, q_scale = self.quantise(hidden)
         self.plan(topk_ids)
-        self.push(q, q_scale, topk_ids)
+        if self.hidden <= 8192:
+            self.push(hidden, None, topk_ids)           # quantised on the way out
+        else:
+            self.push(*self.quantise(hidden), topk_ids)
         self.barrier()
         self.experts(w13, w2)
         self.barrier()
@@ -248,13 +260,15 @@ def emulated_forward(ranks: Sequence[EPExchange], hidden: Sequence[torch.Tensor]
                      w13: Sequence, w2: Sequence) -> List[torch.Tensor]:
     """One layer of every emulated rank, phase by phase (the posting half of each barrier for all
     ranks before any waiting half)."""
-    qs = [r.quantise(h) for r, h in zip(ranks, hidden)]
     for r, ids in zip(ranks, topk_ids):
         r.plan(ids, _cabi.EP_PHASE_POST)
     for r, ids in zip(ranks, topk_ids):
         r.plan(ids, _cabi.EP_PHASE_WAIT)
-    for r, (q, s), ids in zip(ranks, qs, topk_ids):
-        r.push(q, s, ids)
+    for i, (r, h, ids) in enumerate(zip(ranks, hidden, topk_ids)):
+        if i % 2 == 0 and r.hidden <= 8192:
+            r.push(h, None, ids)                    # quantised on the way out
+        else:
+            r.push(*r.quantise(h), ids)             # quantised first: the same bytes
     for ph in (_cabi.EP_PHASE_POST, _cabi.EP_PHASE_WAIT):
         for r in ranks:
             r.barrier(ph)

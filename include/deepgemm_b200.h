@@ -457,6 +457,8 @@ DG_API int dg_quant_group_rows_noalloc(const dg_quant_group_args* args, void* st
  * run at the same time on one GPU. */
 #define DG_EP_PHASE_POST 1
 #define DG_EP_PHASE_WAIT 2
+#define DG_EP_QUANT_E4M3 1
+#define DG_EP_QUANT_I8   2
 
 typedef struct dg_ep_plan_args {
   int32_t world;              /* ranks, 1..DG_EP_MAX_WORLD */
@@ -489,7 +491,10 @@ typedef struct dg_ep_push_args {
   int32_t top_k;              /* <= 32 */
   int32_t row_bytes;          /* bytes per quantised row, multiple of 16, <= DG_MAX_QUANT_HIDDEN */
   int32_t m_cap;
-  int32_t reserved;
+  int32_t quantise;           /* 0: `rows` holds quantised bytes and row_scale their scales;
+                                 DG_EP_QUANT_E4M3 / DG_EP_QUANT_I8: `rows` holds bf16 [T][row_bytes]
+                                 elements (row_bytes % 8 == 0, <= 8192) and each token is quantised
+                                 on the way out exactly as dg_quant_group_rows would (row_scale unused) */
   const void*    rows;        /* [T][row_bytes] this rank's tokens, quantised once per token */
   const float*   row_scale;   /* [T] */
   const int32_t* topk_ids;    /* [T][top_k] */
