@@ -4,7 +4,6 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
-#include <cstdlib>
 #include <mutex>
 
 #include "deepgemm_b200.h"
@@ -517,9 +516,6 @@ int launch_w4_smem(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream
   if (stages < 2) return DG_ERR_TOO_LARGE;
   p.pack_stages = stages;
   p.pack_off = L::pack_offset(table_bytes);
-#ifdef DG_WS_PROF
-  if (const char* e = getenv("DG_PROF_PTR")) p.prof = reinterpret_cast<unsigned long long*>(strtoull(e, nullptr, 16));
-#endif
   const int smem_bytes = L::total(table_bytes, stages);
 
   // Token tiles: boxes of 128, 64, 32 and 8 rows, so an item fetches little more than its rows.

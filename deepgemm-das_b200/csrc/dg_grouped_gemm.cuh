@@ -77,9 +77,6 @@ struct KernelParams {
   int out_kind;    // 0 = bf16 output; 1 = fp16, 2 = fp32 (dense GEMM only, scalar stores)
   int split_tail;  // masked / compact: 1 = the items of a last round that is at most half full are
                    // split into two halves of BN / 2 columns
-#ifdef DG_WS_PROF
-  unsigned long long* prof;
-#endif
   int pack_stages;  // W4A8: stages of the packed-weight ring
   int pack_off;     // W4A8: offset of that ring in the block's shared memory
   // Contiguous layout only: when scatter_tag is given, output row i is written to row

@@ -38,16 +38,6 @@
 
 #include "dg_grouped_gemm.cuh"
 
-#ifdef DG_WS_PROF
-#define WS_PROF_DECL long long prof_t0 = 0; (void)prof_t0
-#define WS_PROF_T0() prof_t0 = clock64()
-#define WS_PROF_ADD(idx) do { if (blockIdx.x == 3 && p.prof) atomicAdd(p.prof + (idx), (unsigned long long)(clock64() - prof_t0)); } while (0)
-#else
-#define WS_PROF_DECL
-#define WS_PROF_T0()
-#define WS_PROF_ADD(idx)
-#endif
-
 namespace dg {
 
 constexpr int kWsBN = 256;                            // output channels per work item
@@ -244,7 +234,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
   if (warp == 0) {
     if (lane == 0) {
       // ---- weight producer: the packed half rows of one K block per stage, streamed once
-      WS_PROF_DECL;
       const uint64_t pol_w = l2_policy_evict_first();
       ItemDecoder dec(p, tbl, kWsBN, p.n_tiles, split_from);
       int ps = 0;
@@ -256,12 +245,10 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const uint32_t bytes = static_cast<uint32_t>(t.width) * 64u;
         const int row0 = t.g * (kblocks >> 1) * p.N + t.n0;  // packed row of K block 0
         for (int kb = 0; kb < kblocks; ++kb) {
-          WS_PROF_T0();
           if (!mbar_wait_bounded(bar_pempty(ps), pph ^ 1u, abort_flag, SITE_WS_PACK_EMPTY)) {
             ok = false;
             break;
           }
-          WS_PROF_ADD(0);
           mbar_arrive_expect_tx(bar_pfull(ps), bytes);
           tma_load_2d(pack_base + ps * kWsPackStageBytes, tm, bar_pfull(ps), (kb & 1) * 64,
                       row0 + (kb >> 1) * p.N, pol_w);
@@ -275,7 +262,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
   } else if (warp == kWsTokWarp) {
     if (lane == 0) {
       // ---- token producer: one [rows][128 B] activation tile per K block (L2 resident)
-      WS_PROF_DECL;
       const uint64_t pol_tok = l2_policy_evict_last();
       ItemDecoder dec(p, tbl, kWsBN, p.n_tiles, split_from);
       int u = 0;
@@ -288,12 +274,10 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
                                 : (a_rows == 64 ? &tm_tok64 : (a_rows == 32 ? &tm_tok32 : &tm_tok8));
         const uint32_t bytes = static_cast<uint32_t>(a_rows) * kRowBytes;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          WS_PROF_T0();
           if (!wait_consumed(it, TOKS, SITE_WS_TOK_EMPTY)) {
             ok = false;
             break;
           }
-          WS_PROF_ADD(1);
           mbar_arrive_expect_tx(bar_tfull(u), bytes);
           const uint32_t dst = base + L::off_tok + u * kWsTokBytes;
           if (p.mode == MODE_MASKED)
@@ -309,7 +293,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
       // ---- barrier watcher: waits in the UMMA thread's place and publishes, in plain
       // shared-memory words, how many items (accumulator free, instruction descriptor posted)
       // and K blocks (tokens and unpacked weights in place) may be issued
-      WS_PROF_DECL;
       ItemDecoder dec(p, tbl, kWsBN, p.n_tiles, split_from);
       int u = 0, a = 0;
       uint32_t uph = 0, tph = 0, it = 0, tile = 0;
@@ -321,26 +304,20 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const uint32_t idesc = (kIdescBase & ~(0x3Fu << 17) & ~(0x1Fu << 24)) |
                                (static_cast<uint32_t>(t.width >> 3) << 17) |
                                ((t.rows_valid <= 64 ? 4u : 8u) << 24);
-        WS_PROF_T0();
         if (!mbar_wait_bounded(bar_acc_empty(tile & 1u), ((tile >> 1) & 1u) ^ 1u, abort_flag,
                                SITE_MMA_ACC_EMPTY))
           break;
-        WS_PROF_ADD(2);
         idesc_ring[tile & 7u] = idesc;
         asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(items_addr), "r"(tile + 1u) : "memory");
         for (int kb = 0; kb < kblocks; ++kb) {
-          WS_PROF_T0();
           if (!mbar_wait_bounded(bar_tfull(a), tph, abort_flag, SITE_WS_TOK_FULL)) {
             ok = false;
             break;
           }
-          WS_PROF_ADD(3);
-          WS_PROF_T0();
           if (!mbar_wait_bounded(bar_sfull(u), uph, abort_flag, SITE_MMA_FULL)) {
             ok = false;
             break;
           }
-          WS_PROF_ADD(4);
           ++it;
           asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(ready_addr), "r"(it) : "memory");
           if (++u == SLOTS) {
@@ -380,26 +357,19 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
           }
         }
       };
-      WS_PROF_DECL;
       int u = 0, a = 0;
       uint32_t it = 0, tile = 0, ready_known = 0, items_known = 0;
       bool ok = true;
-#ifdef DG_WS_PROF
-      const long long mma_start = clock64();
-#endif
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++tile) {
-        WS_PROF_T0();
         if (items_known <= tile && (items_known = poll_above(items_addr, tile, SITE_MMA_ACC_EMPTY)) == 0) {
           ok = false;
           break;
         }
-        WS_PROF_ADD(5);
         const uint32_t idesc = idesc_ring[tile & 7u];
         const uint32_t buf = tile & 1u;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kWsBN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          WS_PROF_T0();
           if (ready_known <= it) {
             if ((ready_known = poll_above(ready_addr, it, SITE_MMA_FULL)) == 0) {
               ok = false;
@@ -407,8 +377,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
             }
             tc_fence_after_sync();
           }
-          WS_PROF_ADD(6);
-          WS_PROF_T0();
           const uint64_t a_desc = umma_desc_sw128(base + L::off_tok + a * kWsTokBytes);
           const uint64_t b_desc = umma_desc_sw128(base + L::off_slot + u * kWsSlotBytes);
 #pragma unroll
@@ -417,16 +385,9 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
           umma_commit(bar_cons(it % kCons));  // frees the slot and the token tile once these UMMAs have read them
           if (++u == SLOTS) u = 0;
           if (++a == TOKS) a = 0;
-          WS_PROF_ADD(7);
         }
         if (ok) umma_commit(bar_acc_full(buf));
       }
-#ifdef DG_WS_PROF
-      if (blockIdx.x == 3 && p.prof) {
-        p.prof[8] = (unsigned long long)(clock64() - mma_start);
-        p.prof[9] = it;
-      }
-#endif
       if (*abort_flag) {
         int local_abort = 0;
         umma_commit(bar_drain);
@@ -435,7 +396,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
     }
   } else if (warp < kWsTokWarp) {
     // ---- epilogue: this warp may touch TMEM lanes [32q, 32q+32); same as grouped_gemm_kernel
-    WS_PROF_DECL;
     const int q = warp & 3;
     ItemDecoder dec(p, tbl, kWsBN, p.n_tiles, split_from);
     uint32_t tile = 0;
@@ -462,10 +422,7 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (rv) row.as = p.a_scale[grow];
         if (p.scale_mode == DG_SCALE_TENSOR_WISE) row.bs_g = p.b_scale[t.g];
       }
-      WS_PROF_T0();
       if (!mbar_wait_warp(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
-      if (q == 0 && lane == 0) WS_PROF_ADD(10);
-      WS_PROF_T0();
       tc_fence_after_sync();
       if (warp_has_rows) {
         row.bs_row = bs_s;
@@ -486,7 +443,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (q == 0 && lane == 0) WS_PROF_ADD(11);
       if (lane == 0) mbar_arrive(bar_acc_empty(buf));
     }
   } else if (warp >= kWsUnpWarp0 && warp < kWsChkWarp) {
@@ -508,7 +464,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
     const uint32_t hi_off = static_cast<uint32_t>(r * 128 + (((2 * (lane & 3)) ^ r) << 4));
     const uint32_t lo_off = static_cast<uint32_t>(r * 128 + (((2 * (lane & 3) + 1) ^ r) << 4));
     constexpr int kMaxIters = kWsBN / 8 / WPG;  // row groups per warp and K block
-    WS_PROF_DECL;
     ItemDecoder dec(p, tbl, kWsBN, p.n_tiles, split_from);
     int ps = 0, u = 0;
     uint32_t pph = 0, it = 0;
@@ -518,13 +473,10 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
       const int groups = t.width >> 3;
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         if (it % NG == g) {
-          WS_PROF_T0();
           if (!mbar_wait_warp(bar_pfull(ps), pph, abort_flag, SITE_WS_PACK_FULL)) {
             ok = false;
             break;
           }
-          if (w == 0 && lane == 0) WS_PROF_ADD(12);
-          WS_PROF_T0();
           const uint32_t src = pack_base + ps * kWsPackStageBytes + src_off;
           uint4 v[kMaxIters];
 #pragma unroll
@@ -538,14 +490,10 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
           }
           __syncwarp();  // the packed rows are in registers: hand the stage back
           if (lane == 0) mbar_arrive(bar_pempty(ps));
-          if (w == 0 && lane == 0) WS_PROF_ADD(13);
-          WS_PROF_T0();
           if (!__all_sync(0xffffffffu, wait_consumed(it, SLOTS, SITE_WS_SLOT_EMPTY))) {
             ok = false;
             break;
           }
-          if (w == 0 && lane == 0) WS_PROF_ADD(14);
-          WS_PROF_T0();
           const uint32_t dst = base + L::off_slot + u * kWsSlotBytes;
 #pragma unroll
           for (int j = 0; j < kMaxIters; ++j) {
@@ -565,7 +513,6 @@ grouped_gemm_w4_smem_kernel(const __grid_constant__ CUtensorMap tm_tok,
           fence_proxy_async_smem();  // generic-proxy stores before the tensor core's reads
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_sfull(u));
-          if (w == 0 && lane == 0) WS_PROF_ADD(15);
         }
         if (++ps == P) {
           ps = 0;

@@ -188,10 +188,12 @@ def test_random_group_sizes_and_tile_choices_bit_exact(seed):
                        what=f"seed {seed}: rows={rows} N={n} K={k} align={align} BN={bn} cut={cut}")
 
 
+@pytest.mark.parametrize("block_n", [0, 512])
 @pytest.mark.parametrize("seed", range(6))
-def test_contiguous_w4a8_random_group_sizes(seed):
+def test_contiguous_w4a8_random_group_sizes(seed, block_n):
     """Seeded random contiguous W4A8 cases: ragged groups (empty ones included) padded to 128
-    rows, N not a multiple of the 128-channel tile, one to four 256-value rounds of K."""
+    rows, N not a multiple of the channel tile, one to four 256-value rounds of K; with the default
+    kernel (block_n 0) and with the one that unpacks in shared memory (512)."""
     gen = torch.Generator().manual_seed(7000 + seed)
     r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=gen))
     G = r(1, 8)
@@ -204,8 +206,13 @@ def test_contiguous_w4a8_random_group_sizes(seed):
     a, a_s = O.per_token_quant_int8(torch.randn(M, k, generator=gen))
     bp = P.pack_w4a8_moe_hipc_weight(cw["b_framework"].clone().to(DEV))
     out = torch.full((M, n), SENTINEL, dtype=torch.bfloat16, device=DEV)
-    deepgemm.m_grouped_w4a8_gemm_nt_contiguous_hipc(
-        (a.to(DEV), a_s.to(DEV)), (bp, (cw["b_scale"] / 16.0).unsqueeze(-1).to(DEV)), out, idx.to(DEV))
+    if block_n == 0:
+        deepgemm.m_grouped_w4a8_gemm_nt_contiguous_hipc(
+            (a.to(DEV), a_s.to(DEV)), (bp, (cw["b_scale"] / 16.0).unsqueeze(-1).to(DEV)), out, idx.to(DEV))
+    else:
+        _core.grouped_gemm_contiguous(_cabi.KIND_W4A8, _cabi.SCALE_PER_CHANNEL, a.to(DEV), bp, out,
+                                      a_s.reshape(-1).to(DEV), (cw["b_scale"] / 16.0).to(DEV), idx.to(DEV),
+                                      block_n=block_n)
     out = out.cpu()
     w_x16 = (cw["w4"].to(torch.int16) * 16).to(torch.int8)
     for g in range(G):

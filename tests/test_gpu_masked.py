@@ -396,3 +396,16 @@ def test_overlap_mode_completion_counters(tensor_wise):
     with pytest.raises(RuntimeError, match="signal"):
         fn((c["a"].to(DEV), c["a_scale"].to(DEV)), (bp, c["b_scale"].to(DEV)), d, c["masked_m"].to(DEV), 300,
            signal=signal)
+
+
+@pytest.mark.parametrize("order", ["high_first", "low_first"])
+def test_masked_w4a8_shared_memory_unpack_kernel_bit_exact(order):
+    """The second W4A8 kernel (tokens on UMMA M, int4 -> int8 unpack in shared memory; block_n =
+    512) against the same bar as the default one: ragged masked_m with empty experts and experts of
+    more than 128 rows, N that is not a multiple of its 256-channel tile, K of several rounds."""
+    mm = [0, 256, 17, 130, 64, 1]
+    c = gen_masked_w4a8(6, 256, 640, 1024, mm, seed=19, nibble_order=order)
+    bp = P.pack_w4a8_moe_hipc_weight(c["b_framework"].clone().to(DEV), nibble_order=order)
+    w_x16 = (c["w4"].to(torch.int16) * 16).to(torch.int8)
+    _check_int_case(c, _cabi.KIND_W4A8, w_x16, bp, c["b_scale"] / 16.0, block_n=512,
+                    what=f"w4a8 shared-memory unpack {order}")
