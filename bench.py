@@ -472,10 +472,22 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
         return e0.elapsed_time(e1) / n
 
     # ---- the whole layer, one timed step (every launch of forward() between the two events)
+    # also with the push in 2 and 4 slices (the later slices cross NVLink under the gate/up GEMM of
+    # the earlier ones); every variant is checked; the layer figure is the unsliced default
     out = torch.empty(T, K, dtype=torch.bfloat16, device=device)
-    layer_ms = timed(lambda: x.forward(hidden, topk, weights, w13p, w2p, out=out))
-    x.check_status()
-    parity = _ep_parity(out, hidden, topk, weights, device, cfg)
+    by_slices, parity = {}, None
+    for n_slices in ((1, 2, 4) if world > 1 else (1,)):
+        out.zero_()
+        by_slices[n_slices] = timed(lambda: x.forward(hidden, topk, weights, w13p, w2p, out=out, slices=n_slices))
+        x.check_status()
+        p_n = _ep_parity(out, hidden, topk, weights, device, cfg)
+        if parity is None or not p_n["ok"]:
+            parity = p_n
+    sl = torch.tensor([by_slices.get(n, 0.0) for n in (1, 2, 4)], device=device, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(sl, op=dist.ReduceOp.MAX)
+    by_slices = {n: float(v) for n, v in zip((1, 2, 4), sl.tolist()) if v > 0.0}
+    layer_ms = by_slices[1]
 
     # ---- its phases, each timed on its own (a barrier closes every phase that writes to peers)
     quant_ms = 0.0            # fused into the push
@@ -535,6 +547,7 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
            "valid_rows_this_rank": valid, "m_total_this_rank": m_total,
            "parity": "ok" if ok_ranks == world else "FAILED", "parity_rank0": parity,
            "layer_ms": layer_ms,
+           "layer_ms_by_push_slices": {str(n): v for n, v in by_slices.items()},
            "layer": {"exchange": "peer-memory stores (dg_ep_plan / dg_ep_push with the per-token quantisation "
                                  "fused in / dg_ep_barrier), result rows scattered home by the down GEMM's "
                                  "epilogue; no host synchronisation",

@@ -1,9 +1,12 @@
-"""Builds libdeepgemm_b200.so (sm_100a only) with nvcc, in-tree.
+"""Builds libdeepgemm_b200.so (sm_100a only) with nvcc, in-tree, and the host glue beside it.
 
 Usage:  python deepgemm-das_b200/build.py [--force] [--verbose]
 
 The library has no torch dependency: it links the static CUDA runtime only and obtains
 cuTensorMapEncodeTiled through cudaGetDriverEntryPoint, so libcuda is not linked either.
+deepgemm/_glue.so is a Python extension (g++, torch headers) that checks torch tensors and calls
+the library natively; the package works without it through the ctypes marshalling, only slower
+per call, so a failure to build it is reported and not fatal.
 """
 from __future__ import annotations
 
@@ -20,6 +23,9 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "deepgemm", "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libdeepgemm_b200.so")
 STAMP_PATH = LIB_PATH + ".stamp"
+GLUE_SRC = os.path.join(CSRC, "dg_torch_glue.cpp")
+GLUE_PATH = os.path.join(PKG_DIR, "deepgemm", "_glue.so")
+GLUE_STAMP = GLUE_PATH + ".stamp"
 
 SOURCES = ["dg_api.cu"]
 HEADERS = ["dg_ptx.cuh", "dg_grouped_gemm.cuh", "dg_grouped_gemm_pair.cuh", "dg_grouped_gemm_w4.cuh", "dg_grouped_gemm_w4s.cuh",
@@ -60,23 +66,78 @@ def nvcc_command(verbose: bool = False) -> list[str]:
     return cmd
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles the library if its sources changed; returns the path of the .so."""
-    os.makedirs(LIB_DIR, exist_ok=True)
-    digest = _digest()
-    if not force and os.path.exists(LIB_PATH) and os.path.exists(STAMP_PATH):
-        with open(STAMP_PATH) as fh:
+def glue_command() -> list[str]:
+    """g++ line for deepgemm/_glue.so: torch's headers and libraries, the C ABI header, and the
+    library itself found at run time beside the module ($ORIGIN/lib)."""
+    import sysconfig
+    import torch
+    tdir = os.path.dirname(torch.__file__)
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    abi = int(getattr(torch._C, "_GLIBCXX_USE_CXX11_ABI", True))
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include")
+    return [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+            f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_glue", "-DTORCH_API_INCLUDE_EXTENSION_H",
+            "-I", os.path.join(REPO_DIR, "include"), "-I", os.path.join(tdir, "include"),
+            "-I", os.path.join(tdir, "include", "torch", "csrc", "api", "include"),
+            "-I", sysconfig.get_paths()["include"], "-I", cuda_inc,
+            GLUE_SRC, "-o", GLUE_PATH,
+            "-L", LIB_DIR, "-ldeepgemm_b200", "-L", os.path.join(tdir, "lib"),
+            "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch", "-ltorch_python",
+            "-Wl,-rpath,$ORIGIN/lib", "-Wl,-rpath," + os.path.join(tdir, "lib")]
+
+
+def build_glue(force: bool = False, verbose: bool = False):
+    """Compiles deepgemm/_glue.so if its inputs changed.  Returns its path, or None (with the
+    compiler's output on stderr) when it cannot be built here."""
+    h = hashlib.sha256()
+    for f in (GLUE_SRC, os.path.join(REPO_DIR, "include", "deepgemm_b200.h"), os.path.abspath(__file__)):
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    try:
+        import torch
+        h.update(torch.__version__.encode())
+    except ImportError:
+        sys.stderr.write("deepgemm build: torch is not importable, the host glue is not built\n")
+        return None
+    digest = h.hexdigest()
+    if not force and os.path.exists(GLUE_PATH) and os.path.exists(GLUE_STAMP):
+        with open(GLUE_STAMP) as fh:
             if fh.read().strip() == digest:
-                return LIB_PATH
-    cmd = nvcc_command(verbose)
+                return GLUE_PATH
+    cmd = glue_command()
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stdout)
         sys.stderr.write(proc.stderr)
     if proc.returncode != 0:
-        raise RuntimeError("nvcc failed building libdeepgemm_b200.so:\n" + " ".join(cmd))
-    with open(STAMP_PATH, "w") as fh:
+        sys.stderr.write("deepgemm build: the host glue did not compile (calls use the ctypes path):\n"
+                         + " ".join(cmd) + "\n")
+        return None
+    with open(GLUE_STAMP, "w") as fh:
         fh.write(digest)
+    return GLUE_PATH
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles the library (and the host glue) if their sources changed; returns the path of
+    libdeepgemm_b200.so."""
+    os.makedirs(LIB_DIR, exist_ok=True)
+    digest = _digest()
+    fresh = False
+    if not force and os.path.exists(LIB_PATH) and os.path.exists(STAMP_PATH):
+        with open(STAMP_PATH) as fh:
+            fresh = fh.read().strip() == digest
+    if not fresh:
+        cmd = nvcc_command(verbose)
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or proc.returncode != 0:
+            sys.stderr.write(proc.stdout)
+            sys.stderr.write(proc.stderr)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed building libdeepgemm_b200.so:\n" + " ".join(cmd))
+        with open(STAMP_PATH, "w") as fh:
+            fh.write(digest)
+    build_glue(force=force, verbose=verbose)
     return LIB_PATH
 
 

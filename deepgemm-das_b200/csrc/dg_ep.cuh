@@ -179,6 +179,7 @@ struct EpPushParams {
   EpPeers peer_tag;          // every rank's [m_cap] tags: source rank << 24 | pair index
   int32_t* pair_dest;        // NULL, or [T][top_k] out: destination row of each pair (-1 = dropped)
   int32_t* status;
+  int local_lo, local_hi;    // only pairs whose expert is number [local_lo, local_hi) of its owner's are sent
 };
 
 constexpr int kEpMaxChunksPerThread = 4;  // row_bytes <= 16 * 256 * 4 = 16384
@@ -197,7 +198,9 @@ __global__ void __launch_bounds__(kEpPushThreads) ep_push_kernel(const EpPushPar
     if (tid < p.top_k) {
       const int e = p.topk_ids[(size_t)t * p.top_k + tid];
       int dest = -1;
-      if (e >= 0 && e < p.E) {
+      const int el = e % p.e_local;
+      const bool mine = e >= 0 && e < p.E && el >= p.local_lo && el < p.local_hi;  // this slice's pair
+      if (mine) {
         dest = p.my_base[e] + atomicAdd(&p.cursor[e], 1);
         if (dest >= p.m_cap) {  // the owning rank's buffer is full: the pair is dropped and reported
           dest = -1;
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(kEpPushThreads) ep_push_kernel(const EpPushPar
         }
       }
       dest_s[tid] = dest;
-      if (p.pair_dest != nullptr) p.pair_dest[(size_t)t * p.top_k + tid] = dest;
+      if (p.pair_dest != nullptr && (mine || e < 0 || e >= p.E)) p.pair_dest[(size_t)t * p.top_k + tid] = dest;
       if (dest >= 0) {
         const int r = e / p.e_local;
         static_cast<float*>(p.peer_scale.ptr[r])[dest] = p.row_scale[t];
@@ -261,7 +264,9 @@ __global__ void __launch_bounds__(kEpPushThreads) ep_push_quant_kernel(const EpP
     if (tid < p.top_k) {
       const int e = p.topk_ids[(size_t)t * p.top_k + tid];
       int dest = -1;
-      if (e >= 0 && e < p.E) {
+      const int el = e % p.e_local;
+      const bool mine = e >= 0 && e < p.E && el >= p.local_lo && el < p.local_hi;  // this slice's pair
+      if (mine) {
         dest = p.my_base[e] + atomicAdd(&p.cursor[e], 1);
         if (dest >= p.m_cap) {
           dest = -1;
@@ -269,7 +274,7 @@ __global__ void __launch_bounds__(kEpPushThreads) ep_push_quant_kernel(const EpP
         }
       }
       dest_s[tid] = dest;
-      if (p.pair_dest != nullptr) p.pair_dest[(size_t)t * p.top_k + tid] = dest;
+      if (p.pair_dest != nullptr && (mine || e < 0 || e >= p.E)) p.pair_dest[(size_t)t * p.top_k + tid] = dest;
       if (dest >= 0) {
         const int r = e / p.e_local;
         static_cast<float*>(p.peer_scale.ptr[r])[dest] = __fdiv_rn(amax, kQmax);

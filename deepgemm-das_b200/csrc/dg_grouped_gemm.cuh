@@ -88,6 +88,8 @@ struct KernelParams {
   // Masked layout only: per (group, 128-row block) completion counters; a finished tile adds the
   // number of columns it covers, a quarter per epilogue warp (the block is done at N).
   int32_t* signal;
+  int group_window;  // contiguous layout: 0, or 1 + the id (in m_indices' numbering) of this call's group 0;
+                     // entries that name a group outside the call are then skipped silently
   int wide_off;  // 0, or offset in shared memory of four 32-row x 128-byte store strips (scattered output)
   int narrow;  // masked / compact: 0 = tiles stay BN columns wide, 1 = the kernel may narrow them
                // (down to 32 columns) when few groups have rows, 128 / 64 / 32 = forced width
@@ -574,7 +576,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
     }
   } else {
-    for (int b = tid; b < p.m_blocks; b += blockDim.x) tbl[b] = p.sched[(size_t)b * kBM];
+    const int window0 = p.group_window ? p.group_window - 1 : 0;
+    for (int b = tid; b < p.m_blocks; b += blockDim.x) {
+      const int e = p.sched[(size_t)b * kBM];
+      tbl[b] = e < 0 ? -1 : e - window0;
+    }
     __syncthreads();
     if (warp == 0) {
       int count = 0;
@@ -583,7 +589,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         const int b = b0 + lane;
         const int e = (b < p.m_blocks) ? tbl[b] : -1;
         const bool ok = (e >= 0) && (e < p.G);
-        bad |= (e >= p.G);
+        bad |= (e >= p.G) && !p.group_window;
         const unsigned mask = __ballot_sync(0xffffffffu, ok);
         __syncwarp();
         if (ok) tbl[count + __popc(mask & ((1u << lane) - 1u))] = (e << 16) | b;

@@ -175,9 +175,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     // two slots per super block: slot 0 = unit of the first half's group (covering both
     // halves when they agree), slot 1 = unit of the second half's group when it differs
     const int sbs = (p.M + 255) / 256;
+    const int window0 = p.group_window ? p.group_window - 1 : 0;
     for (int sb = tid; sb < sbs; sb += blockDim.x) {
-      const int e0 = p.sched[(size_t)sb * 256];
-      const int e1 = ((size_t)sb * 256 + 128 < (size_t)p.M) ? p.sched[(size_t)sb * 256 + 128] : -1;
+      int e0 = p.sched[(size_t)sb * 256];
+      int e1 = ((size_t)sb * 256 + 128 < (size_t)p.M) ? p.sched[(size_t)sb * 256 + 128] : -1;
+      e0 = e0 < 0 ? -1 : e0 - window0;
+      e1 = e1 < 0 ? -1 : e1 - window0;
+      if (p.group_window) {  // groups of other calls: not this call's business
+        if (e0 >= p.G) e0 = -1;
+        if (e1 >= p.G) e1 = -1;
+      }
       const bool v0 = e0 >= 0 && e0 < p.G, v1 = e1 >= 0 && e1 < p.G;
       int u0 = -1, u1 = -1;
       if (v0) {

@@ -19,6 +19,7 @@ STATUS_WORDS = 4
 OUT_BF16, OUT_F16, OUT_F32 = 0, 1, 2
 NOALLOC_MAX_SCRATCH_INTS = 262144 + 1024
 QUERY_ABI_VERSION, QUERY_SM_COUNT, QUERY_MAX_SMEM, QUERY_CC, QUERY_LAUNCH_COUNT = 0, 1, 2, 3, 4
+QUERY_MAP_ENCODES, QUERY_MAP_REUSES = 5, 6
 ERR_CUDA = -7
 
 EXPORTED_SYMBOLS = (
@@ -88,7 +89,7 @@ class ContigArgs(C.Structure):
         ("scatter_tag", C.c_void_p),
         ("scatter_base", C.POINTER(C.c_void_p)),
         ("scatter_world", C.c_int32),
-        ("reserved2", C.c_int32),
+        ("group_window", C.c_int32),
     ]
 
 
@@ -259,6 +260,10 @@ class EpPushArgs(C.Structure):
         ("peer_tag", C.POINTER(C.c_void_p)),
         ("pair_dest", C.c_void_p),
         ("status", C.c_void_p),
+        ("local_lo", C.c_int32),
+        ("local_hi", C.c_int32),
+        ("max_blocks", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

@@ -18,6 +18,15 @@ from . import _cabi
 from ._cabi import (KIND_BF16, KIND_E4M3, KIND_I8, KIND_W4A8, SCALE_NONE, SCALE_PER_CHANNEL,
                     SCALE_TENSOR_WISE)
 
+try:                                   # native argument checks + launch (csrc/dg_torch_glue.cpp)
+    from . import _glue
+    if _glue.abi_version() != _cabi.ABI_VERSION:
+        _glue = None                   # built against another header: the ctypes path below still works
+except ImportError:
+    _glue = None
+if os.environ.get("DEEPGEMM_NO_GLUE"):
+    _glue = None
+
 _FP8 = torch.float8_e4m3fn
 # (device type, index, data pointer) of every [E, N, K/2] int4 tensor a packer of this package has
 # put into the kernel layout: that shape is shared with the unpacked framework layout
@@ -143,6 +152,8 @@ def device_status_words(device: torch.device) -> torch.Tensor:
     if words is None:
         words = torch.zeros(_cabi.STATUS_WORDS, dtype=torch.int32, device=torch.device("cuda", index))
         _status_words[index] = words
+        if _glue is not None:
+            _glue.set_status_words(index, words)
     return words
 
 
@@ -186,6 +197,11 @@ def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Te
     """d[g, :masked_m[g]] = bf16((A[g] @ B[g]^T) * a_scale[g] * b_scale[g]) via dg_masked_gemm.
     ``signal``: int32 [G, ceil(max_m / 128)] completion counters (zeroed by the caller); entry
     (g, mb) reaches N when rows [128 mb, 128 mb + 128) of group g are complete."""
+    # The native glue enqueues the call if every check below would pass; otherwise it enqueues
+    # nothing and the checks run here, for the message or for the case it does not know.
+    if _glue is not None and debug_acc is None and _glue.masked(
+            kind, scale_mode, a, b, d, a_scale, b_scale, masked_m, expected_m, block_n, status, signal):
+        return d
     what = f"masked {KIND_NAMES[kind]} grouped GEMM"
     if not (a.dim() == 3):
         raise RuntimeError(f"{what}: activation must be [G, max_m, K], got {tuple(a.shape)}")
@@ -233,8 +249,11 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
                             d: torch.Tensor, a_scale: Optional[torch.Tensor],
                             b_scale: Optional[torch.Tensor], m_indices: torch.Tensor, *,
                             block_n: int = 0, debug_acc: Optional[torch.Tensor] = None,
-                            status: Optional[torch.Tensor] = None, scatter=None) -> torch.Tensor:
+                            status: Optional[torch.Tensor] = None, scatter=None,
+                            group_window: Optional[int] = None) -> torch.Tensor:
     """d[i] = bf16((A[i] @ B[m_indices[i]]^T) * a_scale[i] * b_scale[m_indices[i]]) via dg_contig_gemm.
+    ``group_window`` = w: ``m_indices`` numbers the groups of a wider set and ``b`` holds groups
+    w .. w + G - 1 of it; rows of other groups are skipped (their output rows stay as they were).
     ``scatter`` = (tag int32 [M] CUDA tensor, ctypes array of buffer pointers, count): result row i
     goes to row ``tag[i] & 0xFFFFFF`` of buffer ``tag[i] >> 24`` instead of ``d[i]`` (``d`` is then
     only checked for dtype and device)."""
@@ -278,6 +297,10 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
         debug_acc=_ptr(debug_acc), status=_ptr(status))
     if scatter is not None:
         args.scatter_tag, args.scatter_base, args.scatter_world = scatter[0].data_ptr(), scatter[1], int(scatter[2])
+    if group_window is not None:
+        if group_window < 0:
+            raise RuntimeError(f"{what}: group_window must not be negative")
+        args.group_window = int(group_window) + 1
     _launch(_cabi.lib.dg_contig_gemm, args, a.device, what)
     return d
 

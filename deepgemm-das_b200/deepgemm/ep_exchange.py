@@ -100,6 +100,9 @@ class EPExchange:
         self.m_cap = _round_up(m_cap, self._ALIGN)
         self.device = device
         self.epoch = 0
+        self._comm = None                              # second stream of a sliced push
+        self.overlap_push_blocks = torch.cuda.get_device_properties(device).multi_processor_count
+        # ^ grid of a push that runs beside a GEMM: one block per SM fits next to a GEMM CTA
         # ---- the one buffer every rank maps: receive side of the dispatch and of the return
         sizes = self._sizes(world, num_experts, hidden, out_hidden, max_tokens, top_k, self.m_cap)
         self._off, total = {}, 0
@@ -164,11 +167,15 @@ class EPExchange:
             status=self.status.data_ptr())
         _launch(_cabi.lib.dg_ep_plan, args, self.device, "dg_ep_plan")
 
-    def push(self, q: torch.Tensor, q_scale: Optional[torch.Tensor], topk_ids: torch.Tensor) -> None:
+    def push(self, q: torch.Tensor, q_scale: Optional[torch.Tensor], topk_ids: torch.Tensor,
+             experts: Optional[Tuple[int, int]] = None, max_blocks: int = 0) -> None:
         """Writes every routed row into its owner's receive buffer (``dg_ep_push``).  ``q`` holds the
         quantised rows and ``q_scale`` their scales, or ``q`` holds the bf16 rows and ``q_scale`` is
-        None: the kernel then quantises each token on the way out."""
+        None: the kernel then quantises each token on the way out.  ``experts`` = (lo, hi): only
+        the pairs whose expert is number lo .. hi - 1 among its owner's experts.  ``max_blocks``
+        bounds the grid (0 = eight blocks per SM) for a push that shares the GPU with a GEMM."""
         t, k = topk_ids.shape
+        lo, hi = experts if experts is not None else (0, 0)
         if q_scale is None:
             if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[1] != self.hidden:
                 raise ValueError("rows to quantise must be a contiguous bf16 [T, hidden] tensor")
@@ -182,7 +189,7 @@ class EPExchange:
             topk_ids=topk_ids.data_ptr(), my_base=self.my_base.data_ptr(),
             cursor=self.cursor.data_ptr(), peer_a=self._peer["recv_a"], peer_scale=self._peer["recv_scale"],
             peer_tag=self._peer["recv_tag"], pair_dest=self.pair_dest.data_ptr(),
-            status=self.status.data_ptr())
+            status=self.status.data_ptr(), local_lo=lo, local_hi=hi, max_blocks=max_blocks)
         _launch(_cabi.lib.dg_ep_push, args, self.device, "dg_ep_push")
 
     def barrier(self, phases: int = 0) -> None:
@@ -192,12 +199,24 @@ class EPExchange:
                                    peer_flags=self._peer["flags"], status=self.status.data_ptr())
         _launch(_cabi.lib.dg_ep_barrier, args, self.device, "dg_ep_barrier")
 
-    def experts(self, w13, w2) -> None:
+    def gate_up(self, w13, experts: Optional[Tuple[int, int]] = None) -> None:
+        """The gate/up GEMM over the received rows; ``experts`` = (lo, hi) restricts it to the rows
+        of this rank's experts lo .. hi - 1 (the other rows of ``h13`` are left alone)."""
+        kind = _cabi.KIND_E4M3 if self.kind == "fp8" else _cabi.KIND_I8
+        if experts is None:
+            _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, self.recv_a, w13[0], self.h13,
+                                          self.recv_scale, w13[1], self.m_indices)
+        else:
+            lo, hi = experts
+            _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, self.recv_a, w13[0][lo:hi], self.h13,
+                                          self.recv_scale, w13[1][lo:hi], self.m_indices, group_window=lo)
+
+    def experts(self, w13, w2, gate_up_done: bool = False) -> None:
         """gate/up GEMM -> SiLU*up + requantise -> down GEMM whose result rows go home."""
         from .moe_chain import silu_mul_quant
         kind = _cabi.KIND_E4M3 if self.kind == "fp8" else _cabi.KIND_I8
-        _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, self.recv_a, w13[0], self.h13,
-                                      self.recv_scale, w13[1], self.m_indices)
+        if not gate_up_done:
+            self.gate_up(w13)
         silu_mul_quant(self.h13, kind=self.kind, m_indices=self.m_indices, out=(self.act_q, self.act_scale))
         # the scattering GEMM never writes `d`; it only has to be a valid bf16 tensor
         _core.grouped_gemm_contiguous(kind, _cabi.SCALE_PER_CHANNEL, self.act_q, w2[0], self.y_back,
@@ -213,23 +232,53 @@ class EPExchange:
         from .quant_group import quantize_rows
         return quantize_rows(hidden, kind=self.kind)
 
+    def slices(self, n: int) -> List[Tuple[int, int]]:
+        """This rank's experts cut into ``n`` runs of (almost) equal length."""
+        n = max(1, min(int(n), self.e_local))
+        cuts = [self.e_local * i // n for i in range(n + 1)]
+        return [(cuts[i], cuts[i + 1]) for i in range(n)]
+
     def forward(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, w13, w2,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, *, slices: int = 1) -> torch.Tensor:
         """One layer for this rank's tokens: hidden bf16 [T, hidden], topk_ids int32 [T, top_k],
         topk_weights fp32 [T, top_k]; ``w13`` / ``w2`` = (packed weight, scale) of this rank's
         experts.  Returns bf16 [T, out_hidden].  Enqueues only; call ``check_status`` after a
-        synchronisation to learn of dropped pairs or a peer that never arrived."""
+        synchronisation to learn of dropped pairs or a peer that never arrived.
+
+        ``slices`` > 1 (the same on every rank): the rows are pushed in that many slices of every
+        owner's experts on a second stream, and the gate/up GEMM of a slice starts as soon as that
+        slice has arrived everywhere, while the next slice is still crossing NVLink.  The result
+        is the same bit for bit."""
         if topk_ids.dtype != torch.int32 or not topk_ids.is_contiguous():
             raise ValueError("topk_ids must be contiguous int32 [T, top_k]")
         if topk_ids.shape[0] > self.max_tokens or topk_ids.shape[1] != self.top_k:
             raise ValueError("more tokens than the exchange was sized for, or another top_k")
-        self.plan(topk_ids)
-        if self.hidden <= 8192:
-            self.push(hidden, None, topk_ids)           # quantised on the way out
+        if self.hidden > 8192:
+            rows, row_scale = self.quantise(hidden)
         else:
-            self.push(*self.quantise(hidden), topk_ids)
-        self.barrier()
-        self.experts(w13, w2)
+            rows, row_scale = hidden, None              # quantised on the way out
+        self.plan(topk_ids)
+        parts = self.slices(slices)
+        if len(parts) == 1:
+            self.push(rows, row_scale, topk_ids)
+            self.barrier()
+            self.experts(w13, w2)
+        else:
+            main = torch.cuda.current_stream(self.device)
+            if self._comm is None:
+                self._comm = torch.cuda.Stream(self.device)
+                self._arrived = [torch.cuda.Event() for _ in range(self.e_local)]
+            self._comm.wait_stream(main)
+            with torch.cuda.stream(self._comm):
+                for i, part in enumerate(parts):
+                    # slices after the first run beside a GEMM: one block per SM fits next to its CTA
+                    self.push(rows, row_scale, topk_ids, experts=part, max_blocks=self.overlap_push_blocks if i else 0)
+                    self.barrier()
+                    self._arrived[i].record(self._comm)
+            for i, part in enumerate(parts):
+                main.wait_event(self._arrived[i])
+                self.gate_up(w13, part)
+            self.experts(w13, w2, gate_up_done=True)
         self.barrier()
         return self.combine(topk_weights.to(torch.float32), out=out)
 
@@ -257,23 +306,30 @@ def make_emulated_ranks(world: int, num_experts: int, hidden: int, inter2: int, 
 
 def emulated_forward(ranks: Sequence[EPExchange], hidden: Sequence[torch.Tensor],
                      topk_ids: Sequence[torch.Tensor], topk_weights: Sequence[torch.Tensor],
-                     w13: Sequence, w2: Sequence) -> List[torch.Tensor]:
+                     w13: Sequence, w2: Sequence, slices: int = 1) -> List[torch.Tensor]:
     """One layer of every emulated rank, phase by phase (the posting half of each barrier for all
-    ranks before any waiting half)."""
+    ranks before any waiting half); with ``slices`` > 1 the push and the gate/up GEMM run slice
+    by slice as in ``EPExchange.forward`` (on one stream)."""
     for r, ids in zip(ranks, topk_ids):
         r.plan(ids, _cabi.EP_PHASE_POST)
     for r, ids in zip(ranks, topk_ids):
         r.plan(ids, _cabi.EP_PHASE_WAIT)
-    for i, (r, h, ids) in enumerate(zip(ranks, hidden, topk_ids)):
-        if i % 2 == 0 and r.hidden <= 8192:
-            r.push(h, None, ids)                    # quantised on the way out
-        else:
-            r.push(*r.quantise(h), ids)             # quantised first: the same bytes
-    for ph in (_cabi.EP_PHASE_POST, _cabi.EP_PHASE_WAIT):
-        for r in ranks:
-            r.barrier(ph)
+    parts = ranks[0].slices(slices)
+    for part in parts:
+        only = part if len(parts) > 1 else None
+        for i, (r, h, ids) in enumerate(zip(ranks, hidden, topk_ids)):
+            if i % 2 == 0 and r.hidden <= 8192:
+                r.push(h, None, ids, experts=only)            # quantised on the way out
+            else:
+                r.push(*r.quantise(h), ids, experts=only)     # quantised first: the same bytes
+        for ph in (_cabi.EP_PHASE_POST, _cabi.EP_PHASE_WAIT):
+            for r in ranks:
+                r.barrier(ph)
+        if only is not None:
+            for r, a in zip(ranks, w13):
+                r.gate_up(a, only)
     for r, a, b in zip(ranks, w13, w2):
-        r.experts(a, b)
+        r.experts(a, b, gate_up_done=len(parts) > 1)
     for ph in (_cabi.EP_PHASE_POST, _cabi.EP_PHASE_WAIT):
         for r in ranks:
             r.barrier(ph)

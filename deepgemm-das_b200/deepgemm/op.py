@@ -4,8 +4,11 @@ The reference exposes its C++ launchers twice: as the pybind module ``deepgemm.o
 (csrc/common/deepgemm_ops.cpp:127-144, argument names in csrc/include/deepgemm_ops.hpp) and
 as dispatcher ops in namespace ``deep_gemm`` (csrc/common/000_deep_gemm_torch_library_root.cu:6,
 schemas e.g. csrc/arch/gfx936_gfx938_shared/low_latency_grouped_gemm.cu:56-103).  Both are
-kept: every function of this module calls the dispatcher op of the same name, and each op
-has a CUDA implementation only, which marshals to the C ABI of libdeepgemm_b200.so.  The
+kept and reach the same implementation: a function of this module calls it directly, as a
+pybind function would (the dispatcher hop costs about 5 us of host time per call, as much as
+everything else on the host path); ``torch.ops.deep_gemm.<name>`` goes through the dispatcher
+for callers that need an op (graph capture by a compiler).  Each op has a CUDA implementation
+only, which marshals to the C ABI of libdeepgemm_b200.so.  The
 ``mode`` / ``cu_s`` / ``block_m`` / ``block_n`` / ``n_loop_num`` integers selected Hygon tile
 variants; here they are accepted and ignored (the library picks its own tile).
 """
@@ -23,9 +26,17 @@ _NS = "deep_gemm"
 _lib = torch.library.Library(_NS, "FRAGMENT")
 
 
+class _Impls:
+    """Implementation of every op by name (attribute access, as on ``torch.ops.deep_gemm``)."""
+
+
+_impl = _Impls()
+
+
 def _define(name: str, schema: str, fn) -> None:
     _lib.define(f"{name}{schema}")
     _lib.impl(name, fn, "CUDA")
+    setattr(_impl, name, fn)
 
 
 # --------------------------------------------------------------------------- masked
@@ -182,7 +193,7 @@ _ops = getattr(torch.ops, _NS)
 def low_latency_grouped_gemm(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens,
                              matrix_c, max_tokens, experts, cu_s, block_wise, b_overlap,
                              signal: Optional[torch.Tensor] = None):
-    return _ops.low_latency_grouped_gemm(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale,
+    return _impl.low_latency_grouped_gemm(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale,
                                          actual_tokens, matrix_c, int(max_tokens), int(experts),
                                          int(cu_s), bool(block_wise), bool(b_overlap), signal)
 
@@ -191,7 +202,7 @@ def m_grouped_w8a8_gemm_nt_masked_gfx936(matrix_a, matrix_b, matrix_a_scale, mat
                                          actual_tokens, matrix_c, max_tokens, experts, cu_s,
                                          block_wise, b_overlap,
                                          signal: Optional[torch.Tensor] = None):
-    return _ops.m_grouped_w8a8_gemm_nt_masked_gfx936(
+    return _impl.m_grouped_w8a8_gemm_nt_masked_gfx936(
         matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
         int(max_tokens), int(experts), int(cu_s), bool(block_wise), bool(b_overlap), signal)
 
@@ -199,71 +210,71 @@ def m_grouped_w8a8_gemm_nt_masked_gfx936(matrix_a, matrix_b, matrix_a_scale, mat
 def low_latency_grouped_gemm_tensor_wise(matrix_a, matrix_b, matrix_a_scale, matrix_b_scale,
                                          actual_tokens, matrix_c, max_tokens, experts, cu_s,
                                          b_overlap, signal: Optional[torch.Tensor] = None):
-    return _ops.low_latency_grouped_gemm_tensor_wise(
+    return _impl.low_latency_grouped_gemm_tensor_wise(
         matrix_a, matrix_b, matrix_a_scale, matrix_b_scale, actual_tokens, matrix_c,
         int(max_tokens), int(experts), int(cu_s), bool(b_overlap), signal)
 
 
 def m_grouped_marlin_w8a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale, masked_m,
                                          expected_m_per_group, mode):
-    return _ops.m_grouped_marlin_w8a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale,
+    return _impl.m_grouped_marlin_w8a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale,
                                                      masked_m, int(expected_m_per_group), int(mode))
 
 
 def m_grouped_marlin_w4a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale, masked_m,
                                          expected_m_per_group, mode):
-    return _ops.m_grouped_marlin_w4a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale,
+    return _impl.m_grouped_marlin_w4a8_gemm_nt_masked(input, b_qweight, output, a_scale, b_scale,
                                                      masked_m, int(expected_m_per_group), int(mode))
 
 
 def m_grouped_marlin_w4a8_gemm_nt_masked_hipc(input, b_qweight, output, a_scale, b_scale,
                                               masked_m, expected_m_per_group, mode):
-    return _ops.m_grouped_marlin_w4a8_gemm_nt_masked_hipc(
+    return _impl.m_grouped_marlin_w4a8_gemm_nt_masked_hipc(
         input, b_qweight, output, a_scale, b_scale, masked_m, int(expected_m_per_group), int(mode))
 
 
 def m_grouped_bf16_gemm_nt_masked(input, b_qweight, output, masked_m, expected_m_per_group, mode):
-    return _ops.m_grouped_bf16_gemm_nt_masked(input, b_qweight, output, masked_m,
+    return _impl.m_grouped_bf16_gemm_nt_masked(input, b_qweight, output, masked_m,
                                               int(expected_m_per_group), int(mode))
 
 
 def m_grouped_bf16_gemm_nt_masked_hipc(input, b_qweight, output, masked_m, expected_m_per_group,
                                        mode):
-    return _ops.m_grouped_bf16_gemm_nt_masked_hipc(input, b_qweight, output, masked_m,
+    return _impl.m_grouped_bf16_gemm_nt_masked_hipc(input, b_qweight, output, masked_m,
                                                    int(expected_m_per_group), int(mode))
 
 
 def m_grouped_w8a8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
-    return _ops.m_grouped_w8a8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
+    return _impl.m_grouped_w8a8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
                                                   m_indices, int(mode))
 
 
 def m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc(input, b_qweight, output, a_scale, b_scale,
                                                   m_indices, mode):
-    return _ops.m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc(input, b_qweight, output, a_scale,
+    return _impl.m_grouped_marlin_w4a8_gemm_nt_contiguous_hipc(input, b_qweight, output, a_scale,
                                                               b_scale, m_indices, int(mode))
 
 
 def m_grouped_marlin_w8a8_gemm_nt_compact_masked(input, b_qweight, output, a_scale, b_scale,
                                                  masked_m, expert_offsets, expected_m_per_group):
-    return _ops.m_grouped_marlin_w8a8_gemm_nt_compact_masked(
+    return _impl.m_grouped_marlin_w8a8_gemm_nt_compact_masked(
         input, b_qweight, output, a_scale, b_scale, masked_m, expert_offsets,
         int(expected_m_per_group))
 
 
 def m_grouped_w8a8_gemm_nt_nopad_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices,
                                             token_per_expert):
-    return _ops.m_grouped_w8a8_gemm_nt_nopad_contiguous(input, b_qweight, output, a_scale, b_scale,
+    return _impl.m_grouped_w8a8_gemm_nt_nopad_contiguous(input, b_qweight, output, a_scale, b_scale,
                                                         m_indices, token_per_expert)
 
 
 def m_grouped_w16a16_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
-    return _ops.m_grouped_w16a16_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
+    return _impl.m_grouped_w16a16_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
                                                     m_indices, int(mode))
 
 
 def m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale, m_indices, mode):
-    return _ops.m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
+    return _impl.m_grouped_fp8_gemm_nt_contiguous(input, b_qweight, output, a_scale, b_scale,
                                                  m_indices, int(mode), 256, 4)
 
 

@@ -166,7 +166,11 @@ typedef struct dg_contig_args {
   const int32_t* scatter_tag;   /* NULL, or [M_total] device array */
   void* const*   scatter_base;  /* HOST array of scatter_world device pointers */
   int32_t        scatter_world; /* 1..DG_EP_MAX_WORLD */
-  int32_t        reserved2;
+  int32_t        group_window;  /* 0: m_indices holds group ids of this call.  w > 0: it holds ids of a wider
+                                   numbering and this call covers ids [w - 1, w - 1 + num_groups) of it
+                                   (b_packed / b_scale start at id w - 1): rows with other ids are skipped
+                                   without a report -- one m_indices array serves several calls that each
+                                   take a slice of the experts (INT8 / FP8 / BF16 kinds) */
 } dg_contig_args;
 
 /* Arguments of the compact-layout grouped GEMM: rows of all groups in one flat tensor, group g
@@ -505,6 +509,12 @@ typedef struct dg_ep_push_args {
   void* const*   peer_tag;    /* int32 [m_cap] of every rank: rank << 24 | (token * top_k + slot) */
   int32_t*       pair_dest;   /* NULL, or [T][top_k] out: row each pair was written to, -1 = dropped */
   int32_t*       status;      /* DG_DEV_BAD_GROUP_INDEX when a pair did not fit (m_cap) and was dropped */
+  int32_t        local_lo;    /* with local_hi > 0: only pairs whose expert is number [local_lo, local_hi) */
+  int32_t        local_hi;    /* among its owner's experts are sent (a layer pushed in several slices, so that
+                                 the owner's GEMM on the first slice overlaps the push of the next); 0 = all */
+  int32_t        max_blocks;  /* 0 = 8 per SM.  A push that runs beside a GEMM on another stream takes fewer
+                                 (NVLink, not the grid, bounds a push: one block per SM is as fast) */
+  int32_t        reserved;
 } dg_ep_push_args;
 
 /* Writes every routed row of this rank into the owning rank's receive buffer (the grouped,
@@ -532,6 +542,9 @@ DG_API int dg_ep_barrier(const dg_ep_barrier_args* args, void* stream);
 #define DG_QUERY_MAX_SMEM      2 /* opt-in shared memory per block, bytes */
 #define DG_QUERY_CC            3 /* compute capability major*10+minor of the current device */
 #define DG_QUERY_LAUNCH_COUNT  4 /* kernels this library has launched in this process */
+#define DG_QUERY_MAP_ENCODES   5 /* tensor maps encoded through the driver so far (a repeated call finds its
+                                   maps in the calling thread's table and encodes none) */
+#define DG_QUERY_MAP_REUSES    6 /* tensor maps taken from that table instead */
 
 /* Returns the queried value (>= 0) or a negative dg_status.  Replaces the reference's
  * per-call hipGetDeviceProperties (m_grouped_w8a8_gemm_nt_masked.cu:85-89) and rocminfo

@@ -222,3 +222,34 @@ def test_contiguous_w4a8_random_group_sizes(seed, block_n):
         want = O.epilogue_from_acc(O.exact_int_acc(a[r_], w_x16[g]), a_s.reshape(-1)[r_], cw["b_scale"][g] / 16.0)
         assert_bf16_within_ulp(out[r_], want, 0, f"seed {seed}: rows={rows} N={n} K={k} group {g}")
     assert torch.all(out[idx < 0].float() == SENTINEL), f"seed {seed}: padding rows were written"
+
+
+@pytest.mark.parametrize("bn", [0, 128, 512])
+def test_group_window_calls_cover_the_same_rows_as_one_call(bn):
+    """Three calls, each with a slice of the groups and the whole m_indices array (group_window),
+    write exactly the rows of their groups and, together, the bytes of the single call; a window
+    is not an out-of-range report."""
+    rows = [300, 0, 511, 101, 256, 1, 77]
+    c = gen_contig("int8", rows, 512, 512, seed=61)
+    M, N = c["a"].shape[0], c["b"].shape[1]
+    bp = P.marlin_i8_contiguous_weight(c["b"].clone()).to(DEV)
+    a, sa, sb, idx = c["a"].to(DEV), c["a_scale"].to(DEV), c["b_scale"].to(DEV), c["m_indices"].to(DEV)
+    whole = torch.full((M, N), SENTINEL, dtype=torch.bfloat16, device=DEV)
+    _core.grouped_gemm_contiguous(_cabi.KIND_I8, _cabi.SCALE_PER_CHANNEL, a, bp, whole, sa, sb, idx, block_n=bn)
+    parts = torch.full((M, N), SENTINEL, dtype=torch.bfloat16, device=DEV)
+    st = torch.zeros(_cabi.STATUS_WORDS, dtype=torch.int32, device=DEV)
+    for lo, hi in ((0, 3), (3, 4), (4, 7)):
+        before = parts.clone()
+        _core.grouped_gemm_contiguous(_cabi.KIND_I8, _cabi.SCALE_PER_CHANNEL, a, bp[lo:hi], parts, sa, sb[lo:hi],
+                                      idx, block_n=bn, status=st, group_window=lo)
+        outside = ~((idx >= lo) & (idx < hi))
+        assert torch.equal(parts[outside].view(torch.int16), before[outside].view(torch.int16)), \
+            f"window {lo}..{hi} wrote rows of other groups"
+    torch.cuda.synchronize()
+    assert st.tolist() == [0, 0, 0, 0]
+    assert torch.equal(parts.view(torch.int16), whole.view(torch.int16))
+    # without a window the same slice call reports the foreign ids
+    _core.grouped_gemm_contiguous(_cabi.KIND_I8, _cabi.SCALE_PER_CHANNEL, a, bp[0:3], parts, sa, sb[0:3], idx,
+                                  block_n=bn, status=st)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 2       # DG_DEV_BAD_GROUP_INDEX

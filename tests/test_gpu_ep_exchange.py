@@ -58,8 +58,8 @@ def _rank_weights(rank, world, dev):
            (pk(w2[sl].clone().to(dev)), s2[sl].contiguous().to(dev))
 
 
-@pytest.mark.parametrize("world", [1, 4])
-def test_emulated_ranks_match_one_gpu_layer(world):
+@pytest.mark.parametrize("world,slices", [(1, 1), (4, 1), (2, 3), (4, 2)])
+def test_emulated_ranks_match_one_gpu_layer(world, slices):
     dev = torch.device("cuda", 0)
     m_cap = 4 * T * TOPK + (E // world) * 256
     ranks = epx.make_emulated_ranks(world, E, H, 2 * INTER, H, T, TOPK, m_cap, dev)
@@ -67,7 +67,8 @@ def test_emulated_ranks_match_one_gpu_layer(world):
     ws = [_rank_weights(r, world, dev) for r in range(world)]
     for rep in range(2):     # twice: epochs advance, buffers are re-used
         outs = epx.emulated_forward(ranks, [t[0].to(dev) for t in toks], [t[1].to(dev) for t in toks],
-                                    [t[2].to(dev) for t in toks], [w[0] for w in ws], [w[1] for w in ws])
+                                    [t[2].to(dev) for t in toks], [w[0] for w in ws], [w[1] for w in ws],
+                                    slices=slices)
         torch.cuda.synchronize()
         for r in range(world):
             ranks[r].check_status()
@@ -92,6 +93,21 @@ def test_emulated_ranks_match_one_gpu_layer(world):
             assert d.unique().numel() == d.numel()
             assert torch.equal(ranks[owner].m_indices.cpu()[d].long() + owner * (E // world),
                                toks[r][1].flatten().long()[sel])
+
+
+def test_sliced_push_on_a_second_stream_one_rank():
+    """``forward(slices=4)`` with one rank: the pushes run on a second stream, each gate/up GEMM waits
+    for its slice only; same bits as the unsliced layer."""
+    dev = torch.device("cuda", 0)
+    x = epx.EPExchange(0, 1, E, H, 2 * INTER, H, T, TOPK, T * TOPK + E * 256, dev)
+    w13, w2 = _rank_weights(0, 1, dev)
+    hidden, topk, w = (t.to(dev) for t in _tokens(0))
+    want = _one_gpu_layer(dev, 0)
+    for slices in (4, 1, 16, 5):
+        got = x.forward(hidden, topk, w, w13, w2, slices=slices).clone()
+        torch.cuda.synchronize()
+        x.check_status()
+        assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16)), f"slices={slices}"
 
 
 def test_rows_that_do_not_fit_are_dropped_and_reported():
@@ -144,8 +160,8 @@ def _worker(rank, world, port, q):
         w13, w2 = _rank_weights(rank, world, dev)
         hidden, topk, w = _tokens(rank)
         outs = []
-        for _ in range(3):
-            outs.append(x.forward(hidden.to(dev), topk.to(dev), w.to(dev), w13, w2).clone())
+        for slices in (1, 2, 4):
+            outs.append(x.forward(hidden.to(dev), topk.to(dev), w.to(dev), w13, w2, slices=slices).clone())
         torch.cuda.synchronize()
         x.check_status()
         assert all(torch.equal(o.view(torch.int16), outs[0].view(torch.int16)) for o in outs)
