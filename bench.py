@@ -572,6 +572,33 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
     return res
 
 
+def bench_host_path(device, cfg, calls=4000):
+    """Host time per call of the public Python entry point (decode shape, no routed rows, so the
+    kernel is an empty launch and the host is what is timed), with no CUDA graph: wall clock over
+    back-to-back asynchronous calls."""
+    import deepgemm
+    from deepgemm import _core
+    G, max_m, N, K = cfg["G"], cfg["max_m"], cfg["N"], cfg["K"]
+    a = torch.zeros(G, max_m, K, device=device, dtype=torch.float8_e4m3fn)
+    bp = deepgemm.marlin_fp8_masked_weight(torch.zeros(G, N, K, device=device, dtype=torch.float8_e4m3fn))
+    a_s, b_s = torch.ones(G, max_m, device=device), torch.ones(G, N, device=device)
+    d = torch.zeros(G, max_m, N, dtype=torch.bfloat16, device=device)
+    mm = torch.zeros(G, dtype=torch.int32, device=device)
+
+    def run(n):
+        for _ in range(n):
+            deepgemm.m_grouped_fp8_gemm_nt_masked((a, a_s), (bp, b_s), d, mm, 4)
+    run(200)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    run(calls)
+    t1 = time.perf_counter()
+    torch.cuda.synchronize()
+    return {"entry": "deepgemm.m_grouped_fp8_gemm_nt_masked", "calls": calls,
+            "host_us_per_call": (t1 - t0) / calls * 1e6,
+            "native_argument_checks": _core._glue is not None}
+
+
 # ----------------------------------------------------------------------------- CPU arm
 def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 120.0):
     """The reference's CPU path (torch fp32 dequant-matmul, via the oracle) on a bounded sample
@@ -874,6 +901,7 @@ def main():
                 extras["contiguous_int8_prefill"] = bench_contig_prefill(device, 20, 3, peaks, "int8")
                 extras["contiguous_fp8_prefill"] = bench_contig_prefill(device, 20, 3, peaks, "fp8")
                 extras["masked_w4a8"] = bench_masked_w4a8(device, 200, 10, peaks)
+                extras["host_path"] = bench_host_path(device, cfg)
             del w
             torch.cuda.empty_cache()
             extras["ep_prefill"] = bench_ep_prefill(device, rank, world, 10, 3, peaks)

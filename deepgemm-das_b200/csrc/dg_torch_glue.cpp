@@ -207,5 +207,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("contiguous", &contiguous, "enqueue dg_contig_gemm if every check passes; False otherwise");
   m.def("set_status_words", &set_status_words);
   m.def("stats", []() { return std::make_pair(g_accepted, g_declined); }, "(calls enqueued here, calls handed back)");
-  m.def("abi_version", []() { return static_cast<int64_t>(dg_query(DG_QUERY_ABI_VERSION)); });
+  // the header this file was compiled against; the caller compares it with the library's own
+  m.def("abi_version", []() { return static_cast<int64_t>(DG_ABI_VERSION); });
 }

@@ -20,7 +20,7 @@ from ._cabi import (KIND_BF16, KIND_E4M3, KIND_I8, KIND_W4A8, SCALE_NONE, SCALE_
 
 try:                                   # native argument checks + launch (csrc/dg_torch_glue.cpp)
     from . import _glue
-    if _glue.abi_version() != _cabi.ABI_VERSION:
+    if _glue.abi_version() != _cabi.query(_cabi.QUERY_ABI_VERSION):
         _glue = None                   # built against another header: the ctypes path below still works
 except ImportError:
     _glue = None
