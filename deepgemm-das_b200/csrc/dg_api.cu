@@ -221,7 +221,7 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.M = pr.M;
   p.N = pr.N;
   p.K = pr.K;
-  p.kblocks = pr.K / elems_per_row;
+  p.kblocks = (pr.K + elems_per_row - 1) / elems_per_row;  // 8-bit kinds: a last half block reads zeros
   p.n_tiles = (pr.N + BN - 1) / BN;
   p.m_blocks = (pr.M + kBM - 1) / kBM;
   p.sched = pr.sched;
@@ -357,7 +357,7 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.M = pr.M;
   p.N = pr.N;
   p.K = pr.K;
-  p.kblocks = pr.K / elems_per_row;
+  p.kblocks = (pr.K + elems_per_row - 1) / elems_per_row;  // 8-bit kinds: a last half block reads zeros
   p.n_tiles = (pr.N + kPairBN - 1) / kPairBN;
   p.m_blocks = (pr.M + 255) / 256;  // super blocks of 256 rows
   p.sched = pr.sched;
@@ -636,9 +636,13 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
   if (pr.mode != MODE_MASKED && pr.M > DG_MAX_CONTIG_ROWS) return DG_ERR_TOO_LARGE;
   if (pr.mode == MODE_COMPACT && pr.kind == DG_KIND_W4A8) return DG_ERR_BAD_KIND;
   if (!pr.dense && pr.N % 16 != 0) return DG_ERR_BAD_SHAPE;
-  const int kq = (pr.kind == DG_KIND_BF16) ? 64 : (pr.kind == DG_KIND_W4A8 ? 256 : 128);
+  // INT8 / FP8: K % 64 (the reference's W6 block, deepgemm/m_group_gemm.py:815-818).  The kernels step K
+  // in 128-byte blocks: the packed weight then carries ceil(K / 128) blocks whose tail is zero
+  // (the packers pad it) and TMA fills the activation's last half block with zeros.
+  const int kq = (pr.kind == DG_KIND_W4A8) ? 256 : 64;
   if (pr.K % kq != 0) return DG_ERR_BAD_SHAPE;
-  if ((long long)pr.G * (pr.K / kq) * pr.N > 0x7fffffffLL) return DG_ERR_TOO_LARGE;
+  const int kstep = (pr.kind == DG_KIND_BF16) ? 64 : (pr.kind == DG_KIND_W4A8 ? 256 : 128);
+  if ((long long)pr.G * ((pr.K + kstep - 1) / kstep) * pr.N > 0x7fffffffLL) return DG_ERR_TOO_LARGE;
   if (pr.M == 0) return DG_OK;
   if (!pr.a || !pr.b || !pr.d || (!pr.sched && !pr.dense)) return DG_ERR_NULL_POINTER;
   if (pr.mode == MODE_COMPACT && !pr.offsets) return DG_ERR_NULL_POINTER;
@@ -1216,7 +1220,7 @@ const char* dg_strerror(int code) {
     case DG_ERR_NULL_POINTER: return "a required pointer is NULL";
     case DG_ERR_BAD_KIND: return "unknown operand kind";
     case DG_ERR_BAD_SHAPE:
-      return "bad shape: need N % 16 == 0, K % 128 == 0 (K % 64 for bf16, K % 256 for W4A8), groups >= 1";
+      return "bad shape: need N % 16 == 0, K % 64 == 0 (K % 256 for W4A8), groups >= 1";
     case DG_ERR_BAD_ALIGNMENT: return "a base pointer is not 16-byte aligned";
     case DG_ERR_BAD_SCALE_MODE: return "scale mode does not fit the operand kind";
     case DG_ERR_NO_DEVICE: return "no current CUDA device of compute capability 10.x (B200)";

@@ -49,6 +49,10 @@ inline bool b_dtype_ok(int kind, at::ScalarType t) {
   }
   return false;
 }
+// the packed weight of an INT8 / FP8 problem with K % 128 == 64 carries one zero-padded block more
+inline bool k_matches(int kind, int64_t packed_k, int64_t k) {
+  return packed_k == k || ((kind == DG_KIND_I8 || kind == DG_KIND_E4M3) && k % 128 == 64 && packed_k == k + 64);
+}
 inline bool d_dtype_ok(int kind, at::ScalarType t) {
   return t == at::kBFloat16 || (kind == DG_KIND_W4A8 && t == at::kHalf);
 }
@@ -99,7 +103,7 @@ bool masked_impl(int64_t kind, int64_t scale_mode, const Tensor& a, const Tensor
   int64_t bg, n, bk;
   if (!weight_dims(b, ki, &bg, &n, &bk)) return false;
   const int64_t g = a.size(0), max_m = a.size(1), k = a.size(2);
-  if (bg != g || bk != k || d.size(0) != g || d.size(1) != max_m || d.size(2) != n || masked_m.numel() != g)
+  if (bg != g || !k_matches(ki, bk, k) || d.size(0) != g || d.size(1) != max_m || d.size(2) != n || masked_m.numel() != g)
     return false;
   if (g > INT32_MAX || max_m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return false;
 
@@ -148,7 +152,7 @@ bool contiguous_impl(int64_t kind, int64_t scale_mode, const Tensor& a, const Te
   int64_t g, n, bk;
   if (!weight_dims(b, ki, &g, &n, &bk)) return false;
   const int64_t m_total = a.size(0), k = a.size(1);
-  if (bk != k || d.size(0) != m_total || d.size(1) != n || m_indices.numel() != m_total) return false;
+  if (!k_matches(ki, bk, k) || d.size(0) != m_total || d.size(1) != n || m_indices.numel() != m_total) return false;
   if (g > INT32_MAX || m_total > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return false;
 
   dg_contig_args args{};

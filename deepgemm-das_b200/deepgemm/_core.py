@@ -70,6 +70,12 @@ def packed_weight_dims(b: torch.Tensor, kind: int, k_hint: Optional[int] = None
     return int(g), int(n), int(kb) * _K_PER_BLOCK[kind]
 
 
+def _k_matches(kind: int, packed_k: int, k: int) -> bool:
+    """The packed weight of an INT8 / FP8 problem whose K is an odd multiple of 64 carries one
+    more, zero-padded, half block (the kernels step K in 128-byte blocks)."""
+    return packed_k == k or (kind in (KIND_I8, KIND_E4M3) and k % 128 == 64 and packed_k == k + 64)
+
+
 def _common_checks(kind, a, b, d, sched, what):
     if not (a.is_cuda and b.is_cuda and d.is_cuda and sched.is_cuda):
         raise RuntimeError(f"{what}: all tensors must be CUDA tensors (there is no CPU implementation)")
@@ -212,7 +218,7 @@ def grouped_gemm_masked(kind: int, scale_mode: int, a: torch.Tensor, b: torch.Te
     _common_checks(kind, a, b, d, masked_m, what)
     if not (bg == g):
         raise RuntimeError(f"{what}: weight has {bg} groups, activation has {g}")
-    if not (bk == k):
+    if not _k_matches(kind, bk, k):
         raise RuntimeError(f"{what}: weight K={bk} does not match activation K={k}")
     if not (tuple(d.shape) == (g, max_m, n)):
         raise RuntimeError(f"{what}: output must be {(g, max_m, n)}, got {tuple(d.shape)}")
@@ -265,7 +271,7 @@ def grouped_gemm_contiguous(kind: int, scale_mode: int, a: torch.Tensor, b: torc
     m_total, k = (int(x) for x in a.shape)
     g, n, bk = packed_weight_dims(b, kind)
     _common_checks(kind, a, b, d, m_indices, what)
-    if not (bk == k):
+    if not _k_matches(kind, bk, k):
         raise RuntimeError(f"{what}: weight K={bk} does not match activation K={k}")
     if scatter is None and not (tuple(d.shape) == (m_total, n)):
         raise RuntimeError(f"{what}: output must be {(m_total, n)}, got {tuple(d.shape)}")
@@ -322,7 +328,7 @@ def grouped_gemm_compact(kind: int, scale_mode: int, a: torch.Tensor, b: torch.T
     cap, k = (int(x) for x in a.shape)
     g, n, bk = packed_weight_dims(b, kind)
     _common_checks(kind, a, b, d, counts, what)
-    if not (bk == k):
+    if not _k_matches(kind, bk, k):
         raise RuntimeError(f"{what}: weight K={bk} does not match activation K={k}")
     if not (tuple(d.shape) == (cap, n)):
         raise RuntimeError(f"{what}: output must be {(cap, n)}, got {tuple(d.shape)}")

@@ -177,8 +177,13 @@ def _validate_8bit_enk(weight: torch.Tensor, what: str) -> torch.Tensor:
     if not weight.is_contiguous():
         raise ValueError(f"{what}: in-place pack requires contiguous [E,N,K] weight input")
     n, k = int(weight.size(1)), int(weight.size(2))
-    if n % 16 != 0 or k % 128 != 0:
-        raise ValueError(f"{what}: N={n}, K={k} must satisfy N%16==0 and K%128==0")
+    if n % 16 != 0 or k % 64 != 0:
+        raise ValueError(f"{what}: N={n}, K={k} must satisfy N%16==0 and K%64==0")
+    if k % 128 != 0:
+        # The reference's W6 block is 64 values (m_group_gemm.py:815-818); the kernels here step K
+        # in 128-byte blocks, so the last block is completed with zeros.  That tensor is larger
+        # than its source: it is a new allocation, the one case where the pack is not in place.
+        weight = torch.nn.functional.pad(weight.view(torch.uint8), (0, 64)).view(weight.dtype)
     return weight
 
 

@@ -56,10 +56,6 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
     size_n = int(output.shape[-1])
     if size_k % 64 != 0:
         raise RuntimeError(f"moe_marlin_prefill_down_fp8: size_k={size_k} must be a multiple of 64")
-    if size_k % 128 != 0:
-        # the reference's kernel takes K % 64; the tcgen05 kernels here step K in 128-byte blocks
-        raise RuntimeError(f"moe_marlin_prefill_down_fp8: size_k={size_k} must be a multiple of 128 on this "
-                           "backend (the reference accepts multiples of 64)")
     experts = int(b_scale.shape[0])
     em, blocks = int(sorted_token_ids.numel()), int(expert_ids.numel())
     if blocks == 0 or em % blocks != 0:

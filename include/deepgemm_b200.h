@@ -93,6 +93,10 @@ typedef enum dg_status {
  * BK = 128 elements for 8-bit kinds, 64 for bf16, 256 int4 values for W4A8: every packed
  * row is 128 bytes.  Each (kb, n-range) tile a thread block needs is one contiguous span, so
  * a single TMA box fetches it.  Same byte count as the row-major [G][N][K] source.
+ * INT8 / FP8 with K % 128 == 64 (the reference's packers take K % 64,
+ * deepgemm/m_group_gemm.py:815-818): the GEMM entry points take the true K, b_packed holds
+ * ceil(K / 128) blocks and the last 64 bytes of every row of the last block must be zero
+ * (pack a source padded to K + 64 columns of zeros; the Python packers do that).
  * For W4A8 each 16-byte chunk j (of 8) of a 128-byte row holds, in byte i, value
  * w[32j+i] in the high nibble and w[32j+16+i] in the low nibble (two's-complement
  * nibbles), so that `x & 0xF0` and `(x << 4) & 0xF0` each yield 16 consecutive int8
@@ -117,7 +121,7 @@ typedef struct dg_masked_args {
   int32_t num_groups;         /* G, 1..DG_MAX_GROUPS */
   int32_t max_m;              /* rows allocated per group */
   int32_t n;                  /* N, multiple of 16 */
-  int32_t k;                  /* K, multiple of 128 (64 for bf16, 256 for W4A8) */
+  int32_t k;                  /* K, multiple of 64 (256 for W4A8) */
   int32_t expected_m;         /* hint only: typical masked_m; never limits the rows computed */
   int32_t block_n;            /* 0 = choose; 128 / 256 = one-CTA tile width; 512 = two-CTA 256x256 tiles;
                                  32 / 64 = 128-wide kernel narrowed to that width (sparse routing) */
@@ -241,7 +245,7 @@ typedef struct dg_dense_args {
   int32_t batch;              /* 1..DG_MAX_GROUPS */
   int32_t m;
   int32_t n;                  /* any n >= 1; n % 8 != 0 and non-bf16 outputs use scalar stores */
-  int32_t k;                  /* multiple of 128 (64 for bf16) */
+  int32_t k;                  /* multiple of 64 */
   int32_t block_n;            /* 0 = choose; 128 / 256 / 512 as in dg_masked_args */
   int32_t reserved;           /* must be 0 */
   void*        debug_acc;     /* NULL, or [batch][m][n] raw 32-bit accumulators */

@@ -57,7 +57,7 @@ def test_calls_validate_before_touching_the_device():
     a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=1, max_m=4, n=60, k=128)
     assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -3      # N % 16
     a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=1, max_m=4, n=64, k=100)
-    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -3      # K % 128
+    assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -3      # K % 64
     a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=5000, max_m=4, n=64, k=128)
     assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -8
     a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=1, max_m=4, n=64, k=128)

@@ -253,3 +253,11 @@ def test_group_window_calls_cover_the_same_rows_as_one_call(bn):
                                   block_n=bn, status=st)
     torch.cuda.synchronize()
     assert st.tolist()[0] == 2       # DG_DEV_BAD_GROUP_INDEX
+
+
+@pytest.mark.parametrize("K", [192, 1088])
+def test_contiguous_k_an_odd_multiple_of_64(K):
+    rows = [300, 0, 511, 101]
+    c = gen_contig("int8", rows, 512, K, seed=K)
+    for bn in (0, 256, 512):
+        _check_int8_contig(c, rows, block_n=bn, what=f"contig int8 K={K} BN={bn}")

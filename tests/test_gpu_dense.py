@@ -92,6 +92,17 @@ def test_argument_errors():
     with pytest.raises(ValueError):
         deepgemm.fp8_gemm((q, e), (q[:, :64].contiguous(), e), d)         # K mismatch
     with pytest.raises(RuntimeError):
-        deepgemm.fp8_gemm((q[:, :64].contiguous(), e), (q[:, :64].contiguous(), e), d)   # K % 128 != 0
+        deepgemm.fp8_gemm((q[:, :32].contiguous(), e), (q[:, :32].contiguous(), e), d)   # K % 64 != 0
     with pytest.raises(RuntimeError):
         deepgemm.fp8_gemm((q.cpu(), e.cpu()), (q.cpu(), e.cpu()), d.cpu())
+
+
+@pytest.mark.parametrize("k", [64, 192, 1088])
+def test_dense_k_an_odd_multiple_of_64(k):
+    m, n = 130, 264
+    g = torch.Generator().manual_seed(k)
+    a = torch.randint(-8, 9, (m, k), generator=g).to(torch.int8)
+    b = torch.randint(-8, 9, (n, k), generator=g).to(torch.int8)
+    d = torch.zeros(m, n, dtype=torch.float32, device=DEV)
+    deepgemm.fp8_gemm((a.to(DEV), torch.ones(m, device=DEV)), (b.to(DEV), torch.ones(n, device=DEV)), d)
+    assert torch.equal(d.cpu(), O.exact_int_acc(a, b).float())

@@ -409,3 +409,24 @@ def test_masked_w4a8_shared_memory_unpack_kernel_bit_exact(order):
     w_x16 = (c["w4"].to(torch.int16) * 16).to(torch.int8)
     _check_int_case(c, _cabi.KIND_W4A8, w_x16, bp, c["b_scale"] / 16.0, block_n=512,
                     what=f"w4a8 shared-memory unpack {order}")
+
+
+@pytest.mark.parametrize("K", [64, 192, 448, 7232])
+def test_k_an_odd_multiple_of_64(K):
+    """The reference's packers and kernels take K % 64 (deepgemm/m_group_gemm.py:815-818).  Here the
+    packed weight gets a zero-filled last half block and TMA reads zeros past the end of an
+    activation row: int32 accumulators bit-exact through every tile width, also with garbage
+    where a kernel reading past the row's end would find it (the next row)."""
+    c = gen_masked_int8(3, 128, 272, K, [128, 0, 61], seed=K)
+    bp = P.marlin_i8_masked_weight(c["b"].clone())
+    assert tuple(bp.shape) == (3, (K + 64) // 128, 272, 128)
+    assert bool((bp[:, -1, :, 64:] == 0).all())
+    for bn in (0, 128, 256, 512):
+        _check_int_case(c, _cabi.KIND_I8, c["b"], bp, c["b_scale"], block_n=bn, what=f"K={K} BN={bn}")
+    # FP8, small integers (exact in fp32), public API
+    mm = [128, 3, 77]
+    f = gen_masked_fp8(3, 128, 256, K, mm, seed=K + 1, integer=True)
+    d = _run_fp8(f, False, None)
+    ref = O.ref_masked_scaled(f["a"], f["b"], f["a_scale"], f["b_scale"])
+    for g, m in enumerate(mm):
+        assert_bf16_within_ulp(d[g, :m], ref[g, :m], 0, f"fp8 K={K} group {g}")

@@ -75,9 +75,28 @@ def test_reference_framework_packer_matches_golden():
     assert torch.equal(P.pack_w4a8_weight_k_contiguous(g["u4"]), g["framework"])
 
 
+def test_k_an_odd_multiple_of_64_gets_a_zero_filled_last_block():
+    """K % 128 == 64 (accepted by the reference's packers, deepgemm/m_group_gemm.py:815-818): the
+    packed tensor is a new one with ceil(K / 128) blocks, the tail of the last block is zero and
+    the first K columns unpack to the source."""
+    g = torch.Generator().manual_seed(3)
+    w = torch.randint(-128, 128, (2, 32, 192), generator=g).to(torch.int8)
+    src = w.clone()
+    packed = P.marlin_i8_contiguous_weight(w)
+    assert tuple(packed.shape) == (2, 2, 32, 128)
+    assert torch.equal(w, src), "the source is left alone when the packed tensor cannot share its storage"
+    back = P.unpack_weight(packed, P.KIND_I8)
+    assert torch.equal(back[:, :, :192], src) and bool((back[:, :, 192:] == 0).all())
+    f = (torch.randn(1, 16, 64, generator=g)).to(torch.float8_e4m3fn)
+    pf = P.marlin_fp8_masked_weight(f.clone())
+    assert tuple(pf.shape) == (1, 1, 16, 128) and pf.dtype == torch.float8_e4m3fn
+    assert torch.equal(pf.view(torch.uint8)[0, 0, :, :64], f.view(torch.uint8)[0])
+    assert bool((pf.view(torch.uint8)[0, 0, :, 64:] == 0).all())
+
+
 def test_packer_argument_errors():
     with pytest.raises(ValueError):
-        P.marlin_i8_masked_weight(torch.zeros(2, 32, 100, dtype=torch.int8))       # K % 128
+        P.marlin_i8_masked_weight(torch.zeros(2, 32, 100, dtype=torch.int8))       # K % 64
     with pytest.raises(ValueError):
         P.marlin_i8_masked_weight(torch.zeros(2, 30, 128, dtype=torch.int8))       # N % 16
     with pytest.raises(ValueError):
