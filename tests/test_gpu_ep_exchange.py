@@ -58,7 +58,7 @@ def _rank_weights(rank, world, dev):
            (pk(w2[sl].clone().to(dev)), s2[sl].contiguous().to(dev))
 
 
-@pytest.mark.parametrize("world,slices", [(1, 1), (4, 1), (2, 3), (4, 2)])
+@pytest.mark.parametrize("world,slices", [(1, 1), (4, 1), (2, 3), (4, 2), (8, 1), (8, 2)])
 def test_emulated_ranks_match_one_gpu_layer(world, slices):
     dev = torch.device("cuda", 0)
     m_cap = 4 * T * TOPK + (E // world) * 256
