@@ -11,8 +11,21 @@ for p in (os.path.join(REPO, "deepgemm-das_b200"), os.path.join(REPO, "oracle"),
         sys.path.insert(0, p)
 
 
+def _build():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "dg_build", os.path.join(REPO, "deepgemm-das_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device of compute capability 10.x (B200)")
+    # Before any test module imports the package: libdeepgemm_b200.so and the host glue are
+    # looked up at import time (a no-op when the stamps match the sources).
+    if not hasattr(config, "workerinput"):      # once, not in every xdist worker
+        _build()
 
 
 def pytest_collection_modifyitems(config, items):
@@ -29,11 +42,5 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session", autouse=True)
 def _built_library():
-    """Builds libdeepgemm_b200.so if its sources changed (no-op when the stamp matches)."""
-    import importlib.util
-    spec = importlib.util.spec_from_file_location(
-        "dg_build", os.path.join(REPO, "deepgemm-das_b200", "build.py"))
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    mod.build()
+    """The library was built in pytest_configure; kept so that tests can depend on it by name."""
     yield
