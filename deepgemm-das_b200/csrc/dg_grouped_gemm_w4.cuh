@@ -45,6 +45,11 @@ constexpr int kW4SlotBase = 256;
 // each has two groups of four warps: unpack groups alternate rounds, epilogue groups alternate
 // work items (group e owns accumulator e).
 constexpr int kW4Groups = 2;
+// A group finds "its" stage of the weight ring by the parity of the stage's barrier, which only
+// tells neighbouring fills apart: the fill before the one it waits for must be one it consumed
+// itself, or it could take the barrier's initial state for its fill, read a stage that has not
+// landed and arrive on the stage-empty barrier a phase early.
+static_assert(kW4WStages % kW4Groups == 0, "the weight ring must be a multiple of the unpack groups");
 constexpr int kW4EpiWarp0 = 2;                            // warps 2..9
 constexpr int kW4UnpWarp0 = kW4EpiWarp0 + 4 * kW4Groups;  // warps 10..17
 constexpr int kW4TokWarp = kW4UnpWarp0 + 4 * kW4Groups;   // warp 18
