@@ -203,14 +203,21 @@ struct Problem {
   int scatter_world;
   int32_t* signal;
   int group_window;
+  // MODE_SORTED
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  const float* row_weight;
+  int block_m, num_blocks, num_sorted, real_topk, max_runs;
 };
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool kGather = false>
 int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   constexpr int STAGES = StagesFor<KIND, BN>::value;
   using L = SmemLayout<KIND, BN, STAGES>;
   static_assert(STAGES >= 2, "ring too shallow");
-  auto kernel = grouped_gemm_kernel<KIND, BN, STAGES>;
+  static_assert(kGatherDepth < STAGES, "the gathering warps would wait for stages they have not signalled");
+  auto kernel = grouped_gemm_kernel<KIND, BN, STAGES, kGather>;
 
   const int esize = (KIND == DG_KIND_BF16) ? 2 : 1;
   const int elems_per_row = kRowBytes / esize;  // A elements per 128-byte K block
@@ -237,19 +244,33 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.group_window = pr.group_window;
   p.scatter_tag = pr.scatter_tag;
   for (int r = 0; r < pr.scatter_world && pr.scatter_tag != nullptr; ++r) p.scatter_base[r] = pr.scatter_base[r];
+  p.tbl_groups = pr.mode == MODE_SORTED ? pr.max_runs : pr.G;
+  p.sorted_ids = pr.sorted_ids;
+  p.expert_ids = pr.expert_ids;
+  p.num_post_pad = pr.num_post_pad;
+  p.row_weight = pr.row_weight;
+  p.gather_a = pr.a;
+  p.block_m = pr.block_m;
+  p.num_blocks = pr.num_blocks;
+  p.num_sorted = pr.num_sorted;
+  p.real_topk = pr.real_topk;
+  p.size_m = pr.M;
 
+  // MODE_SORTED: 128-entry tiles of the routing list; every run of blocks may end in a partial one
   const long long max_blocks = pr.mode == MODE_MASKED    ? (long long)pr.G * p.m_blocks
                                : pr.mode == MODE_COMPACT ? (long long)p.m_blocks + pr.G
+                               : pr.mode == MODE_SORTED  ? (long long)(pr.num_sorted + kBM - 1) / kBM + pr.max_runs
                                                          : (long long)p.m_blocks;
   const long long max_items = max_blocks * p.n_tiles;
   if (max_items <= 0) return DG_OK;
   const int table_bytes = pr.mode == MODE_MASKED    ? (2 * pr.G + 1) * 4
                           : pr.mode == MODE_COMPACT ? (3 * pr.G + 1) * 4
+                          : pr.mode == MODE_SORTED  ? (4 * pr.max_runs + 2) * 4
                                                     : p.m_blocks * 4;
   int smem_bytes = L::total(table_bytes);
   if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
   // scattered output: wider store strips behind the table when they fit
-  if (pr.scatter_tag != nullptr || kWideStripsAlways) {
+  if (pr.scatter_tag != nullptr || pr.mode == MODE_SORTED || kWideStripsAlways) {
     const int off = (L::off_table + table_bytes + 15) & ~15;
     if (off + 4 * 4096 + 1024 <= dev.max_smem && off + 4 * 4096 + 1024 <= kMaxSmem) {
       p.wide_off = off;
@@ -307,8 +328,9 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // Weight boxes of 128, 64 and 32 rows: narrowed tiles (sparse routing) and the half items of a
   // split last round.
   CUtensorMap tm_b128 = tm_b, tm_b64 = tm_b, tm_b32 = tm_b;
-  p.narrow = (pr.mode != MODE_CONTIG) ? pr.narrow : 0;
-  p.split_tail = (pr.mode != MODE_CONTIG) ? 1 : 0;
+  const bool fixed_tiles = pr.mode == MODE_CONTIG || pr.mode == MODE_SORTED;
+  p.narrow = fixed_tiles ? 0 : pr.narrow;
+  p.split_tail = fixed_tiles ? 0 : 1;
   if (p.narrow || p.split_tail) {
     const uint32_t box128[2] = {(uint32_t)elems_per_row, 128u};
     const uint32_t box64[2] = {(uint32_t)elems_per_row, 64u};
@@ -336,7 +358,8 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   // With narrowing allowed the item count can reach max_blocks * ceil(N / 32).
   const long long grid_items = p.narrow ? max_blocks * ((pr.N + 31) / 32) : max_items;  // split tails need no more
   const int grid = static_cast<int>(grid_items < dev.sm_count ? grid_items : dev.sm_count);
-  kernel<<<grid, L::kThreads, smem_bytes, stream>>>(tm_a, tm_a64, tm_a32, tm_a8, tm_b, tm_b128, tm_b64, tm_b32, p);
+  kernel<<<grid, L::kThreads + (kGather ? kGatherThreads : 0), smem_bytes, stream>>>(tm_a, tm_a64, tm_a32, tm_a8, tm_b,
+                                                                                    tm_b128, tm_b64, tm_b32, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -644,7 +667,7 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
   const int kstep = (pr.kind == DG_KIND_BF16) ? 64 : (pr.kind == DG_KIND_W4A8 ? 256 : 128);
   if ((long long)pr.G * ((pr.K + kstep - 1) / kstep) * pr.N > 0x7fffffffLL) return DG_ERR_TOO_LARGE;
   if (pr.M == 0) return DG_OK;
-  if (!pr.a || !pr.b || !pr.d || (!pr.sched && !pr.dense)) return DG_ERR_NULL_POINTER;
+  if (!pr.a || !pr.b || !pr.d || (!pr.sched && !pr.dense && pr.mode != MODE_SORTED)) return DG_ERR_NULL_POINTER;
   if (pr.mode == MODE_COMPACT && !pr.offsets) return DG_ERR_NULL_POINTER;
   if (pr.scale_mode != DG_SCALE_NONE && (!pr.a_scale || !pr.b_scale)) return DG_ERR_NULL_POINTER;
   if (!aligned16(pr.a) || !aligned16(pr.b) || !aligned16(pr.d)) return DG_ERR_BAD_ALIGNMENT;
@@ -682,6 +705,8 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
     const long long pair_items = (rows / 256) * (pr.N / 256);
     if (pr.mode == MODE_COMPACT)
       bn = (pr.N >= 256 && (rows / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
+    else if (pr.mode == MODE_SORTED)  // the gathering producer lives in the one-CTA kernel
+      bn = (pr.N >= 256 && ((long long)pr.num_sorted / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
     else if (big_groups && pr.N >= 256 && pair_items >= 2LL * (dev->sm_count / 2))
       bn = 512;
     else if (pr.mode == MODE_CONTIG)
@@ -697,6 +722,7 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
     }
   }
   if (bn == 512 && (pr.N < 256 || pr.mode == MODE_COMPACT)) bn = 128;
+  if (bn == 512 && pr.mode == MODE_SORTED) bn = 256;
   if (bn == 512 && pr.signal != nullptr) bn = 256;  // completion counters live in the one-CTA kernel
   if (bn == 512 && scalar_out) bn = 256;
   if (pr.kind == DG_KIND_W4A8) {
@@ -711,6 +737,12 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
       case DG_KIND_BF16: return launch_pair<DG_KIND_BF16>(pr, *dev, stream);
       default: return DG_ERR_BAD_KIND;
     }
+  }
+  if (pr.mode == MODE_SORTED) {
+    if (pr.kind == DG_KIND_I8)
+      return bn == 256 ? launch<DG_KIND_I8, 256, true>(pr, *dev, stream) : launch<DG_KIND_I8, 128, true>(pr, *dev, stream);
+    return bn == 256 ? launch<DG_KIND_E4M3, 256, true>(pr, *dev, stream)
+                     : launch<DG_KIND_E4M3, 128, true>(pr, *dev, stream);
   }
   switch (pr.kind) {
     case DG_KIND_I8:
@@ -846,6 +878,46 @@ int dg_contig_gemm(const dg_contig_args* a, void* stream) {
     pr.scatter_base = a->scatter_base;
     pr.scatter_world = a->scatter_world;
   }
+  return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
+}
+
+int dg_sorted_gemm(const dg_sorted_args* a, void* stream) {
+  if (a == nullptr) return DG_ERR_NULL_POINTER;
+  if (a->kind != DG_KIND_I8 && a->kind != DG_KIND_E4M3) return DG_ERR_BAD_KIND;
+  if (a->num_sorted < 0 || a->block_m < 1 || a->num_blocks < 0 || a->real_topk < 1 || a->size_m < 0)
+    return DG_ERR_BAD_ARGUMENT;
+  if ((long long)a->num_blocks * a->block_m < a->num_sorted) return DG_ERR_BAD_ARGUMENT;
+  if (a->size_m > 0x00FFFFFF * (long long)a->real_topk || a->num_sorted > DG_MAX_CONTIG_ROWS) return DG_ERR_TOO_LARGE;
+  if (a->num_sorted == 0 || a->num_blocks == 0 || a->size_m == 0) return DG_OK;
+  if (!a->sorted_token_ids || !a->expert_ids || !a->num_tokens_post_pad) return DG_ERR_NULL_POINTER;
+  Problem pr{};
+  pr.kind = a->kind;
+  pr.scale_mode = DG_SCALE_PER_CHANNEL;
+  pr.mode = MODE_SORTED;
+  pr.a = a->a;
+  pr.b = a->b_packed;
+  pr.d = a->d;
+  pr.a_scale = a->a_scale;
+  pr.b_scale = a->b_scale;
+  pr.row_weight = a->row_weight;
+  pr.sorted_ids = a->sorted_token_ids;
+  pr.expert_ids = a->expert_ids;
+  pr.num_post_pad = a->num_tokens_post_pad;
+  pr.G = a->num_groups;
+  pr.M = a->size_m;
+  pr.N = a->n;
+  pr.K = a->k;
+  pr.block_m = a->block_m;
+  pr.num_blocks = a->num_blocks;
+  pr.num_sorted = a->num_sorted;
+  pr.real_topk = a->real_topk;
+  // runs of blocks with one expert: one per expert in a sorted list, some more for the blocks of
+  // experts that live elsewhere; more than this many and the launch reports DG_DEV_BAD_GROUP_INDEX
+  const long long runs = 2LL * a->num_groups + 2;
+  pr.max_runs = static_cast<int>(runs < a->num_blocks ? runs : a->num_blocks);
+  pr.out_kind = DG_OUT_BF16;
+  pr.status = a->status;
+  if (a->n % 8 != 0) return DG_ERR_BAD_SHAPE;  // result rows leave through 16-byte stores
   return validate_and_launch(pr, static_cast<cudaStream_t>(stream));
 }
 

@@ -43,7 +43,7 @@ constexpr int kRowBytes = 128;   // bytes of K per shared-memory row (one swizzl
 constexpr int kATileBytes = kBM * kRowBytes;
 constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per block on sm_100
 
-enum : int { MODE_MASKED = 0, MODE_CONTIG = 1, MODE_COMPACT = 2 };
+enum : int { MODE_MASKED = 0, MODE_CONTIG = 1, MODE_COMPACT = 2, MODE_SORTED = 3 };
 
 // Where a bounded wait gave up (reported in status[2]).
 enum : int {
@@ -91,6 +91,23 @@ struct KernelParams {
   int group_window;  // contiguous layout: 0, or 1 + the id (in m_indices' numbering) of this call's group 0;
                      // entries that name a group outside the call are then skipped silently
   int wide_off;  // 0, or offset in shared memory of four 32-row x 128-byte store strips (scattered output)
+  // MODE_SORTED (one-CTA kernel): the rows are named by a routing list instead of lying in place.
+  // Entry i of sorted_ids packs (top-k slot << 24 | token) and names row token * real_topk + slot
+  // of the [size_m][K] activation and of the [size_m][N] output; entries come in blocks of
+  // block_m that share expert_ids[i / block_m] (-1: the expert lives on another rank, its rows
+  // are written as zeros); entries at or beyond *num_post_pad, with slot >= real_topk or a row
+  // >= size_m are padding.  A tile is 128 consecutive entries of a run of blocks with one expert:
+  // the producer warp fetches the rows one by one (a one-row TMA box each, the swizzle is a
+  // function of the shared-memory address, so 128 of them make the tile a 128-row box would),
+  // the epilogue writes each result row to its place.  a_scale is per activation row, row_weight
+  // (nullable) multiplies it.
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  const float* row_weight;
+  const void* gather_a;  // the [size_m][K] activation the rows are gathered from
+  int block_m, num_blocks, num_sorted, real_topk, size_m;
+  int tbl_groups;  // entries per array of the schedule table: G, or (MODE_SORTED) the most runs it holds
   int narrow;  // masked / compact: 0 = tiles stay BN columns wide, 1 = the kernel may narrow them
                // (down to 32 columns) when few groups have rows, 128 / 64 / 32 = forced width
 };
@@ -417,6 +434,15 @@ struct TileCoord {
 // off[G]; item = (global row block) * n_tiles + column tile.  Contiguous table: list of row
 // blocks as (group << 16 | block).  `bn` / `n_tiles` are the tile width in use and the number
 // of column tiles at that width.
+// MODE_SORTED: activation / output row named by entry `pos` of the routing list, -1 for padding.
+__device__ __forceinline__ int sorted_row(const KernelParams& p, int pos, int post_pad) {
+  if (pos >= post_pad) return -1;
+  const uint32_t id = static_cast<uint32_t>(p.sorted_ids[pos]);
+  const int slot = static_cast<int>(id >> 24);
+  const long long row = static_cast<long long>(id & 0x00FFFFFFu) * p.real_topk + slot;
+  return (slot >= p.real_topk || row >= p.size_m) ? -1 : static_cast<int>(row);
+}
+
 struct ItemDecoder {
   const KernelParams& p;
   const int32_t* tbl;
@@ -439,7 +465,7 @@ struct ItemDecoder {
     }
     if (p.mode != MODE_CONTIG) {
       const int32_t* cnt = tbl;
-      const int32_t* pref = tbl + p.G;
+      const int32_t* pref = tbl + p.tbl_groups;
       const int blk = item / n_tiles;
       while (blk >= pref[cursor + 1]) ++cursor;  // items only grow, so the cursor persists
       const int mt = blk - pref[cursor];
@@ -450,6 +476,9 @@ struct ItemDecoder {
       if (p.mode == MODE_COMPACT) {  // rows of group g start at offsets[g] in the flat tensor
         t.row0 += tbl[2 * p.G + 1 + cursor];
         t.rows_valid = min(t.rows_valid, p.M - t.row0);
+      } else if (p.mode == MODE_SORTED) {  // the cursor counts runs: expert (-1: zeros) and first list entry
+        t.g = tbl[2 * p.tbl_groups + 1 + cursor];
+        t.row0 += tbl[3 * p.tbl_groups + 1 + cursor];
       }
     } else {
       const int bi = item / n_tiles;
@@ -463,8 +492,12 @@ struct ItemDecoder {
   }
 };
 
-template <int KIND, int BN, int STAGES>
-__global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads, 1)
+// kGather: the instantiation behind MODE_SORTED, with four more warps that fetch the rows of a
+// tile by index (the other instantiations carry none of that code).
+constexpr int kGatherThreads = 128;
+constexpr int kGatherDepth = 2;  // K blocks a gathering thread keeps in flight behind the one it issues
+template <int KIND, int BN, int STAGES, bool kGather = false>
+__global__ void __launch_bounds__(SmemLayout<KIND, BN, STAGES>::kThreads + (kGather ? kGatherThreads : 0), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_a64,
                     const __grid_constant__ CUtensorMap tm_a32,
@@ -501,13 +534,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   volatile int* n_items_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 8);
   volatile int* bn_eff_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 12);
   volatile int* split_from_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 16);
+  volatile int* post_pad_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 20);  // MODE_SORTED
   int32_t* tbl = reinterpret_cast<int32_t*>(smem + L::off_table);
 
   // ------------------------------------------------------------------ one-time set-up
   if (tid == 0) {
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full(s), 1);
+      mbar_init(bar_full(s), kGather ? 5 : 1);  // the producer thread (+ the four gathering warps)
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -523,7 +557,64 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   // Schedule table.  Masked / compact: cnt[G] (clamped rows per group), pref[G+1] (running
   // number of work items) and, compact, off[G] (first row of each group).  Contiguous: the
   // list of 128-row blocks whose first row belongs to a group, as (group << 16 | block).
-  if (p.mode != MODE_CONTIG) {
+  if (p.mode == MODE_SORTED) {
+    // Runs of list blocks with one expert: cnt[r] entries, pref[r + 1] running 128-entry tiles,
+    // run_e[r] the expert (-1: rows to be written as zeros), run_p0[r] the first list entry.
+    const int RM = p.tbl_groups;
+    int32_t* cnt = tbl;
+    int32_t* pref = tbl + RM;
+    int32_t* run_e = tbl + 2 * RM + 1;
+    int32_t* run_p0 = tbl + 3 * RM + 1;
+    if (warp == 0) {
+      const int post = max(0, min(*p.num_post_pad, p.num_sorted));
+      const int nb = min(p.num_blocks, (post + p.block_m - 1) / p.block_m);
+      int runs = 0;
+      bool bad = false;
+      for (int b0 = 0; b0 < nb; b0 += 32) {
+        const int b = b0 + lane;
+        const int e = (b < nb) ? p.expert_ids[b] : 0;
+        const bool start = b < nb && (b == 0 || p.expert_ids[b - 1] != e);
+        const unsigned mask = __ballot_sync(0xffffffffu, start);
+        const int r = runs + __popc(mask & ((1u << lane) - 1u));
+        if (start && r < RM) {
+          run_e[r] = e >= p.G ? -2 : (e < 0 ? -1 : e);  // -2: no such expert, nothing is computed
+          run_p0[r] = b * p.block_m;
+          bad |= e >= p.G;
+        }
+        runs += __popc(mask);
+      }
+      __syncwarp();
+      const bool overflow = runs > RM;  // more runs than the table holds: compute nothing, say so
+      if (overflow) runs = 0;
+      int running = 0;
+      for (int r0 = 0; r0 < runs; r0 += 32) {
+        const int r = r0 + lane;
+        int x = 0;
+        if (r < runs) {
+          const int end = (r + 1 < runs) ? run_p0[r + 1] : nb * p.block_m;
+          const int rows = run_e[r] == -2 ? 0 : end - run_p0[r];
+          cnt[r] = rows;
+          x = (rows + kBM - 1) / kBM;
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, x, o);
+          if (lane >= o) x += y;
+        }
+        if (r < runs) pref[r + 1] = running + x;
+        running += __shfl_sync(0xffffffffu, x, 31);
+      }
+      if (lane == 0) {
+        pref[0] = 0;
+        *bn_eff_s = BN;
+        *split_from_s = 0x7fffffff;
+        *n_items_s = running * p.n_tiles;
+        *post_pad_s = post;
+      }
+      if ((__any_sync(0xffffffffu, bad) || overflow) && lane == 0 && blockIdx.x == 0 && p.status != nullptr)
+        atomicCAS(p.status, DG_DEV_OK, DG_DEV_BAD_GROUP_INDEX);
+    }
+  } else if (p.mode != MODE_CONTIG) {
     int32_t* cnt = tbl;
     int32_t* pref = tbl + p.G;
     for (int g = tid; g < p.G; g += blockDim.x) {
@@ -621,7 +712,93 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int nt_eff = (p.N + bn_eff - 1) / bn_eff;    // column tiles at that width
 
   // ------------------------------------------------------------------ roles
-  if (warp == 0) {
+  if (kGather && warp >= 6) {
+    if constexpr (kGather) {
+      // ---- gathering warps (MODE_SORTED): thread g copies the 16-byte piece g % 8 of rows g / 8,
+      // g / 8 + 16, ... of the tile, so that eight neighbouring lanes read one row's 128 bytes.
+      // A thread keeps kGatherDepth K blocks in flight: after issuing block i it waits for block
+      // i - kGatherDepth, makes it visible to the tensor core's proxy and its warp signals the
+      // stage.
+      const int g = tid - L::kThreads;
+      const int piece = g & 7, rsub = g >> 3;
+      const int post = *post_pad_s;
+      const uint8_t* a_bytes = static_cast<const uint8_t*>(p.gather_a);
+      const size_t row_bytes = static_cast<size_t>(p.K) * (KIND == DG_KIND_BF16 ? 2 : 1);
+      ItemDecoder dec(p, tbl, BN, p.n_tiles);
+      uint32_t it = 0;
+      bool ok = true;
+      auto signal_done = [&](uint32_t j) {  // K block j of this block's sequence has landed
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full(j % STAGES));
+      };
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        const TileCoord t = dec.get(item);
+        if (t.g < 0) continue;  // rows of an absent expert: nothing to load
+        int src[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = rsub + 16 * i;
+          src[i] = r < t.rows_valid ? sorted_row(p, t.row0 + r, post) : -1;
+        }
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait_warp(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const size_t col = static_cast<size_t>(kb) * kRowBytes + piece * 16;
+          const uint32_t in_row = col < row_bytes ? 16u : 0u;  // last half block of K % 128 == 64: zeros
+          const uint32_t a_dst = base + L::off_a + s * L::kAStage;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = rsub + 16 * i;
+            if (src[i] >= 0)
+              cp_async_16(a_dst + r * kRowBytes + ((piece ^ (r & 7)) << 4),
+                          a_bytes + static_cast<size_t>(src[i]) * row_bytes + (in_row ? col : 0), in_row);
+          }
+          cp_async_commit();
+          if (it >= kGatherDepth) {
+            cp_async_wait_group<kGatherDepth>();
+            signal_done(it - kGatherDepth);
+          }
+        }
+      }
+      cp_async_wait_group<0>();
+      if (ok)
+        for (uint32_t j = it > kGatherDepth ? it - kGatherDepth : 0; j < it; ++j) signal_done(j);
+    }
+  } else if (warp == 0 && p.mode == MODE_SORTED) {
+    if (lane == 0) {
+      // ---- weight producer of MODE_SORTED (the activation rows come from the gathering warps)
+      const uint64_t pol_b = l2_policy_evict_first();
+      ItemDecoder dec(p, tbl, BN, p.n_tiles);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        const TileCoord t = dec.get(item);
+        if (t.g < 0) continue;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(bar_full(s), static_cast<uint32_t>(BN) * kRowBytes);
+          int bx, by;
+          weight_coords(p, t.g, t.n0, kb, kElemsPerRow, bx, by);
+          tma_load_2d(base + L::off_b + s * L::kBStage, &tm_b, bar_full(s), bx, by, pol_b);
+        }
+      }
+      if (*abort_flag) {  // the stage barriers also count the gathering warps: just let copies land
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+  } else if (warp == 0) {
     if (lane == 0) {
       // ---- TMA producer.  kNarrow = false is the straight-line loop for full-width tiles
       // (one K block per stage); kNarrow = true handles 64 / 32-column tiles.
@@ -699,7 +876,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (!mbar_wait_bounded(bar_acc_empty(buf), aph ^ 1u, abort_flag, SITE_MMA_ACC_EMPTY)) return;
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          for (int kb0 = 0; kb0 < p.kblocks; kb0 += kps, ++it) {
+          const int k_end = (p.mode == MODE_SORTED && t.g < 0) ? 0 : p.kblocks;  // zero rows: no products
+          for (int kb0 = 0; kb0 < k_end; kb0 += kps, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
             if (!mbar_wait_bounded(bar_full(s), ph, abort_flag, SITE_MMA_FULL)) return;
@@ -756,7 +934,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       EpiRow row;
       row.as = 1.0f;
       row.bs_g = 1.0f;
-      if (warp_has_rows) {
+      const bool sorted = p.mode == MODE_SORTED;
+      if (warp_has_rows && sorted) {
+        // the list entry of this lane's row names the activation / output row
+        if (t.g >= 0)
+          stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, t.width, p.N, lane,
+                            p.scale_mode == DG_SCALE_PER_CHANNEL);
+        const int srow = (lane < rows_per_warp && row_in_tile < t.rows_valid)
+                             ? sorted_row(p, t.row0 + row_in_tile, *post_pad_s) : -1;
+        rv = srow >= 0;
+        grow = rv ? static_cast<size_t>(srow) : 0;
+        if (rv) row.as = p.row_weight ? __fmul_rn(p.row_weight[grow], p.a_scale[grow]) : p.a_scale[grow];
+        if (p.scale_mode == DG_SCALE_TENSOR_WISE && t.g >= 0) row.bs_g = p.b_scale[t.g];
+      } else if (warp_has_rows) {
         stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, t.width, p.N, lane,
                           p.scale_mode == DG_SCALE_PER_CHANNEL);
         rv = lane < rows_per_warp && row_in_tile < t.rows_valid;
@@ -767,13 +957,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       if (!mbar_wait_warp(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
-      if (warp_has_rows) {
+      if (warp_has_rows && sorted && t.g < 0) {
+        // rows of an expert that lives elsewhere: zeros (one 16-byte store per lane and row
+        // covers up to 256 columns; the accumulator was never written and is not read)
+        const unsigned rows_mask = __ballot_sync(0xffffffffu, rv);
+        const int cols = min(t.width, p.N - t.n0);
+        for (int r = 0; r < 32; ++r) {
+          if (!((rows_mask >> r) & 1u)) continue;
+          const size_t zr = __shfl_sync(0xffffffffu, grow, r);
+          __nv_bfloat16* dst = p.d + zr * p.N + t.n0;
+          for (int c = lane * 8; c < cols; c += 256) {
+            if (c + 8 <= cols && (p.N & 7) == 0)
+              *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
+            else
+              for (int i = c; i < min(c + 8, cols); ++i) dst[i] = __float2bfloat16_rn(0.0f);
+          }
+        }
+      } else if (warp_has_rows) {
         row.bs_row = bs_s;  // PER_CHANNEL only
         const size_t d_off = grow * p.N + t.n0;  // in output elements
         row.d_row = p.out_kind == 2 ? reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<float*>(p.d) + d_off)
                                     : p.d + d_off;
-        const bool scatter = p.mode == MODE_CONTIG && p.scatter_tag != nullptr;
-        if (scatter && rv) {
+        const bool scatter = sorted || (p.mode == MODE_CONTIG && p.scatter_tag != nullptr);
+        if (scatter && rv && !sorted) {
           const int tag = p.scatter_tag[grow];
           row.d_row = static_cast<__nv_bfloat16*>(p.scatter_base[(tag >> 24) & 15]) +
                       (size_t)(tag & 0xFFFFFF) * p.N + t.n0;

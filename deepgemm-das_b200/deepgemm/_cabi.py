@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "dg_masked_gemm",
     "dg_contig_gemm",
     "dg_compact_gemm",
+    "dg_sorted_gemm",
     "dg_dense_gemm",
     "dg_quant_group_rows",
     "dg_quant_group_scratch_bytes",
@@ -111,6 +112,31 @@ class CompactArgs(C.Structure):
         ("expected_m", C.c_int32),
         ("block_n", C.c_int32),
         ("debug_acc", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
+class SortedGemmArgs(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("num_groups", C.c_int32),
+        ("a", C.c_void_p),
+        ("b_packed", C.c_void_p),
+        ("d", C.c_void_p),
+        ("a_scale", C.c_void_p),
+        ("row_weight", C.c_void_p),
+        ("b_scale", C.c_void_p),
+        ("sorted_token_ids", C.c_void_p),
+        ("expert_ids", C.c_void_p),
+        ("num_tokens_post_pad", C.c_void_p),
+        ("num_sorted", C.c_int32),
+        ("num_blocks", C.c_int32),
+        ("block_m", C.c_int32),
+        ("size_m", C.c_int32),
+        ("real_topk", C.c_int32),
+        ("n", C.c_int32),
+        ("k", C.c_int32),
+        ("reserved", C.c_int32),
         ("status", C.c_void_p),
     ]
 
@@ -307,6 +333,8 @@ def _load() -> C.CDLL:
     lib.dg_quant_group_rows_noalloc.restype = C.c_int
     lib.dg_quant_group_scratch_bytes.argtypes = [C.c_int32, C.c_int32]
     lib.dg_quant_group_scratch_bytes.restype = C.c_size_t
+    lib.dg_sorted_gemm.argtypes = [C.POINTER(SortedGemmArgs), C.c_void_p]
+    lib.dg_sorted_gemm.restype = C.c_int
     lib.dg_dense_gemm.argtypes = [C.POINTER(DenseArgs), C.c_void_p]
     lib.dg_dense_gemm.restype = C.c_int
     lib.dg_group_sorted_rows.argtypes = [C.POINTER(GroupSortedArgs), C.c_void_p]

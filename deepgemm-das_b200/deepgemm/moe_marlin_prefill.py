@@ -8,15 +8,15 @@ Same name, argument order and checks as the reference's ``deepgemm/moe_marlin_pr
 for every ``row = token * real_topk + slot`` named by ``sorted_token_ids`` (``slot << 24 | token``,
 blocks of ``len(sorted_token_ids) / len(expert_ids)`` entries per expert), zeros for rows whose
 block has ``expert_ids == -1``; rows the list never names are left untouched, as in the
-reference.  The reference's kernel gathers 32-row blocks itself; a tcgen05 tile wants 128 rows of
-one expert, so the rows are first regrouped into 128-row blocks per expert
-(``dg_group_sorted_rows``, which also zeroes the rows of absent experts) and the contiguous
-grouped GEMM then writes every result row straight to its place in ``output`` from its epilogue
-(``scatter_tag``): two device steps, five launches, no pass over the result afterwards.  The
-regrouped operand lives in a workspace kept per problem size, so steady-state calls allocate
-nothing.  ``b_qweight`` must come from ``marlin_fp8_contiguous_weight`` /
-``marlin_i8_contiguous_weight`` of this package; K must be a multiple of 128 (the reference:
-64).
+reference.  Like the reference's kernel, which gathers its 32-row blocks itself, the GEMM does the
+gathering: ``dg_sorted_gemm`` tiles every expert's run of the list into 128 entries, its producer
+warp fetches the rows of a tile by index and its epilogue writes each result row to its place
+(and zeros for absent experts): one launch, no allocation, no pass over the operands or the
+result.  Large problems with many rows per expert (where two-CTA 256 x 256 tiles pay) take two
+steps instead: ``dg_group_sorted_rows`` regroups the rows into 128-row blocks per expert in a
+workspace kept per problem size, and the contiguous grouped GEMM scatters the result rows from
+its epilogue (``scatter_tag``).  Both give the same bytes.  ``b_qweight`` must come from
+``marlin_fp8_contiguous_weight`` / ``marlin_i8_contiguous_weight`` of this package.
 """
 from __future__ import annotations
 
@@ -64,6 +64,22 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
         raise RuntimeError("output, topk_weights and a_scale must have one row per row of input")
     dev = input.device
     kind = _cabi.KIND_E4M3 if input.dtype == torch.float8_e4m3fn else _cabi.KIND_I8
+    path = FORCE_PATH or ("regroup" if _two_cta_tiles_pay(em, experts, size_n) else "gather")
+    if path == "gather":
+        if not (input.is_contiguous() and output.is_contiguous()):
+            raise RuntimeError("input and output must be contiguous")
+        args = _cabi.SortedGemmArgs(
+            kind=kind, num_groups=experts, a=input.data_ptr(), b_packed=b_qweight.data_ptr(),
+            d=output.data_ptr(), a_scale=a_scale.contiguous().data_ptr(),
+            row_weight=topk_weights.contiguous().data_ptr(),
+            b_scale=b_scale.reshape(experts, size_n).contiguous().data_ptr(),
+            sorted_token_ids=sorted_token_ids.contiguous().data_ptr(),
+            expert_ids=expert_ids.contiguous().data_ptr(),
+            num_tokens_post_pad=num_tokens_post_pad.contiguous().data_ptr(),
+            num_sorted=em, num_blocks=blocks, block_m=em // blocks, size_m=size_m, real_topk=int(real_topk),
+            n=size_n, k=size_k, reserved=0, status=_core.device_status_words(dev).data_ptr())
+        _core._launch(_cabi.lib.dg_sorted_gemm, args, dev, "dg_sorted_gemm")
+        return output
     m_cap = quant_group_capacity(em, experts, 128)
     ws = _workspace(dev, m_cap, size_k, em, experts, input.dtype)
     out2d = output.view(size_m, size_n)
@@ -84,6 +100,16 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
                                   b_scale.reshape(experts, size_n), ws["m_idx"],
                                   scatter=(ws["src"], _cabi.pointer_array([out2d.data_ptr()]), 1))
     return output
+
+
+# None: choose by size; "gather" / "regroup": tests pin one of the two paths
+FORCE_PATH = None
+
+
+def _two_cta_tiles_pay(em: int, experts: int, size_n: int) -> bool:
+    """The rule of the contiguous GEMM's tile choice: 256 x 256 two-CTA tiles from about 320
+    routed rows per expert upwards, when there are at least two of them for every SM pair."""
+    return em // max(experts, 1) >= 320 and (em // 256) * (size_n // 256) >= 148
 
 
 _WORKSPACES = {}

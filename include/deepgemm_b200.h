@@ -265,6 +265,45 @@ DG_API int dg_dense_gemm(const dg_dense_args* args, void* stream);
 #define DG_NIBBLE_HIGH_FIRST 0
 #define DG_NIBBLE_LOW_FIRST  1
 
+/* Grouped GEMM on a routing list (the second-stage op of a MoE layer whose rows are named by a
+ * vLLM-style sorted_token_ids / expert_ids pair): replaces the launcher behind
+ * moe_w8a8_marlin_prefill_down_fp8 (csrc/arch/gfx938/moe_w8a8_marlin_prefill_down_fp8.cu:27-110,
+ * device code csrc/include/moe_marlin/moe_marlin_prefill_down_fp8_device.inc.h:58-64,262-272).
+ *   entry i of sorted_token_ids = (slot << 24 | token) names row = token * real_topk + slot;
+ *   blocks of block_m entries share expert e = expert_ids[i / block_m];
+ *   entries at or beyond *num_tokens_post_pad, with slot >= real_topk or row >= size_m are padding.
+ *   e >= 0:  D[row][n] = bf16_rne( (float(sum_k A[row][k]*B[e][n][k]) * (row_weight[row]*a_scale[row])) * b_scale[e][n] )
+ *   e <  0:  D[row][:] = 0          (the expert lives on another rank)
+ *   rows the list never names are not written.
+ * One launch: the kernel's producer fetches the rows of a tile by index and its epilogue writes
+ * each result row to its place; nothing is regrouped or allocated.  Blocks of one expert should
+ * follow one another (they do in a list sorted by expert): every run of blocks is tiled on its
+ * own, and more than 2 * num_groups + 2 runs are refused on the device (DG_DEV_BAD_GROUP_INDEX in
+ * `status`, nothing computed).  INT8 / FP8, per-channel weight scales, bf16 output, N % 8 == 0. */
+typedef struct dg_sorted_args {
+  int32_t kind;                        /* DG_KIND_I8 or DG_KIND_E4M3 */
+  int32_t num_groups;                  /* experts held in b_packed */
+  const void*    a;                    /* [size_m][K] quantised activations */
+  const void*    b_packed;             /* packed layout, num_groups experts */
+  void*          d;                    /* [size_m][N] bf16 */
+  const float*   a_scale;              /* [size_m] */
+  const float*   row_weight;           /* NULL, or [size_m]: multiplies a_scale (top-k weights) */
+  const float*   b_scale;              /* [num_groups][N] */
+  const int32_t* sorted_token_ids;     /* [num_sorted] */
+  const int32_t* expert_ids;           /* [num_blocks] */
+  const int32_t* num_tokens_post_pad;  /* device scalar: entries of the list in use */
+  int32_t num_sorted;
+  int32_t num_blocks;
+  int32_t block_m;                     /* entries per block; num_blocks * block_m >= num_sorted */
+  int32_t size_m;                      /* rows of a and d */
+  int32_t real_topk;
+  int32_t n;
+  int32_t k;
+  int32_t reserved;
+  int32_t*       status;               /* NULL, or int32[DG_STATUS_WORDS] */
+} dg_sorted_args;
+DG_API int dg_sorted_gemm(const dg_sorted_args* args, void* stream);
+
 /* Re-lays a row-major weight [G][N][K] (W4A8: [G][N][K/2] bytes) into the packed layout.
  * src and dst must not overlap (the Python packers pass a per-group temporary to get the
  * reference's in-place behaviour).  Stands in for the torch re-layout code of

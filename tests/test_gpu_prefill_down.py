@@ -15,6 +15,16 @@ DEV = "cuda"
 FP8 = torch.float8_e4m3fn
 
 
+@pytest.fixture(params=["gather", "regroup"], autouse=True)
+def _path(request):
+    """Every test runs through both implementations: the one-launch GEMM that gathers the rows
+    itself, and the regroup step + scattering contiguous GEMM used for large problems."""
+    from deepgemm import moe_marlin_prefill as M
+    M.FORCE_PATH = request.param
+    yield request.param
+    M.FORCE_PATH = None
+
+
 def _case(kind, t, k, e, hid, n, block_m, seed, local=None, extra_blocks=0):
     g = torch.Generator().manual_seed(seed)
     topk_ids = torch.rand(t, e, generator=g).topk(k, dim=1).indices
@@ -79,6 +89,23 @@ def test_experts_of_other_ranks_give_zero_rows():
     out, want = _run(c, "int8")
     assert_bf16_within_ulp(out, want, 1, "prefill-down, half of the experts remote")
     assert float(want.abs().sum()) > 0 and torch.any(torch.all(out == 0, dim=1))
+
+
+def test_gathering_gemm_is_one_launch_and_matches_the_regroup_path_bit_for_bit(_path):
+    from deepgemm import _cabi, moe_marlin_prefill as M
+    if _path != "gather":
+        pytest.skip("compares the two paths once")
+    for kind, n in (("int8", 512), ("fp8", 384)):
+        c = _case(kind, 300, 4, 7, 448, n, 16, seed=77, local={0, 2, 3, 5, 6}, extra_blocks=3)
+        before = _cabi.query(_cabi.QUERY_LAUNCH_COUNT)
+        out_g, _ = _run(c, kind)
+        # the weight packer launches once per expert; the op itself is one launch
+        assert _cabi.query(_cabi.QUERY_LAUNCH_COUNT) - before == c["w"].shape[0] + 1
+        M.FORCE_PATH = "regroup"
+        out_r, _ = _run(c, kind)
+        M.FORCE_PATH = "gather"
+        assert torch.equal(out_g.view(torch.int16), out_r.view(torch.int16)), kind
+    deepgemm.check_device_status()
 
 
 def test_argument_errors():
