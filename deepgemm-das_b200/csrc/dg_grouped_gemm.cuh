@@ -107,7 +107,7 @@ struct KernelParams {
   const float* row_weight;
   const void* gather_a;  // the [size_m][K] activation the rows are gathered from
   int block_m, num_blocks, num_sorted, real_topk, size_m;
-  int tbl_groups;  // entries per array of the schedule table: G, or (MODE_SORTED) the most runs it holds
+  int tbl_groups;  // MODE_SORTED: entries per array of the schedule table (the most runs it holds)
   int narrow;  // masked / compact: 0 = tiles stay BN columns wide, 1 = the kernel may narrow them
                // (down to 32 columns) when few groups have rows, 128 / 64 / 32 = forced width
 };
@@ -464,8 +464,9 @@ struct ItemDecoder {
       sub = (j & 1) * t.width;
     }
     if (p.mode != MODE_CONTIG) {
+      const int tg = p.mode == MODE_SORTED ? p.tbl_groups : p.G;  // entries per array of the table
       const int32_t* cnt = tbl;
-      const int32_t* pref = tbl + p.tbl_groups;
+      const int32_t* pref = tbl + tg;
       const int blk = item / n_tiles;
       while (blk >= pref[cursor + 1]) ++cursor;  // items only grow, so the cursor persists
       const int mt = blk - pref[cursor];
@@ -477,8 +478,8 @@ struct ItemDecoder {
         t.row0 += tbl[2 * p.G + 1 + cursor];
         t.rows_valid = min(t.rows_valid, p.M - t.row0);
       } else if (p.mode == MODE_SORTED) {  // the cursor counts runs: expert (-1: zeros) and first list entry
-        t.g = tbl[2 * p.tbl_groups + 1 + cursor];
-        t.row0 += tbl[3 * p.tbl_groups + 1 + cursor];
+        t.g = tbl[2 * tg + 1 + cursor];
+        t.row0 += tbl[3 * tg + 1 + cursor];
       }
     } else {
       const int bi = item / n_tiles;
