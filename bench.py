@@ -572,6 +572,70 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
     return res
 
 
+def _sorted_routing(topk_ids, experts, block_m):
+    """A routing list as vLLM's moe_align_block_size produces it (torch ops, plumbing): pairs
+    sorted by expert, every expert's run padded to a multiple of block_m with an id no row has;
+    entry = slot << 24 | token.  Returns (sorted_token_ids, expert_ids, num_tokens_post_pad)."""
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    flat = topk_ids.flatten().long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=experts)
+    padded = (counts + block_m - 1) // block_m * block_m
+    starts = torch.cumsum(padded, 0) - padded
+    total = int(padded.sum())
+    ids = torch.full((total,), (k << 24), dtype=torch.int64, device=dev)       # slot = top_k: padding
+    rank_in_expert = torch.arange(flat.numel(), device=dev) - (torch.cumsum(counts, 0) - counts)[flat[order]]
+    ids[starts[flat[order]] + rank_in_expert] = ((order % k) << 24) | (order // k)
+    expert_ids = torch.repeat_interleave(torch.arange(experts, device=dev), padded // block_m)
+    return ids.to(torch.int32), expert_ids.to(torch.int32), torch.tensor([total], dtype=torch.int32, device=dev)
+
+
+def make_prefill_down(device, small=False, path=None):
+    """Second-stage op on a routing list (moe_w8a8_marlin_prefill_down_fp8): FP8, N=7168, K=2048,
+    4096 tokens top-8 over 256 experts (small: 512 tokens, 32 experts), blocks of 32 entries.
+    `path` pins the implementation ("gather": the one-launch GEMM that fetches the rows by index;
+    "regroup": regroup step + contiguous GEMM); None lets the op choose."""
+    import deepgemm
+    from deepgemm import moe_marlin_prefill as M
+    t, e = (512, 32) if small else (4096, 256)
+    k, n, hid, block_m = 8, 7168, 2048, 32
+    gen = torch.Generator(device=device).manual_seed(12)
+    topk_ids = torch.rand(t, e, device=device, generator=gen).topk(k, dim=1).indices
+    inp = (torch.randn(t * k, hid, device=device, generator=gen) * 0.5).to(torch.float8_e4m3fn)
+    w = deepgemm.marlin_fp8_contiguous_weight(
+        (torch.randn(e, n, hid, device=device, generator=gen) * 0.05).to(torch.float8_e4m3fn))
+    a_s = torch.rand(t * k, device=device, generator=gen) * 0.02 + 0.01
+    b_s = torch.rand(e, n, device=device, generator=gen) * 0.02 + 0.01
+    tw = torch.softmax(torch.randn(t, k, device=device, generator=gen), dim=1)
+    ids, experts, used = _sorted_routing(topk_ids, e, block_m)
+    out = torch.zeros(t * k, n, dtype=torch.bfloat16, device=device)
+
+    def fn():
+        M.FORCE_PATH = path
+        try:
+            deepgemm.moe_w8a8_marlin_prefill_down_fp8(inp, w, out, a_s, b_s, tw, ids, experts, used, k, k)
+        finally:
+            M.FORCE_PATH = None
+    info = {"workload": "prefill_down_fp8 tokens=%d top%d experts=%d N=%d K=%d" % (t, k, e, n, hid),
+            "ops": 2.0 * t * k * n * hid, "bytes": algorithmic_bytes(t * k, e, e, n, hid, 1, 1)}
+    return fn, info
+
+
+def bench_prefill_down(device, steps, warmup):
+    res = None
+    for path in ("gather", "regroup"):
+        fn, info = make_prefill_down(device, path=path)
+        ms, _, _ = time_launches(fn, steps, warmup)
+        if res is None:
+            res = {"workload": info["workload"]}
+        res["ms_" + ("one_launch_gathering_gemm" if path == "gather" else "regroup_then_gemm")] = ms / steps
+        del fn
+        torch.cuda.empty_cache()
+    res["tflops_one_launch"] = info["ops"] / (res["ms_one_launch_gathering_gemm"] * 1e-3) / 1e12
+    return res
+
+
 def bench_host_path(device, cfg, calls=4000):
     """Host time per call of the public Python entry point (decode shape, no routed rows, so the
     kernel is an empty launch and the host is what is timed), with no CUDA graph: wall clock over
@@ -661,7 +725,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="profiler run: one workload's timed region only, bracketed by cudaProfilerStart/Stop")
     ap.add_argument("--workload", default="decode",
-                    choices=["decode", "prefill_int8", "prefill_fp8", "w4a8", "w4a8_smem", "chain"],
+                    choices=["decode", "prefill_int8", "prefill_fp8", "w4a8", "w4a8_smem", "chain", "prefill_down"],
                     help="with --profile: which configuration to run (the JSON line is always decode)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -711,6 +775,8 @@ def main():
     if args.profile and args.workload != "decode":
         if args.workload in ("w4a8", "w4a8_smem"):
             fn, info = make_masked_w4a8(device, args.small, smem_unpack=args.workload == "w4a8_smem")
+        elif args.workload == "prefill_down":
+            fn, info = make_prefill_down(device, args.small, path="gather")
         else:
             fn, info = make_contig_prefill(device, args.small, "int8" if args.workload == "prefill_int8" else "fp8")
         for _ in range(warmup):
@@ -902,6 +968,7 @@ def main():
                 extras["contiguous_fp8_prefill"] = bench_contig_prefill(device, 20, 3, peaks, "fp8")
                 extras["masked_w4a8"] = bench_masked_w4a8(device, 200, 10, peaks)
                 extras["host_path"] = bench_host_path(device, cfg)
+                extras["prefill_down_routing_list"] = bench_prefill_down(device, 20, 3)
             del w
             torch.cuda.empty_cache()
             extras["ep_prefill"] = bench_ep_prefill(device, rank, world, 10, 3, peaks)
