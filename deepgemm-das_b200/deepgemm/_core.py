@@ -147,8 +147,9 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 _status_words = {}
 _STATUS_TEXT = {1: "a bounded wait inside a kernel ran out (thread block {1}, wait site {2}, {3} work items): "
                    "the launch left part of its output unwritten",
-                2: "an expert index was outside [0, num_groups) (m_indices entry or routed pair): "
-                   "the rows it names were skipped"}
+                2: "an expert index was outside [0, num_groups) (m_indices entry, routed pair or block of a "
+                   "routing list): the rows it names were skipped; or a routing list had more runs of "
+                   "blocks than 2 * experts + 2 and nothing was computed"}
 
 
 def device_status_words(device: torch.device) -> torch.Tensor:

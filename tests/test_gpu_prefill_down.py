@@ -42,7 +42,7 @@ def _case(kind, t, k, e, hid, n, block_m, seed, local=None, extra_blocks=0):
                 used=used, k=k)
 
 
-def _run(c, kind, sentinel=3.0):
+def _call(c, kind, sentinel=3.0):
     pack = deepgemm.marlin_fp8_contiguous_weight if kind == "fp8" else deepgemm.marlin_i8_contiguous_weight
     size_m, n = c["inp"].shape[0], c["w"].shape[1]
     out = torch.full((size_m, n), sentinel, dtype=torch.bfloat16, device=DEV)
@@ -50,6 +50,12 @@ def _run(c, kind, sentinel=3.0):
         c["inp"].to(DEV), pack(c["w"].clone().to(DEV)), out, c["a_scale"].to(DEV), c["b_scale"].to(DEV),
         c["topk_w"].to(DEV), c["ids"].to(DEV), c["experts"].to(DEV), c["used"].to(DEV), c["k"], c["k"])
     assert r is out
+    return out
+
+
+def _run(c, kind, sentinel=3.0):
+    out = _call(c, kind, sentinel)
+    size_m, n = c["inp"].shape[0], c["w"].shape[1]
     want = O.ref_prefill_down(c["inp"], c["w"], c["a_scale"], c["b_scale"], c["topk_w"], c["ids"],
                               c["experts"], c["used"], c["k"],
                               torch.full((size_m, n), sentinel, dtype=torch.bfloat16))
@@ -106,6 +112,69 @@ def test_gathering_gemm_is_one_launch_and_matches_the_regroup_path_bit_for_bit(_
         M.FORCE_PATH = "gather"
         assert torch.equal(out_g.view(torch.int16), out_r.view(torch.int16)), kind
     deepgemm.check_device_status()
+
+
+@pytest.mark.parametrize("block_m", [16, 64, 128])
+def test_other_block_sizes(block_m):
+    c = _case("int8", 150, 4, 5, 256, 512, block_m, seed=block_m, extra_blocks=1)
+    out, want = _run(c, "int8")
+    assert_bf16_within_ulp(out, want, 1, f"prefill-down block_m={block_m}")
+
+
+def test_a_list_that_is_not_sorted_by_expert(_path):
+    """Blocks of one expert need not be neighbours: every run of blocks is tiled on its own.  The
+    gathering GEMM holds 2 * experts + 2 runs; beyond that it computes nothing and says so."""
+    c = _case("int8", 200, 4, 4, 256, 512, 16, seed=31)
+    blocks = c["experts"].numel()
+    used_blocks = int(c["used"]) // 16
+    g = torch.Generator().manual_seed(3)
+    perm = torch.cat([torch.randperm(used_blocks, generator=g), torch.arange(used_blocks, blocks)])
+    ids = c["ids"].view(blocks, 16)[perm].reshape(-1).contiguous()
+    experts = c["experts"][perm].contiguous()
+    runs = 1 + int((experts[1:used_blocks] != experts[:used_blocks - 1]).sum())
+    c2 = dict(c, ids=ids, experts=experts)
+    if _path == "gather" and runs > 2 * 4 + 2:
+        out, _ = _run(c2, "int8", sentinel=5.0)
+        assert bool((out.float() == 5.0).all()), "a refused list must leave the output alone"
+        with pytest.raises(RuntimeError, match="expert index"):
+            deepgemm.check_device_status()
+        # a few runs more than experts are fine: swap two neighbouring blocks of different experts
+        b = int(torch.nonzero(c["experts"][1:used_blocks] != c["experts"][:used_blocks - 1])[0]) + 1
+        perm2 = torch.arange(blocks)
+        perm2[b - 1], perm2[b] = b, b - 1
+        c3 = dict(c, ids=c["ids"].view(blocks, 16)[perm2].reshape(-1).contiguous(),
+                  experts=c["experts"][perm2].contiguous())
+        out, want = _run(c3, "int8")
+        assert_bf16_within_ulp(out, want, 1, "two blocks swapped")
+    else:
+        out, want = _run(c2, "int8")
+        assert_bf16_within_ulp(out, want, 1, "unsorted list")
+    deepgemm.check_device_status()
+
+
+def test_empty_list_and_unknown_experts(_path):
+    c = _case("int8", 40, 2, 3, 128, 256, 32, seed=8)
+    out, _ = _run(dict(c, used=torch.zeros(1, dtype=torch.int32)), "int8", sentinel=5.0)
+    assert bool((out.float() == 5.0).all()), "a list with no entries in use writes nothing"
+    deepgemm.check_device_status()
+    bad = c["experts"].clone()
+    bad[0] = 7                                                  # only experts 0..2 exist
+    out = _call(dict(c, experts=bad), "int8", sentinel=5.0).cpu()
+    if _path == "gather":
+        with pytest.raises(RuntimeError, match="expert index"):
+            deepgemm.check_device_status()
+    else:
+        try:
+            deepgemm.check_device_status()
+        except RuntimeError:
+            pass
+    rows = ((c["ids"][:32].long() & 0xFFFFFF) * 2 + (c["ids"][:32].long() >> 24))[(c["ids"][:32].long() >> 24) < 2]
+    assert bool((out[rows].float() == 5.0).all()), "rows of a block with an unknown expert are skipped"
+    others = torch.ones(out.shape[0], dtype=torch.bool)
+    others[rows] = False
+    c_ok = dict(c)
+    out_ok, want_ok = _run(c_ok, "int8", sentinel=5.0)
+    assert torch.equal(out[others].view(torch.int16), out_ok[others].view(torch.int16))
 
 
 def test_argument_errors():
