@@ -62,6 +62,15 @@ def test_calls_validate_before_touching_the_device():
     assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -8
     a = _cabi.MaskedArgs(kind=_cabi.KIND_I8, scale_mode=0, num_groups=1, max_m=4, n=64, k=128)
     assert _cabi.lib.dg_masked_gemm(ctypes.byref(a), None) == -1      # null pointers
+    assert _cabi.lib.dg_sorted_gemm(None, None) == -1
+    g = _cabi.SortedGemmArgs(kind=_cabi.KIND_BF16)
+    assert _cabi.lib.dg_sorted_gemm(ctypes.byref(g), None) == -2      # INT8 / FP8 only
+    g = _cabi.SortedGemmArgs(kind=_cabi.KIND_I8, num_groups=2, num_sorted=64, num_blocks=1, block_m=32,
+                             size_m=8, real_topk=2, n=64, k=128)
+    assert _cabi.lib.dg_sorted_gemm(ctypes.byref(g), None) == -9      # blocks do not cover the list
+    g = _cabi.SortedGemmArgs(kind=_cabi.KIND_I8, num_groups=2, num_sorted=64, num_blocks=2, block_m=32,
+                             size_m=8, real_topk=2, n=64, k=128)
+    assert _cabi.lib.dg_sorted_gemm(ctypes.byref(g), None) == -1      # null pointers
     c = _cabi.ContigArgs(kind=_cabi.KIND_E4M3, scale_mode=0, num_groups=1, m_total=1 << 22, n=64, k=128)
     assert _cabi.lib.dg_contig_gemm(ctypes.byref(c), None) == -8
     c = _cabi.ContigArgs(kind=_cabi.KIND_E4M3, scale_mode=0, num_groups=1, m_total=128, n=64, k=128,
