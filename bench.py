@@ -636,6 +636,27 @@ def bench_prefill_down(device, steps, warmup):
     return res
 
 
+def bench_masked_bf16(device, steps, warmup, peaks, active_m=112):
+    """Masked BF16 at the shape the reference benchmarks (16 experts, M = 2048, N = 2048, K = 6144,
+    op_test/test_deepgemm_masked_w16a16_bf16.py:11-20) with `active_m` rows in every expert: weight
+    streaming, so the figure is GB/s of the reference's own byte count against the copy rate."""
+    import deepgemm
+    E, M, N, K = 16, 2048, 2048, 6144
+    gen = torch.Generator(device=device).manual_seed(5)
+    a = (torch.randn(E, M, K, device=device, generator=gen) * 0.1).bfloat16()
+    packed, cfg = deepgemm.pack_bf16_masked_weight((torch.randn(E, N, K, device=device, generator=gen) * 0.1).bfloat16())
+    mm = torch.full((E,), active_m, dtype=torch.int32, device=device)
+    d = torch.zeros(E, M, N, dtype=torch.bfloat16, device=device)
+    ms, _, _ = time_launches(lambda: deepgemm.m_grouped_bf16_gemm_nt_masked(a, packed, d, mm, active_m, cfg),
+                             steps, warmup)
+    nbytes = E * (active_m * K + N * K + active_m * N) * 2
+    gbs = nbytes / (ms * 1e-3 / steps) / 1e9
+    return {"workload": "masked_bf16 E=16 max_m=2048 N=2048 K=6144 masked_m=%d" % active_m, "ms": ms / steps,
+            "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+            "tflops": 2.0 * E * active_m * N * K / (ms * 1e-3 / steps) / 1e12,
+            "l2": "0.4 GB of weights, larger than the 126 MB L2"}
+
+
 def bench_host_path(device, cfg, calls=4000):
     """Host time per call of the public Python entry point (decode shape, no routed rows, so the
     kernel is an empty launch and the host is what is timed), with no CUDA graph: wall clock over
@@ -967,6 +988,7 @@ def main():
                 extras["contiguous_int8_prefill"] = bench_contig_prefill(device, 20, 3, peaks, "int8")
                 extras["contiguous_fp8_prefill"] = bench_contig_prefill(device, 20, 3, peaks, "fp8")
                 extras["masked_w4a8"] = bench_masked_w4a8(device, 200, 10, peaks)
+                extras["masked_bf16"] = bench_masked_bf16(device, 100, 10, peaks)
                 extras["host_path"] = bench_host_path(device, cfg)
                 extras["prefill_down_routing_list"] = bench_prefill_down(device, 20, 3)
             del w
