@@ -9,7 +9,8 @@ This module is the device-side form: every rank maps one buffer of every other r
 grouped, padded activation buffer; the second GEMM's epilogue writes every result row straight
 back into the buffer of the rank the token came from (``scatter_tag`` of ``dg_contig_gemm``), so
 the return transfer overlaps the GEMM tile by tile and the final weighted sum is a local read.
-A layer is eight launches on one stream and never synchronises with the host:
+A layer is eight launches on one stream (the two barriers included) and never synchronises with
+the host:
 
     plan (counts exchange) -> push (quantising each token on the way out) -> barrier ->
     gate/up GEMM -> SiLU*up + requantise -> down GEMM (scattering) -> barrier -> weighted top-k sum
