@@ -101,8 +101,11 @@ def test_gathering_gemm_is_one_launch_and_matches_the_regroup_path_bit_for_bit(_
     from deepgemm import _cabi, moe_marlin_prefill as M
     if _path != "gather":
         pytest.skip("compares the two paths once")
-    for kind, n in (("int8", 512), ("fp8", 384)):
-        c = _case(kind, 300, 4, 7, 448, n, 16, seed=77, local={0, 2, 3, 5, 6}, extra_blocks=3)
+    # the last case is large enough for the two-CTA tiles (1024 routed rows per expert, 160 units)
+    for kind, n, shape in (("int8", 512, (300, 4, 7, 448, 16)), ("fp8", 384, (300, 4, 7, 448, 16)),
+                           ("int8", 1280, (2048, 4, 8, 192, 32))):
+        t_, k_, e_, hid_, bm_ = shape
+        c = _case(kind, t_, k_, e_, hid_, n, bm_, seed=77, local=set(range(e_)) - {1, 4}, extra_blocks=3)
         before = _cabi.query(_cabi.QUERY_LAUNCH_COUNT)
         out_g, _ = _run(c, kind)
         # the weight packer launches once per expert; the op itself is one launch
