@@ -367,11 +367,10 @@ int launch(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
 }
 
 // Two-CTA (cta_group::2) 256x256 tiles for compute-bound shapes; one cluster per TPC.
-template <int KIND, bool kGather = false>
+template <int KIND>
 int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   using L = PairSmem;
-  static_assert(kGatherDepth < kPairStages, "the gathering warps would wait for stages they have not signalled");
-  auto kernel = grouped_gemm_pair_kernel<KIND, kGather>;
+  auto kernel = grouped_gemm_pair_kernel<KIND>;
   const int esize = (KIND == DG_KIND_BF16) ? 2 : 1;
   const int elems_per_row = kRowBytes / esize;
   KernelParams p{};
@@ -395,29 +394,14 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   p.group_window = pr.group_window;
   p.scatter_tag = pr.scatter_tag;
   for (int r = 0; r < pr.scatter_world && pr.scatter_tag != nullptr; ++r) p.scatter_base[r] = pr.scatter_base[r];
-  p.tbl_groups = pr.max_runs;
-  p.sorted_ids = pr.sorted_ids;
-  p.expert_ids = pr.expert_ids;
-  p.num_post_pad = pr.num_post_pad;
-  p.row_weight = pr.row_weight;
-  p.gather_a = pr.a;
-  p.block_m = pr.block_m;
-  p.num_blocks = pr.num_blocks;
-  p.num_sorted = pr.num_sorted;
-  p.real_topk = pr.real_topk;
-  p.size_m = pr.M;
 
   const long long max_items =
-      (pr.mode == MODE_MASKED   ? (long long)pr.G * p.m_blocks
-       : pr.mode == MODE_SORTED ? (long long)(pr.num_sorted + 255) / 256 + pr.max_runs
-                                : 2LL * p.m_blocks) * p.n_tiles;
+      (pr.mode == MODE_MASKED ? (long long)pr.G * p.m_blocks : 2LL * p.m_blocks) * p.n_tiles;
   if (max_items <= 0) return DG_OK;
-  const int table_bytes = pr.mode == MODE_MASKED   ? (2 * pr.G + 1) * 4
-                          : pr.mode == MODE_SORTED ? (4 * pr.max_runs + 2) * 4
-                                                   : 2 * p.m_blocks * 4;
+  const int table_bytes = (pr.mode == MODE_MASKED) ? (2 * pr.G + 1) * 4 : 2 * p.m_blocks * 4;
   int smem_bytes = L::total(table_bytes);
   if (smem_bytes > dev.max_smem || smem_bytes > kMaxSmem) return DG_ERR_TOO_LARGE;
-  if (pr.scatter_tag != nullptr || pr.mode == MODE_SORTED || kWideStripsAlways) {
+  if (pr.scatter_tag != nullptr || kWideStripsAlways) {
     const int off = (L::off_table + table_bytes + 15) & ~15;
     if (off + 4 * 4096 + 1024 <= dev.max_smem && off + 4 * 4096 + 1024 <= kMaxSmem) {
       p.wide_off = off;
@@ -456,7 +440,7 @@ int launch_pair(const Problem& pr, const DeviceInfo& dev, cudaStream_t stream) {
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cudaLaunchConfig_t cfg{};
-  cfg.blockDim = dim3(L::kThreads + (kGather ? kGatherThreads : 0), 1, 1);
+  cfg.blockDim = dim3(L::kThreads, 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = stream;
   cfg.attrs = attr;
@@ -721,14 +705,8 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
     const long long pair_items = (rows / 256) * (pr.N / 256);
     if (pr.mode == MODE_COMPACT)
       bn = (pr.N >= 256 && (rows / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
-    else if (pr.mode == MODE_SORTED) {
-      // as for the contiguous layout: two-CTA tiles from about 320 routed rows per expert upwards
-      const long long listed = pr.num_sorted;
-      if (listed / pr.G >= 320 && pr.N >= 256 && (listed / 256) * (pr.N / 256) >= 2LL * (dev->sm_count / 2))
-        bn = 512;
-      else
-        bn = (pr.N >= 256 && (listed / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
-    }
+    else if (pr.mode == MODE_SORTED)  // the gathering producer lives in the one-CTA kernel
+      bn = (pr.N >= 256 && ((long long)pr.num_sorted / 128) * (pr.N / 256) >= dev->sm_count) ? 256 : 128;
     else if (big_groups && pr.N >= 256 && pair_items >= 2LL * (dev->sm_count / 2))
       bn = 512;
     else if (pr.mode == MODE_CONTIG)
@@ -744,6 +722,7 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
     }
   }
   if (bn == 512 && (pr.N < 256 || pr.mode == MODE_COMPACT)) bn = 128;
+  if (bn == 512 && pr.mode == MODE_SORTED) bn = 256;
   if (bn == 512 && pr.signal != nullptr) bn = 256;  // completion counters live in the one-CTA kernel
   if (bn == 512 && scalar_out) bn = 256;
   if (pr.kind == DG_KIND_W4A8) {
@@ -760,9 +739,6 @@ int validate_and_launch(Problem& pr, cudaStream_t stream) {
     }
   }
   if (pr.mode == MODE_SORTED) {
-    if (bn == 512)
-      return pr.kind == DG_KIND_I8 ? launch_pair<DG_KIND_I8, true>(pr, *dev, stream)
-                                   : launch_pair<DG_KIND_E4M3, true>(pr, *dev, stream);
     if (pr.kind == DG_KIND_I8)
       return bn == 256 ? launch<DG_KIND_I8, 256, true>(pr, *dev, stream) : launch<DG_KIND_I8, 128, true>(pr, *dev, stream);
     return bn == 256 ? launch<DG_KIND_E4M3, 256, true>(pr, *dev, stream)

@@ -77,20 +77,6 @@ struct PairDecoder {
       t.n0 = (local - sb * p.n_tiles) * kPairBN;
       t.rows_valid = min(256, cnt[cursor] - t.row0);
       t.half_mask = 3;
-    } else if (p.mode == MODE_SORTED) {
-      // as masked, with the runs of the routing list in the place of the groups: cnt / pref, then
-      // each run's expert (-1: zeros) and first list entry
-      const int tg = p.tbl_groups;
-      const int32_t* cnt = tbl;
-      const int32_t* pref = tbl + tg;
-      while (item >= pref[cursor + 1]) ++cursor;
-      const int local = item - pref[cursor];
-      const int sb = local / p.n_tiles;
-      t.g = tbl[2 * tg + 1 + cursor];
-      t.row0 = tbl[3 * tg + 1 + cursor] + sb * 256;
-      t.n0 = (local - sb * p.n_tiles) * kPairBN;
-      t.rows_valid = min(256, cnt[cursor] - sb * 256);
-      t.half_mask = 3;
     } else {
       const int ui = item / p.n_tiles;
       const int e = tbl[ui];
@@ -104,10 +90,8 @@ struct PairDecoder {
   }
 };
 
-// kGather: the instantiation behind MODE_SORTED, with four more warps per block that fetch the
-// rows of the block's half of a super block by index (see grouped_gemm_kernel).
-template <int KIND, bool kGather = false>
-__global__ void __launch_bounds__(PairSmem::kThreads + (kGather ? kGatherThreads : 0), 1)
+template <int KIND>
+__global__ void __launch_bounds__(PairSmem::kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                          const __grid_constant__ CUtensorMap tm_b, const KernelParams p) {
   using L = PairSmem;
@@ -143,7 +127,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   volatile int* n_items_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 8);
   const uint32_t stages_addr = base + L::off_misc + 12;  // stages whose full barrier was seen complete (leader)
   const uint32_t items_addr = base + L::off_misc + 16;   // work items whose accumulator is free (leader)
-  volatile int* post_pad_s = reinterpret_cast<volatile int*>(smem + L::off_misc + 20);  // MODE_SORTED
   int32_t* tbl = reinterpret_cast<int32_t*>(smem + L::off_table);
 
   if (tid == 0) {
@@ -151,8 +134,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     *reinterpret_cast<volatile uint32_t*>(smem + L::off_misc + 12) = 0;
     *reinterpret_cast<volatile uint32_t*>(smem + L::off_misc + 16) = 0;
     for (int s = 0; s < STAGES; ++s) {
-      // leader's producer (+ the four gathering warps of each block); the peer's copy stays unused
-      mbar_init(bar_full(s), kGather ? 9 : 1);
+      mbar_init(bar_full(s), 1);   // leader's producer (the peer's barrier stays unused)
       mbar_init(bar_empty(s), 1);  // one commit from the leader's UMMA thread
     }
     for (int b = 0; b < 2; ++b) {
@@ -166,61 +148,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
 
   // Schedule table (identical in both blocks of a pair).
-  if (p.mode == MODE_SORTED) {
-    // runs of list blocks with one expert, tiled into 256-entry super blocks (see grouped_gemm_kernel)
-    const int RM = p.tbl_groups;
-    int32_t* cnt = tbl;
-    int32_t* pref = tbl + RM;
-    int32_t* run_e = tbl + 2 * RM + 1;
-    int32_t* run_p0 = tbl + 3 * RM + 1;
-    if (warp == 0) {
-      const int post = max(0, min(*p.num_post_pad, p.num_sorted));
-      const int nb = min(p.num_blocks, (post + p.block_m - 1) / p.block_m);
-      int runs = 0;
-      bool bad = false;
-      for (int b0 = 0; b0 < nb; b0 += 32) {
-        const int b = b0 + lane;
-        const int e = (b < nb) ? p.expert_ids[b] : 0;
-        const bool start = b < nb && (b == 0 || p.expert_ids[b - 1] != e);
-        const unsigned mask = __ballot_sync(0xffffffffu, start);
-        const int r = runs + __popc(mask & ((1u << lane) - 1u));
-        if (start && r < RM) {
-          run_e[r] = e >= p.G ? -2 : (e < 0 ? -1 : e);
-          run_p0[r] = b * p.block_m;
-          bad |= e >= p.G;
-        }
-        runs += __popc(mask);
-      }
-      __syncwarp();
-      const bool overflow = runs > RM;
-      if (overflow) runs = 0;
-      int running = 0;
-      for (int r0 = 0; r0 < runs; r0 += 32) {
-        const int r = r0 + lane;
-        int x = 0;
-        if (r < runs) {
-          const int end = (r + 1 < runs) ? run_p0[r + 1] : nb * p.block_m;
-          const int rows = run_e[r] == -2 ? 0 : end - run_p0[r];
-          cnt[r] = rows;
-          x = ((rows + 255) / 256) * p.n_tiles;
-        }
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int y = __shfl_up_sync(0xffffffffu, x, o);
-          if (lane >= o) x += y;
-        }
-        if (r < runs) pref[r + 1] = running + x;
-        running += __shfl_sync(0xffffffffu, x, 31);
-      }
-      if (lane == 0) {
-        pref[0] = 0;
-        *n_items_s = running;
-        *post_pad_s = post;
-      }
-      if ((__any_sync(0xffffffffu, bad) || overflow) && lane == 0 && blockIdx.x == 0 && p.status != nullptr)
-        atomicCAS(p.status, DG_DEV_OK, DG_DEV_BAD_GROUP_INDEX);
-    }
-  } else if (p.mode == MODE_MASKED) {
+  if (p.mode == MODE_MASKED) {
     int32_t* cnt = tbl;
     int32_t* pref = tbl + p.G;
     for (int g = tid; g < p.G; g += blockDim.x) cnt[g] = p.sched ? max(0, min(p.sched[g], p.M)) : p.M;
@@ -299,91 +227,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t tmem_base = *tmem_slot;
   const int n_items = *n_items_s;
 
-  if (kGather && warp >= 7) {
-    if constexpr (kGather) {
-      // ---- gathering warps (both blocks): this block's half of the super block, 16 bytes per
-      // thread and copy as in grouped_gemm_kernel; the stage barrier they signal is the leader's
-      const int g = tid - L::kThreads;
-      const int piece = g & 7, rsub = g >> 3;
-      const int post = *post_pad_s;
-      const uint8_t* a_bytes = static_cast<const uint8_t*>(p.gather_a);
-      const size_t row_bytes = static_cast<size_t>(p.K) * (KIND == DG_KIND_BF16 ? 2 : 1);
-      PairDecoder dec(p, tbl);
-      uint32_t it = 0;
-      bool ok = true;
-      auto signal_done = [&](uint32_t j) {
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_remote(mapa_shared(bar_full(j % STAGES), 0));
-      };
-      for (int item = pair; ok && item < n_items; item += num_pairs) {
-        const PairTile t = dec.get(item);
-        if (t.g < 0) continue;
-        int src[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int r = static_cast<int>(rank) * 128 + rsub + 16 * i;
-          src[i] = r < t.rows_valid ? sorted_row(p, t.row0 + r, post) : -1;
-        }
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait_warp(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) {
-            ok = false;
-            break;
-          }
-          const size_t col = static_cast<size_t>(kb) * kRowBytes + piece * 16;
-          const uint32_t in_row = col < row_bytes ? 16u : 0u;
-          const uint32_t a_dst = base + L::off_a + s * kATileBytes;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = rsub + 16 * i;
-            if (src[i] >= 0)
-              cp_async_16(a_dst + r * kRowBytes + ((piece ^ (r & 7)) << 4),
-                          a_bytes + static_cast<size_t>(src[i]) * row_bytes + (in_row ? col : 0), in_row);
-          }
-          cp_async_commit();
-          if (it >= kGatherDepth) {
-            cp_async_wait_group<kGatherDepth>();
-            signal_done(it - kGatherDepth);
-          }
-        }
-      }
-      cp_async_wait_group<0>();
-      if (ok)
-        for (uint32_t j = it > kGatherDepth ? it - kGatherDepth : 0; j < it; ++j) signal_done(j);
-    }
-  } else if (warp == 0 && p.mode == MODE_SORTED) {
-    if (lane == 0) {
-      // ---- weight producer of MODE_SORTED (both blocks): this block's half of the weight tile
-      const uint64_t pol_b = l2_policy_evict_last();
-      PairDecoder dec(p, tbl);
-      uint32_t it = 0;
-      bool ok = true;
-      for (int item = pair; ok && item < n_items; item += num_pairs) {
-        const PairTile t = dec.get(item);
-        if (t.g < 0) continue;
-        const int b_n0 = t.n0 + static_cast<int>(rank) * 128;
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, SITE_PRODUCER_EMPTY)) {
-            ok = false;
-            break;
-          }
-          if (rank == 0) mbar_arrive_expect_tx(bar_full(s), 2u * L::kBHalfBytes);
-          int bx, by;
-          weight_coords(p, t.g, b_n0, kb, kElemsPerRow, bx, by);
-          tma_load_2d_pair(base + L::off_b + s * L::kBHalfBytes, &tm_b, mapa_shared(bar_full(s), 0), bx, by, pol_b);
-        }
-      }
-      if (*abort_flag) {
-        const uint64_t t0 = global_timer_ns();
-        while (global_timer_ns() - t0 < 200000ull) {
-        }
-      }
-    }
-  } else if (warp == 0) {
+  if (warp == 0) {
     if (lane == 0) {
       // ---- TMA producer (both blocks)
       const uint64_t pol_a = l2_policy_evict_last();
@@ -456,7 +300,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       };
       uint32_t it = 0, tile = 0, stages_known = 0, items_known = 0;
       bool ok = true;
-      PairDecoder zdec(p, tbl);  // MODE_SORTED: units of an absent expert have no products
       for (int item = pair; ok && item < n_items; item += num_pairs, ++tile) {
         const uint32_t buf = tile & 1u;
         if (items_known <= tile && (items_known = poll_above(items_addr, tile, SITE_MMA_ACC_EMPTY)) == 0) {
@@ -465,8 +308,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kPairBN;
-        const int k_end = (kGather && zdec.get(item).g < 0) ? 0 : p.kblocks;
-        for (int kb = 0; kb < k_end; ++kb, ++it) {
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           if (stages_known <= it) {
             if ((stages_known = poll_above(stages_addr, it, SITE_MMA_FULL)) == 0) {
@@ -496,14 +338,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       // ---- barrier watcher (leader only): waits in the UMMA thread's place
       uint32_t it = 0, tile = 0;
       bool ok = true;
-      PairDecoder zdec(p, tbl);
       for (int item = pair; ok && item < n_items; item += num_pairs, ++tile) {
         if (!mbar_wait_bounded(bar_acc_empty(tile & 1u), ((tile >> 1) & 1u) ^ 1u, abort_flag,
                                SITE_MMA_ACC_EMPTY))
           break;
         asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(items_addr), "r"(tile + 1u) : "memory");
-        const int k_end = (kGather && zdec.get(item).g < 0) ? 0 : p.kblocks;
-        for (int kb = 0; kb < k_end; ++kb) {
+        for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_bounded(bar_full(it % STAGES), (it / STAGES) & 1u, abort_flag, SITE_MMA_FULL)) {
             ok = false;
             break;
@@ -535,17 +375,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       EpiRow row;
       row.as = 1.0f;
       row.bs_g = 1.0f;
-      const bool sorted = kGather && p.mode == MODE_SORTED;
-      if (warp_has_rows && sorted) {
-        if (t.g >= 0)
-          stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, kPairBN, p.N, lane,
-                            p.scale_mode == DG_SCALE_PER_CHANNEL);
-        const int srow = row_in_half < half_rows
-                             ? sorted_row(p, t.row0 + static_cast<int>(rank) * 128 + row_in_half, *post_pad_s) : -1;
-        rv = srow >= 0;
-        grow = rv ? static_cast<size_t>(srow) : 0;
-        if (rv) row.as = p.row_weight ? __fmul_rn(p.row_weight[grow], p.a_scale[grow]) : p.a_scale[grow];
-      } else if (warp_has_rows) {
+      if (warp_has_rows) {
         stage_tile_scales(bs_s, p.b_scale + (size_t)t.g * p.N, t.n0, kPairBN, p.N, lane,
                           p.scale_mode == DG_SCALE_PER_CHANNEL);
         rv = row_in_half < half_rows;
@@ -556,26 +386,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       if (!mbar_wait_warp(bar_acc_full(buf), aph, abort_flag, SITE_EPI_ACC_FULL)) break;
       tc_fence_after_sync();
-      if (warp_has_rows && sorted && t.g < 0) {
-        // rows of an expert that lives elsewhere: zeros
-        const unsigned rows_mask = __ballot_sync(0xffffffffu, rv);
-        const int cols = min(kPairBN, p.N - t.n0);
-        for (int r = 0; r < 32; ++r) {
-          if (!((rows_mask >> r) & 1u)) continue;
-          const size_t zr = __shfl_sync(0xffffffffu, grow, r);
-          __nv_bfloat16* dst = p.d + zr * p.N + t.n0;
-          const int c = lane * 8;
-          if (c + 8 <= cols)
-            *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
-          else
-            for (int i = c; i < cols; ++i) dst[i] = __float2bfloat16_rn(0.0f);
-        }
-      } else if (warp_has_rows) {
+      if (warp_has_rows) {
         row.bs_row = bs_s;
         row.f16 = p.out_kind == 1;
         row.d_row = p.d + grow * p.N + t.n0;
-        const bool scatter = sorted || (p.mode == MODE_CONTIG && p.scatter_tag != nullptr);
-        if (scatter && rv && !sorted) {
+        const bool scatter = p.mode == MODE_CONTIG && p.scatter_tag != nullptr;
+        if (scatter && rv) {
           const int tag = p.scatter_tag[grow];
           row.d_row = static_cast<__nv_bfloat16*>(p.scatter_base[(tag >> 24) & 15]) +
                       (size_t)(tag & 0xFFFFFF) * p.N + t.n0;

@@ -12,11 +12,10 @@ reference.  Like the reference's kernel, which gathers its 32-row blocks itself,
 gathering: ``dg_sorted_gemm`` tiles every expert's run of the list into 128 entries, its producer
 warp fetches the rows of a tile by index and its epilogue writes each result row to its place
 (and zeros for absent experts): one launch, no allocation, no pass over the operands or the
-result; the library picks one-CTA 128-row tiles or, from about 320 routed rows per expert, two-CTA
-256 x 256 tiles.  The earlier two-step form is kept for comparison (``FORCE_PATH = "regroup"``):
-``dg_group_sorted_rows`` regroups the rows into 128-row blocks per expert in a workspace kept
-per problem size, and the contiguous grouped GEMM scatters the result rows from its epilogue
-(``scatter_tag``).  Both give the same bytes.  ``b_qweight`` must come from
+result.  Large problems with many rows per expert (where two-CTA 256 x 256 tiles pay) take two
+steps instead: ``dg_group_sorted_rows`` regroups the rows into 128-row blocks per expert in a
+workspace kept per problem size, and the contiguous grouped GEMM scatters the result rows from
+its epilogue (``scatter_tag``).  Both give the same bytes.  ``b_qweight`` must come from
 ``marlin_fp8_contiguous_weight`` / ``marlin_i8_contiguous_weight`` of this package.
 """
 from __future__ import annotations
@@ -65,7 +64,7 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
         raise RuntimeError("output, topk_weights and a_scale must have one row per row of input")
     dev = input.device
     kind = _cabi.KIND_E4M3 if input.dtype == torch.float8_e4m3fn else _cabi.KIND_I8
-    path = FORCE_PATH or "gather"
+    path = FORCE_PATH or ("regroup" if _two_cta_tiles_pay(em, experts, size_n) else "gather")
     if path == "gather":
         if not (input.is_contiguous() and output.is_contiguous()):
             raise RuntimeError("input and output must be contiguous")
@@ -103,8 +102,14 @@ def _impl(input, b_qweight, output, a_scale, b_scale, topk_weights, sorted_token
     return output
 
 
-# None: the one-launch GEMM; "regroup": the two-step form kept for comparison (tests pin either)
+# None: choose by size; "gather" / "regroup": tests pin one of the two paths
 FORCE_PATH = None
+
+
+def _two_cta_tiles_pay(em: int, experts: int, size_n: int) -> bool:
+    """The rule of the contiguous GEMM's tile choice: 256 x 256 two-CTA tiles from about 320
+    routed rows per expert upwards, when there are at least two of them for every SM pair."""
+    return em // max(experts, 1) >= 320 and (em // 256) * (size_n // 256) >= 148
 
 
 _WORKSPACES = {}

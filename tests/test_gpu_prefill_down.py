@@ -101,7 +101,8 @@ def test_gathering_gemm_is_one_launch_and_matches_the_regroup_path_bit_for_bit(_
     from deepgemm import _cabi, moe_marlin_prefill as M
     if _path != "gather":
         pytest.skip("compares the two paths once")
-    # the last case is large enough for the two-CTA tiles (1024 routed rows per expert, 160 units)
+    # the last case is large enough for the regroup path's GEMM to take the two-CTA tiles (1024
+    # routed rows per expert, 160 units); two of its experts live elsewhere
     for kind, n, shape in (("int8", 512, (300, 4, 7, 448, 16)), ("fp8", 384, (300, 4, 7, 448, 16)),
                            ("int8", 1280, (2048, 4, 8, 192, 32))):
         t_, k_, e_, hid_, bm_ = shape
