@@ -472,8 +472,9 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
         return e0.elapsed_time(e1) / n
 
     # ---- the whole layer, one timed step (every launch of forward() between the two events)
-    # also with the push in 2 and 4 slices (the later slices cross NVLink under the gate/up GEMM of
-    # the earlier ones); every variant is checked; the layer figure is the unsliced default
+    # with the push in 1, 2 and 4 slices (the later slices cross NVLink under the gate/up GEMM of the
+    # earlier ones); every variant is checked; the layer figure is the one forward() takes by
+    # default (EPExchange.default_slices: 4 from eight ranks upwards, else 1)
     out = torch.empty(T, K, dtype=torch.bfloat16, device=device)
     by_slices, parity = {}, None
     for n_slices in ((1, 2, 4) if world > 1 else (1,)):
@@ -487,7 +488,7 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
     if dist:
         dist.all_reduce(sl, op=dist.ReduceOp.MAX)
     by_slices = {n: float(v) for n, v in zip((1, 2, 4), sl.tolist()) if v > 0.0}
-    layer_ms = by_slices[1]
+    layer_ms = by_slices[x.default_slices]
 
     # ---- its phases, each timed on its own (a barrier closes every phase that writes to peers)
     quant_ms = 0.0            # fused into the push
@@ -546,7 +547,7 @@ def bench_ep_prefill(device, rank, world, steps, warmup, peaks, cfg=EP):
                               "configuration states; the layer below does not use it",
            "valid_rows_this_rank": valid, "m_total_this_rank": m_total,
            "parity": "ok" if ok_ranks == world else "FAILED", "parity_rank0": parity,
-           "layer_ms": layer_ms,
+           "layer_ms": layer_ms, "layer_push_slices": x.default_slices,
            "layer_ms_by_push_slices": {str(n): v for n, v in by_slices.items()},
            "layer": {"exchange": "peer-memory stores (dg_ep_plan / dg_ep_push with the per-token quantisation "
                                  "fused in / dg_ep_barrier), result rows scattered home by the down GEMM's "
